@@ -1,0 +1,853 @@
+// Collective kernels over peer-mapped memory (NVLink 5 / NVSwitch), sm_100a.
+//
+// Each kernel is the whole collective: it stages or pushes data into the
+// peers' arenas with 16-byte stores, meets the peers on the signal pad, and
+// reduces / pulls with 16-byte loads, applying the wire cast (fp32 → bf16 on
+// the wire, fp32 accumulation) and the AVG scale in registers.  These replace
+// the reference's host loops of socket send/recv plus Metal reduce kernels
+// (csrc/backend/AllreduceAlgos.cpp:52-206, ProcessGroupMCCL.cpp:188-601,
+// csrc/metal/shaders.metal:196-552); schedule names follow the reference:
+//   twoshot  = "butterfly": direct reduce-scatter + direct allgather
+//   oneshot  = latency path used where the reference picks "tree" under auto
+//   ring, tree = same step structure as the reference, flags instead of sockets
+//   nvls     = in-switch reduction with multimem.ld_reduce / multimem.st
+//
+// blockIdx.y is the virtual rank and is non-zero only in single-GPU
+// emulation, where all ranks' CTAs run as one cooperative launch so that the
+// index arithmetic and the flag protocol can be tested on one device.
+#include "collectives.hpp"
+
+#include <cstdio>
+
+#include "comm_device.cuh"
+
+namespace mccl {
+namespace dev {
+
+namespace {
+
+__device__ __forceinline__ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+__device__ __forceinline__ int valid_in_pack(long long first, long long limit, int pack) {
+  long long left = limit - first;
+  return left >= pack ? pack : (left > 0 ? static_cast<int>(left) : 0);
+}
+
+// Copies n bytes; both pointers may have any alignment.  Work is split over
+// the threads of this CTA only (the caller has already picked the CTA's byte
+// range when more than one CTA shares a copy).
+__device__ __forceinline__ void cta_copy_bytes(char* dst, const char* src, unsigned long long n) {
+  if (n == 0) return;
+  if (aligned16(dst) && aligned16(src)) {
+    unsigned long long vecs = n / 16;
+    unsigned long long i = threadIdx.x;
+    // four independent 16-byte transfers in flight per thread
+    for (; i + 3ull * blockDim.x < vecs; i += 4ull * blockDim.x) {
+      uint4 a = reinterpret_cast<const uint4*>(src)[i];
+      uint4 b = reinterpret_cast<const uint4*>(src)[i + blockDim.x];
+      uint4 c = reinterpret_cast<const uint4*>(src)[i + 2ull * blockDim.x];
+      uint4 d = reinterpret_cast<const uint4*>(src)[i + 3ull * blockDim.x];
+      reinterpret_cast<uint4*>(dst)[i] = a;
+      reinterpret_cast<uint4*>(dst)[i + blockDim.x] = b;
+      reinterpret_cast<uint4*>(dst)[i + 2ull * blockDim.x] = c;
+      reinterpret_cast<uint4*>(dst)[i + 3ull * blockDim.x] = d;
+    }
+    for (; i < vecs; i += blockDim.x) reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(src)[i];
+    for (unsigned long long b = vecs * 16 + threadIdx.x; b < n; b += blockDim.x) dst[b] = src[b];
+  } else if (((reinterpret_cast<uintptr_t>(dst) | reinterpret_cast<uintptr_t>(src)) & 3u) == 0) {
+    unsigned long long words = n / 4;
+    for (unsigned long long i = threadIdx.x; i < words; i += blockDim.x)
+      reinterpret_cast<uint32_t*>(dst)[i] = reinterpret_cast<const uint32_t*>(src)[i];
+    for (unsigned long long b = words * 4 + threadIdx.x; b < n; b += blockDim.x) dst[b] = src[b];
+  } else {
+    for (unsigned long long b = threadIdx.x; b < n; b += blockDim.x) dst[b] = src[b];
+  }
+}
+
+// Byte range [begin, end) of an n-byte segment owned by this CTA, in 16-byte units.
+__device__ __forceinline__ void cta_byte_span(unsigned long long n, unsigned long long& begin, unsigned long long& end) {
+  unsigned long long units = (n + 15) / 16;
+  unsigned long long per = (units + gridDim.x - 1) / gridDim.x;
+  begin = blockIdx.x * per * 16;
+  end = begin + per * 16;
+  if (begin > n) begin = n;
+  if (end > n) end = n;
+}
+
+}  // namespace
+
+// ============================================================== two-shot ==
+// kScatter = false: allreduce.  kScatter = true: reduce-scatter (input holds
+// world chunks of exactly a.numel elements; output is this rank's chunk).
+template <typename T, typename W, bool kScatter>
+__global__ void __launch_bounds__(kThreads) twoshot_kernel(DevComm c, CollArgs a) {
+  using PK = Pack<T, W>;
+  constexpr int E = PK::kElems;
+  using Acc = typename PK::Acc;
+  const int vr = blockIdx.y, rank = c.rank_base + vr, N = c.world;
+  CtaSync s = cta_begin(c, vr);
+  const T* in = static_cast<const T*>(a.in[vr]);
+  T* out = static_cast<T*>(a.out[vr]);
+  const long long per = a.per;                         // arena slot length (elements, padded)
+  const long long stride = kScatter ? a.stride : per;  // distance between chunks in the input
+  const long long total = kScatter ? a.stride * (N - 1) + a.numel : a.numel;
+  const size_t slot_bytes = static_cast<size_t>(per) * sizeof(W);
+  const size_t recv_off = static_cast<size_t>(s.half) * c.half_bytes;
+  const size_t red_off = recv_off + static_cast<size_t>(N) * slot_bytes;
+  long long pb, pe;
+  cta_span(per / E, pb, pe);
+  auto chunk_limit = [&](int p) -> long long {  // one past the last valid element of chunk p
+    long long lim = static_cast<long long>(p) * stride + (kScatter ? a.numel : per);
+    return lim < total ? lim : total;
+  };
+
+  // Phase 1: push my copy of chunk p to rank p.
+  for (long long i = pb + threadIdx.x; i < pe; i += blockDim.x) {
+#pragma unroll 1
+    for (int k = 1; k < N; ++k) {
+      const int p = (rank + k) % N;
+      const long long e0 = static_cast<long long>(p) * stride + i * E;
+      const int nv = valid_in_pack(e0, chunk_limit(p), E);
+      if (nv <= 0) continue;
+      Acc v[E];
+      load_pack<T, E, Acc>(in + e0, v, nv, aligned16(in + e0));
+      W* dst = reinterpret_cast<W*>(c.arena[p] + recv_off + static_cast<size_t>(rank) * slot_bytes) + i * E;
+      store_pack<W, E, Acc>(dst, v, E, true);
+    }
+  }
+  if (barrier_all(c, vr, rank, s, PH_PUSH)) {
+    cta_end(c, vr, s);
+    return;
+  }
+
+  // Phase 2: reduce chunk `rank` (own copy in full precision, peers' from the arena).
+  for (long long i = pb + threadIdx.x; i < pe; i += blockDim.x) {
+    const long long e0 = static_cast<long long>(rank) * stride + i * E;
+    const int nv = valid_in_pack(e0, chunk_limit(rank), E);
+    if (nv <= 0) continue;
+    Acc acc[E];
+    load_pack<T, E, Acc>(in + e0, acc, nv, aligned16(in + e0));
+#pragma unroll 1
+    for (int src = 0; src < N; ++src) {
+      if (src == rank) continue;
+      Acc v[E];
+      const W* sp = reinterpret_cast<const W*>(c.arena[rank] + recv_off + static_cast<size_t>(src) * slot_bytes) + i * E;
+      load_pack<W, E, Acc>(sp, v, E, true);
+#pragma unroll
+      for (int e = 0; e < E; ++e) acc[e] = apply_op<Acc>(a.op, acc[e], v[e]);
+    }
+    if (a.op == OP_AVG) {
+#pragma unroll
+      for (int e = 0; e < E; ++e) acc[e] = finish_avg<Acc>(acc[e], N, a.inv_world);
+    }
+    if constexpr (kScatter) {
+      T* op = out + i * E;
+      store_pack<T, E, Acc>(op, acc, nv, aligned16(op));
+    } else {
+      round_through_wire<T, W, E, Acc>(acc);
+      store_pack<W, E, Acc>(reinterpret_cast<W*>(c.arena[rank] + red_off) + i * E, acc, E, true);
+      store_pack<T, E, Acc>(out + e0, acc, nv, aligned16(out + e0));
+    }
+  }
+  if constexpr (kScatter) {
+    cta_end(c, vr, s);
+    return;
+  } else {
+    if (barrier_all(c, vr, rank, s, PH_REDUCE)) {
+      cta_end(c, vr, s);
+      return;
+    }
+    // Phase 3: pull every other rank's reduced chunk.  All loads of one pack
+    // index are issued before the stores so that N-1 remote reads are in flight.
+    for (long long i = pb + threadIdx.x; i < pe; i += blockDim.x) {
+      uint4 raw[kMaxRanks - 1];
+#pragma unroll
+      for (int k = 1; k < kMaxRanks; ++k) {
+        if (k < N) {
+          const int p = (rank + k) % N;
+          raw[k - 1] = *reinterpret_cast<const uint4*>(c.arena[p] + red_off + static_cast<size_t>(i) * 16);
+        }
+      }
+#pragma unroll
+      for (int k = 1; k < kMaxRanks; ++k) {
+        if (k < N) {
+          const int p = (rank + k) % N;
+          const long long e0 = static_cast<long long>(p) * per + i * E;
+          const int nv = valid_in_pack(e0, chunk_limit(p), E);
+          if (nv > 0) {
+            Acc v[E];
+            const W* w = reinterpret_cast<const W*>(&raw[k - 1]);
+#pragma unroll
+            for (int e = 0; e < E; ++e) v[e] = static_cast<Acc>(Elem<W>::up(w[e]));
+            store_pack<T, E, Acc>(out + e0, v, nv, aligned16(out + e0));
+          }
+        }
+      }
+    }
+    cta_end(c, vr, s);
+  }
+}
+
+// =============================================================== one-shot ==
+template <typename T, typename W>
+__global__ void __launch_bounds__(kThreads) oneshot_kernel(DevComm c, CollArgs a) {
+  using PK = Pack<T, W>;
+  constexpr int E = PK::kElems;
+  using Acc = typename PK::Acc;
+  const int vr = blockIdx.y, rank = c.rank_base + vr, N = c.world;
+  CtaSync s = cta_begin(c, vr);
+  const T* in = static_cast<const T*>(a.in[vr]);
+  T* out = static_cast<T*>(a.out[vr]);
+  const long long padded = (a.numel + 15) / 16 * 16;
+  const size_t slot_bytes = static_cast<size_t>(padded) * sizeof(W);
+  const size_t base = static_cast<size_t>(s.half) * c.half_bytes;
+  long long pb, pe;
+  cta_span(padded / E, pb, pe);
+  const bool al_in = aligned16(in), al_out = aligned16(out);
+
+  // Phase 1: every rank gets my whole (wire-cast) input, my own arena included,
+  // so that all ranks later add the same N values in the same order.
+  for (long long i = pb + threadIdx.x; i < pe; i += blockDim.x) {
+    const long long e0 = i * E;
+    const int nv = valid_in_pack(e0, a.numel, E);
+    Acc v[E];
+    load_pack<T, E, Acc>(in + e0, v, nv, al_in);
+    uint4 raw;
+    {
+      W* w = reinterpret_cast<W*>(&raw);
+#pragma unroll
+      for (int e = 0; e < E; ++e) w[e] = Elem<W>::down(static_cast<typename Elem<W>::Acc>(v[e]));
+    }
+#pragma unroll
+    for (int k = 0; k < kMaxRanks; ++k) {
+      if (k < N) {
+        const int p = (rank + k) % N;
+        *reinterpret_cast<uint4*>(c.arena[p] + base + static_cast<size_t>(rank) * slot_bytes + static_cast<size_t>(i) * 16) = raw;
+      }
+    }
+  }
+  if (barrier_all(c, vr, rank, s, PH_PUSH)) {
+    cta_end(c, vr, s);
+    return;
+  }
+  // Phase 2: reduce the N slots in rank order.
+  for (long long i = pb + threadIdx.x; i < pe; i += blockDim.x) {
+    const long long e0 = i * E;
+    const int nv = valid_in_pack(e0, a.numel, E);
+    if (nv <= 0) continue;
+    uint4 raw[kMaxRanks];
+#pragma unroll
+    for (int src = 0; src < kMaxRanks; ++src)
+      if (src < N)
+        raw[src] = *reinterpret_cast<const uint4*>(c.arena[rank] + base + static_cast<size_t>(src) * slot_bytes + static_cast<size_t>(i) * 16);
+    Acc acc[E];
+    {
+      const W* w = reinterpret_cast<const W*>(&raw[0]);
+#pragma unroll
+      for (int e = 0; e < E; ++e) acc[e] = static_cast<Acc>(Elem<W>::up(w[e]));
+    }
+#pragma unroll
+    for (int src = 1; src < kMaxRanks; ++src) {
+      if (src < N) {
+        const W* w = reinterpret_cast<const W*>(&raw[src]);
+#pragma unroll
+        for (int e = 0; e < E; ++e) acc[e] = apply_op<Acc>(a.op, acc[e], static_cast<Acc>(Elem<W>::up(w[e])));
+      }
+    }
+    if (a.op == OP_AVG) {
+#pragma unroll
+      for (int e = 0; e < E; ++e) acc[e] = finish_avg<Acc>(acc[e], N, a.inv_world);
+    }
+    store_pack<T, E, Acc>(out + e0, acc, nv, al_out);
+  }
+  cta_end(c, vr, s);
+}
+
+// =================================================================== ring ==
+template <typename T, typename W>
+__global__ void __launch_bounds__(kThreads) ring_kernel(DevComm c, CollArgs a) {
+  using PK = Pack<T, W>;
+  constexpr int E = PK::kElems;
+  using Acc = typename PK::Acc;
+  const int vr = blockIdx.y, rank = c.rank_base + vr, N = c.world;
+  CtaSync s = cta_begin(c, vr);
+  const T* in = static_cast<const T*>(a.in[vr]);
+  T* out = static_cast<T*>(a.out[vr]);
+  const long long per = a.per;
+  const size_t slot_bytes = static_cast<size_t>(per) * sizeof(W);
+  const size_t base = static_cast<size_t>(s.half) * c.half_bytes;
+  auto rs_buf = [&](int r, int k) { return reinterpret_cast<W*>(c.arena[r] + base + static_cast<size_t>(k) * slot_bytes); };
+  auto ag_buf = [&](int r, int k) { return reinterpret_cast<W*>(c.arena[r] + base + static_cast<size_t>(N - 1 + k) * slot_bytes); };
+  const int next = (rank + 1) % N, prev = (rank + N - 1) % N;
+  long long pb, pe;
+  cta_span(per / E, pb, pe);
+  auto chunk_limit = [&](int p) -> long long {
+    long long lim = static_cast<long long>(p + 1) * per;
+    return lim < a.numel ? lim : a.numel;
+  };
+  const uint32_t e0v = s.epoch;
+  bool failed = false;
+
+  // Reduce-scatter: N-1 steps.
+  for (int k = 0; k < N - 1 && !failed; ++k) {
+    const int sc = ((rank - k) % N + N) % N;
+    for (long long i = pb + threadIdx.x; i < pe; i += blockDim.x) {
+      const long long el = static_cast<long long>(sc) * per + i * E;
+      const int nv = valid_in_pack(el, chunk_limit(sc), E);
+      Acc acc[E];
+      load_pack<T, E, Acc>(in + el, acc, nv, aligned16(in + el));
+      if (k > 0) {
+        Acc v[E];
+        load_pack<W, E, Acc>(rs_buf(rank, k - 1) + i * E, v, E, true);
+#pragma unroll
+        for (int e = 0; e < E; ++e) acc[e] = apply_op<Acc>(a.op, acc[e], v[e]);
+      }
+      store_pack<W, E, Acc>(rs_buf(next, k) + i * E, acc, E, true);
+    }
+    signal_one(c, rank, next, e0v + k + 1, s);
+    failed = wait_one(c, vr, rank, prev, e0v + k + 1, PH_RING);
+  }
+  s.epoch = e0v + 2 * (N - 1);
+  if (failed) {
+    cta_end(c, vr, s);
+    return;
+  }
+  // Finish the chunk this rank owns and start the allgather with it.
+  const int fc = (rank + 1) % N;
+  for (long long i = pb + threadIdx.x; i < pe; i += blockDim.x) {
+    const long long el = static_cast<long long>(fc) * per + i * E;
+    const int nv = valid_in_pack(el, chunk_limit(fc), E);
+    Acc acc[E], v[E];
+    load_pack<T, E, Acc>(in + el, acc, nv, aligned16(in + el));
+    load_pack<W, E, Acc>(rs_buf(rank, N - 2) + i * E, v, E, true);
+#pragma unroll
+    for (int e = 0; e < E; ++e) acc[e] = apply_op<Acc>(a.op, acc[e], v[e]);
+    if (a.op == OP_AVG) {
+#pragma unroll
+      for (int e = 0; e < E; ++e) acc[e] = finish_avg<Acc>(acc[e], N, a.inv_world);
+    }
+    round_through_wire<T, W, E, Acc>(acc);
+    store_pack<W, E, Acc>(ag_buf(next, 0) + i * E, acc, E, true);
+    if (nv > 0) store_pack<T, E, Acc>(out + el, acc, nv, aligned16(out + el));
+  }
+  // Allgather: N-1 steps, forwarding what arrives.
+  for (int k = 0; k < N - 1 && !failed; ++k) {
+    signal_one(c, rank, next, e0v + (N - 1) + k + 1, s);
+    failed = wait_one(c, vr, rank, prev, e0v + (N - 1) + k + 1, PH_RING);
+    if (failed) break;
+    const int rc = ((rank - k) % N + N) % N;
+    for (long long i = pb + threadIdx.x; i < pe; i += blockDim.x) {
+      const long long el = static_cast<long long>(rc) * per + i * E;
+      const int nv = valid_in_pack(el, chunk_limit(rc), E);
+      Acc v[E];
+      load_pack<W, E, Acc>(ag_buf(rank, k) + i * E, v, E, true);
+      if (k < N - 2) store_pack<W, E, Acc>(ag_buf(next, k + 1) + i * E, v, E, true);
+      if (nv > 0) store_pack<T, E, Acc>(out + el, v, nv, aligned16(out + el));
+    }
+  }
+  cta_end(c, vr, s);
+}
+
+// =================================================================== tree ==
+template <typename T, typename W>
+__global__ void __launch_bounds__(kThreads) tree_kernel(DevComm c, CollArgs a) {
+  using PK = Pack<T, W>;
+  constexpr int E = PK::kElems;
+  using Acc = typename PK::Acc;
+  const int vr = blockIdx.y, rank = c.rank_base + vr, N = c.world;
+  CtaSync s = cta_begin(c, vr);
+  const T* in = static_cast<const T*>(a.in[vr]);
+  T* out = static_cast<T*>(a.out[vr]);
+  const long long padded = (a.numel + 15) / 16 * 16;
+  const size_t slot_bytes = static_cast<size_t>(padded) * sizeof(W);
+  const size_t base = static_cast<size_t>(s.half) * c.half_bytes;
+  int R = 0;
+  while ((1 << R) < N) ++R;
+  auto tbuf = [&](int r, int j) { return reinterpret_cast<W*>(c.arena[r] + base + static_cast<size_t>(j) * slot_bytes); };
+  auto bbuf = [&](int r) { return reinterpret_cast<W*>(c.arena[r] + base + static_cast<size_t>(R) * slot_bytes); };
+  long long pb, pe;
+  cta_span(padded / E, pb, pe);
+  const bool al_in = aligned16(in), al_out = aligned16(out);
+  const uint32_t e0v = s.epoch;
+  s.epoch = e0v + R + 1;
+  bool failed = false;
+
+  // The running partial lives in `out`.
+  if (out != in) {
+    for (long long i = pb + threadIdx.x; i < pe; i += blockDim.x) {
+      const int nv = valid_in_pack(i * E, a.numel, E);
+      if (nv <= 0) continue;
+      Acc v[E];
+      load_pack<T, E, Acc>(in + i * E, v, nv, al_in);
+      store_pack<T, E, Acc>(out + i * E, v, nv, al_out);
+    }
+  }
+  // Binomial reduce towards rank 0.
+  for (int j = 0; j < R && !failed; ++j) {
+    const int mask = 1 << j;
+    if (rank & mask) {
+      const int parent = rank - mask;
+      for (long long i = pb + threadIdx.x; i < pe; i += blockDim.x) {
+        const int nv = valid_in_pack(i * E, a.numel, E);
+        Acc v[E];
+        load_pack<T, E, Acc>(out + i * E, v, nv, al_out);
+        store_pack<W, E, Acc>(tbuf(parent, j) + i * E, v, E, true);
+      }
+      signal_one(c, rank, parent, e0v + 1 + j, s);
+      break;
+    }
+    if (rank + mask < N) {
+      failed = wait_one(c, vr, rank, rank + mask, e0v + 1 + j, PH_TREE);
+      if (failed) break;
+      for (long long i = pb + threadIdx.x; i < pe; i += blockDim.x) {
+        const int nv = valid_in_pack(i * E, a.numel, E);
+        if (nv <= 0) continue;
+        Acc acc[E], v[E];
+        load_pack<T, E, Acc>(out + i * E, acc, nv, al_out);
+        load_pack<W, E, Acc>(tbuf(rank, j) + i * E, v, E, true);
+#pragma unroll
+        for (int e = 0; e < E; ++e) acc[e] = apply_op<Acc>(a.op, acc[e], v[e]);
+        store_pack<T, E, Acc>(out + i * E, acc, nv, al_out);
+      }
+      __syncthreads();
+    }
+  }
+  if (failed) {
+    cta_end(c, vr, s);
+    return;
+  }
+  // Binomial broadcast from rank 0.
+  int low = 1;
+  if (rank == 0) {
+    while (low < N) low <<= 1;
+    // Root finalises: AVG scale, round through the wire type, keep a wire copy to forward.
+    for (long long i = pb + threadIdx.x; i < pe; i += blockDim.x) {
+      const int nv = valid_in_pack(i * E, a.numel, E);
+      Acc acc[E];
+      load_pack<T, E, Acc>(out + i * E, acc, nv, al_out);
+      if (a.op == OP_AVG) {
+#pragma unroll
+        for (int e = 0; e < E; ++e) acc[e] = finish_avg<Acc>(acc[e], N, a.inv_world);
+      }
+      round_through_wire<T, W, E, Acc>(acc);
+      store_pack<W, E, Acc>(bbuf(rank) + i * E, acc, E, true);
+      if (nv > 0) store_pack<T, E, Acc>(out + i * E, acc, nv, al_out);
+    }
+  } else {
+    while (!(rank & low)) low <<= 1;  // lowest set bit: parent = rank - low
+    failed = wait_one(c, vr, rank, rank - low, e0v + R + 1, PH_TREE);
+    if (failed) {
+      cta_end(c, vr, s);
+      return;
+    }
+    for (long long i = pb + threadIdx.x; i < pe; i += blockDim.x) {
+      const int nv = valid_in_pack(i * E, a.numel, E);
+      if (nv <= 0) continue;
+      Acc v[E];
+      load_pack<W, E, Acc>(bbuf(rank) + i * E, v, E, true);
+      store_pack<T, E, Acc>(out + i * E, v, nv, al_out);
+    }
+  }
+  for (int mask = low >> 1; mask > 0; mask >>= 1) {
+    const int child = rank + mask;
+    if (child >= N) continue;
+    for (long long i = pb + threadIdx.x; i < pe; i += blockDim.x)
+      *reinterpret_cast<uint4*>(reinterpret_cast<char*>(bbuf(child)) + static_cast<size_t>(i) * 16) =
+          *reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(bbuf(rank)) + static_cast<size_t>(i) * 16);
+    signal_one(c, rank, child, e0v + R + 1, s);
+  }
+  cta_end(c, vr, s);
+}
+
+// =================================================================== NVLS ==
+// In-switch reduction.  `local` is this rank's mapping of a symmetric buffer
+// holding the (wire-typed) input, `mc` the multicast mapping of the same
+// buffer; the reduced values are written back through the multicast mapping,
+// so afterwards every rank's copy holds the result.  When kStage is set the
+// kernel first copies `in` into the arena and afterwards copies the result to
+// `out`; otherwise the caller's buffer already lives in symmetric memory.
+template <typename W> struct Multimem;
+template <> struct Multimem<float> {
+  static __device__ __forceinline__ uint4 ld_reduce(const void* mc) {
+    uint4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");
+    return v;
+  }
+};
+template <> struct Multimem<__nv_bfloat16> {
+  static __device__ __forceinline__ uint4 ld_reduce(const void* mc) {
+    uint4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");
+    return v;
+  }
+};
+template <> struct Multimem<__half> {
+  static __device__ __forceinline__ uint4 ld_reduce(const void* mc) {
+    uint4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");
+    return v;
+  }
+};
+__device__ __forceinline__ void multimem_st16(void* mc, uint4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(mc), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
+
+template <typename T, typename W, bool kStage>
+__global__ void __launch_bounds__(kThreads) nvls_kernel(DevComm c, CollArgs a, char* local_sym, char* mc_sym) {
+  using PK = Pack<T, W>;
+  constexpr int E = PK::kElems;
+  using Acc = typename PK::Acc;
+  constexpr int WE = 16 / sizeof(W);  // wire elements per 16 bytes
+  const int rank = c.rank_base, N = c.world;
+  CtaSync s = cta_begin(c, 0);
+  const long long per = a.per;
+  long long pb, pe;
+  char* stage_local;
+  char* stage_mc;
+  char* result_local;
+  char* result_mc;
+  if constexpr (kStage) {
+    const size_t base = static_cast<size_t>(s.half) * c.half_bytes;
+    const size_t region = static_cast<size_t>(N) * per * sizeof(W);
+    stage_local = c.arena[rank] + base;
+    stage_mc = c.mc_arena + base;
+    result_local = stage_local + region;
+    result_mc = stage_mc + region;
+    // Phase 0: wire-cast copy of the whole input into my arena.  The work is
+    // split per chunk so that CTA b stages exactly the part of every chunk
+    // that CTA b of the chunk's owner will reduce.
+    const T* in = static_cast<const T*>(a.in[0]);
+    cta_span(per / E, pb, pe);
+    for (int p = 0; p < N; ++p) {
+      for (long long i = pb + threadIdx.x; i < pe; i += blockDim.x) {
+        const long long el = static_cast<long long>(p) * per + i * E;
+        const int nv = valid_in_pack(el, a.numel, E);
+        Acc v[E];
+        load_pack<T, E, Acc>(in + el, v, nv, aligned16(in + el));
+        store_pack<W, E, Acc>(reinterpret_cast<W*>(stage_local) + el, v, E, true);
+      }
+    }
+  } else {
+    stage_local = result_local = local_sym;
+    stage_mc = result_mc = mc_sym;
+  }
+  if (barrier_all(c, 0, rank, s, PH_NVLS)) {
+    cta_end(c, 0, s);
+    return;
+  }
+  // Phase 1: reduce chunk `rank` in the switch and broadcast it back.
+  cta_span(per / WE, pb, pe);
+  const size_t chunk_byte0 = static_cast<size_t>(rank) * per * sizeof(W);
+  for (long long i = pb + threadIdx.x; i < pe; i += blockDim.x) {
+    const size_t off = chunk_byte0 + static_cast<size_t>(i) * 16;
+    uint4 v = Multimem<W>::ld_reduce(stage_mc + off);
+    if (a.op == OP_AVG) {
+      W* w = reinterpret_cast<W*>(&v);
+#pragma unroll
+      for (int e = 0; e < WE; ++e) w[e] = Elem<W>::down(Elem<W>::up(w[e]) * a.inv_world);
+    }
+    multimem_st16(result_mc + off, v);
+  }
+  if (barrier_all(c, 0, rank, s, PH_NVLS)) {
+    cta_end(c, 0, s);
+    return;
+  }
+  if constexpr (kStage) {
+    // Phase 2: copy the result out of my arena (same per-chunk split).
+    T* out = static_cast<T*>(a.out[0]);
+    cta_span(per / E, pb, pe);
+    for (int p = 0; p < N; ++p) {
+      for (long long i = pb + threadIdx.x; i < pe; i += blockDim.x) {
+        const long long el = static_cast<long long>(p) * per + i * E;
+        const int nv = valid_in_pack(el, a.numel, E);
+        if (nv <= 0) continue;
+        Acc v[E];
+        load_pack<W, E, Acc>(reinterpret_cast<const W*>(result_local) + el, v, E, true);
+        store_pack<T, E, Acc>(out + el, v, nv, aligned16(out + el));
+      }
+    }
+  }
+  cta_end(c, 0, s);
+}
+
+// ====================================================== symmetric in-place ==
+// Allreduce of a buffer that every rank allocated in the symmetric heap, so
+// peers' copies are directly addressable: a.in[r] is rank r's copy as mapped
+// here.  No staging: rank r reads chunk r of every copy, reduces, writes its
+// own copy, and after a meeting everyone pulls the other chunks.  A third
+// meeting keeps a fast rank from overwriting its copy while peers still read it.
+template <typename T>
+__global__ void __launch_bounds__(kThreads) symm_allreduce_kernel(DevComm c, CollArgs a) {
+  using Acc = typename Elem<T>::Acc;
+  constexpr int E = 16 / sizeof(T);
+  const int vr = blockIdx.y, rank = c.rank_base + vr, N = c.world;
+  CtaSync s = cta_begin(c, vr);
+  const long long per = a.per;
+  long long pb, pe;
+  cta_span(per / E, pb, pe);
+  T* mine = static_cast<T*>(const_cast<void*>(a.in[rank]));
+  bool failed = barrier_all(c, vr, rank, s, PH_PUSH);
+  if (!failed) {
+    for (long long i = pb + threadIdx.x; i < pe; i += blockDim.x) {
+      const long long el = static_cast<long long>(rank) * per + i * E;
+      const int nv = valid_in_pack(el, a.numel, E);
+      if (nv <= 0) continue;
+      uint4 raw[kMaxRanks];
+#pragma unroll
+      for (int src = 0; src < kMaxRanks; ++src)
+        if (src < N) raw[src] = *reinterpret_cast<const uint4*>(static_cast<const T*>(a.in[src]) + el);
+      Acc acc[E];
+#pragma unroll
+      for (int e = 0; e < E; ++e) acc[e] = static_cast<Acc>(Elem<T>::up(reinterpret_cast<const T*>(&raw[0])[e]));
+#pragma unroll
+      for (int src = 1; src < kMaxRanks; ++src) {
+        if (src < N) {
+#pragma unroll
+          for (int e = 0; e < E; ++e)
+            acc[e] = apply_op<Acc>(a.op, acc[e], static_cast<Acc>(Elem<T>::up(reinterpret_cast<const T*>(&raw[src])[e])));
+        }
+      }
+      if (a.op == OP_AVG) {
+#pragma unroll
+        for (int e = 0; e < E; ++e) acc[e] = finish_avg<Acc>(acc[e], N, a.inv_world);
+      }
+      store_pack<T, E, Acc>(mine + el, acc, E, true);
+    }
+    failed = barrier_all(c, vr, rank, s, PH_REDUCE);
+  }
+  if (!failed) {
+    for (long long i = pb + threadIdx.x; i < pe; i += blockDim.x) {
+      uint4 raw[kMaxRanks - 1];
+#pragma unroll
+      for (int k = 1; k < kMaxRanks; ++k) {
+        if (k < N) {
+          const int p = (rank + k) % N;
+          raw[k - 1] = *reinterpret_cast<const uint4*>(static_cast<const T*>(a.in[p]) + static_cast<long long>(p) * per + i * E);
+        }
+      }
+#pragma unroll
+      for (int k = 1; k < kMaxRanks; ++k) {
+        if (k < N) {
+          const int p = (rank + k) % N;
+          *reinterpret_cast<uint4*>(mine + static_cast<long long>(p) * per + i * E) = raw[k - 1];
+        }
+      }
+    }
+    barrier_all(c, vr, rank, s, PH_GATHER);
+  }
+  cta_end(c, vr, s);
+}
+
+// ============================================================== allgather ==
+// Bytes, any alignment.  Stage my block in my arena, meet, pull the others.
+__global__ void __launch_bounds__(kThreads) allgather_kernel(DevComm c, CollArgs a) {
+  const int vr = blockIdx.y, rank = c.rank_base + vr, N = c.world;
+  CtaSync s = cta_begin(c, vr);
+  const unsigned long long nbytes = static_cast<unsigned long long>(a.numel);
+  const unsigned long long stride = static_cast<unsigned long long>(a.stride);
+  const char* in = static_cast<const char*>(a.in[vr]);
+  char* out = static_cast<char*>(a.out[vr]);
+  const size_t base = static_cast<size_t>(s.half) * c.half_bytes;
+  unsigned long long b0, b1;
+  cta_byte_span(nbytes, b0, b1);
+  cta_copy_bytes(c.arena[rank] + base + b0, in + b0, b1 - b0);
+  if (out + static_cast<size_t>(rank) * stride != in) cta_copy_bytes(out + static_cast<size_t>(rank) * stride + b0, in + b0, b1 - b0);
+  if (barrier_all(c, vr, rank, s, PH_GATHER)) {
+    cta_end(c, vr, s);
+    return;
+  }
+  for (int k = 1; k < N; ++k) {
+    const int p = (rank + k) % N;
+    cta_copy_bytes(out + static_cast<size_t>(p) * stride + b0, c.arena[p] + base + b0, b1 - b0);
+  }
+  cta_end(c, vr, s);
+}
+
+// ============================================================== broadcast ==
+// Scatter + allgather: the root pushes slice p of its buffer into rank p's
+// arena, then every rank pulls the other slices from their holders, so the
+// root's links carry the message once instead of N-1 times.
+__global__ void __launch_bounds__(kThreads) broadcast_kernel(DevComm c, CollArgs a) {
+  const int vr = blockIdx.y, rank = c.rank_base + vr, N = c.world, root = a.root;
+  CtaSync s = cta_begin(c, vr);
+  const unsigned long long nbytes = static_cast<unsigned long long>(a.numel);
+  char* data = static_cast<char*>(a.out[vr]);
+  const size_t base = static_cast<size_t>(s.half) * c.half_bytes;
+  const unsigned long long slice = (nbytes + N - 1) / N;
+  const unsigned long long slice16 = (slice + 15) / 16 * 16;  // slices start on 16-byte boundaries
+  auto slice_len = [&](int p) -> unsigned long long {
+    unsigned long long lo = p * slice16;
+    if (lo >= nbytes) return 0ull;
+    unsigned long long hi = lo + slice16;
+    return (hi < nbytes ? hi : nbytes) - lo;
+  };
+  if (rank == root) {
+    for (int k = 0; k < N; ++k) {
+      const int p = (rank + k) % N;
+      unsigned long long b0, b1;
+      cta_byte_span(slice_len(p), b0, b1);
+      cta_copy_bytes(c.arena[p] + base + b0, data + p * slice16 + b0, b1 - b0);
+    }
+  }
+  if (barrier_all(c, vr, rank, s, PH_GATHER)) {
+    cta_end(c, vr, s);
+    return;
+  }
+  if (rank != root) {
+    for (int k = 0; k < N; ++k) {
+      const int p = (rank + k) % N;
+      unsigned long long b0, b1;
+      cta_byte_span(slice_len(p), b0, b1);
+      cta_copy_bytes(data + p * slice16 + b0, c.arena[p] + base + b0, b1 - b0);
+    }
+  }
+  cta_end(c, vr, s);
+}
+
+// =============================================================== alltoall ==
+// P2P dispatch: rank r stages the segment meant for rank q in slot q of its
+// own arena; after the meeting, rank q pulls slot q of every rank straight
+// into its output at that peer's offset.  Segment sizes may differ per pair.
+__global__ void __launch_bounds__(kThreads) alltoall_kernel(DevComm c, A2AArgs a) {
+  const int vr = blockIdx.y, rank = c.rank_base + vr, N = c.world;
+  CtaSync s = cta_begin(c, vr);
+  const char* in = static_cast<const char*>(a.in[vr]);
+  char* out = static_cast<char*>(a.out[vr]);
+  const size_t base = static_cast<size_t>(s.half) * c.half_bytes;
+  for (int k = 0; k < N; ++k) {
+    const int q = (rank + k) % N;
+    unsigned long long b0, b1;
+    cta_byte_span(a.in_len[vr][q], b0, b1);
+    if (q == rank)
+      cta_copy_bytes(out + a.out_off[vr][q] + b0, in + a.in_off[vr][q] + b0, b1 - b0);
+    else
+      cta_copy_bytes(c.arena[rank] + base + q * a.slot_bytes + b0, in + a.in_off[vr][q] + b0, b1 - b0);
+  }
+  if (barrier_all(c, vr, rank, s, PH_GATHER)) {
+    cta_end(c, vr, s);
+    return;
+  }
+  for (int k = 1; k < N; ++k) {
+    const int p = (rank + k) % N;
+    unsigned long long b0, b1;
+    cta_byte_span(a.out_len[vr][p], b0, b1);
+    cta_copy_bytes(out + a.out_off[vr][p] + b0, c.arena[p] + base + rank * a.slot_bytes + b0, b1 - b0);
+  }
+  cta_end(c, vr, s);
+}
+
+// ================================================================ barrier ==
+__global__ void __launch_bounds__(32) barrier_kernel(DevComm c) {
+  const int vr = blockIdx.y, rank = c.rank_base + vr;
+  CtaSync s = cta_begin(c, vr);
+  barrier_all(c, vr, rank, s, PH_BARRIER);
+  cta_end(c, vr, s);
+}
+
+// ============================================================== launchers ==
+namespace {
+
+template <typename... KArgs, typename... Args>
+cudaError_t launch(void (*kernel)(KArgs...), const LaunchCfg& cfg, int threads, Args... args) {
+  dim3 grid(cfg.ctas, cfg.nlocal > 1 ? cfg.nlocal : 1);
+  if (cfg.nlocal > 1) {
+    void* params[] = {static_cast<void*>(&args)...};
+    return cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(kernel), grid, dim3(threads), params, 0, cfg.stream);
+  }
+  kernel<<<grid, threads, 0, cfg.stream>>>(args...);
+  return cudaGetLastError();
+}
+
+enum class Sched { TWOSHOT, SCATTER, ONESHOT, RING, TREE };
+
+template <typename T, typename W>
+cudaError_t launch_typed(Sched k, const DevComm& c, const CollArgs& a, const LaunchCfg& cfg) {
+  switch (k) {
+    case Sched::TWOSHOT: return launch(twoshot_kernel<T, W, false>, cfg, kThreads, c, a);
+    case Sched::SCATTER: return launch(twoshot_kernel<T, W, true>, cfg, kThreads, c, a);
+    case Sched::ONESHOT: return launch(oneshot_kernel<T, W>, cfg, kThreads, c, a);
+    case Sched::RING: return launch(ring_kernel<T, W>, cfg, kThreads, c, a);
+    case Sched::TREE: return launch(tree_kernel<T, W>, cfg, kThreads, c, a);
+  }
+  return cudaErrorInvalidValue;
+}
+
+cudaError_t dispatch(Sched k, ElemType t, bool bf16_wire, const DevComm& c, const CollArgs& a, const LaunchCfg& cfg) {
+  switch (t) {
+    case ElemType::F32:
+      return bf16_wire ? launch_typed<float, __nv_bfloat16>(k, c, a, cfg) : launch_typed<float, float>(k, c, a, cfg);
+    case ElemType::F16: return launch_typed<__half, __half>(k, c, a, cfg);
+    case ElemType::BF16: return launch_typed<__nv_bfloat16, __nv_bfloat16>(k, c, a, cfg);
+    case ElemType::F64: return launch_typed<double, double>(k, c, a, cfg);
+    case ElemType::I32: return launch_typed<int32_t, int32_t>(k, c, a, cfg);
+    case ElemType::I64: return launch_typed<int64_t, int64_t>(k, c, a, cfg);
+  }
+  return cudaErrorInvalidValue;
+}
+
+}  // namespace
+
+cudaError_t launch_allreduce_twoshot(ElemType t, bool bf16_wire, const DevComm& c, const CollArgs& a, const LaunchCfg& cfg) {
+  return dispatch(Sched::TWOSHOT, t, bf16_wire, c, a, cfg);
+}
+cudaError_t launch_reduce_scatter(ElemType t, bool bf16_wire, const DevComm& c, const CollArgs& a, const LaunchCfg& cfg) {
+  return dispatch(Sched::SCATTER, t, bf16_wire, c, a, cfg);
+}
+cudaError_t launch_allreduce_oneshot(ElemType t, bool bf16_wire, const DevComm& c, const CollArgs& a, const LaunchCfg& cfg) {
+  return dispatch(Sched::ONESHOT, t, bf16_wire, c, a, cfg);
+}
+cudaError_t launch_allreduce_ring(ElemType t, bool bf16_wire, const DevComm& c, const CollArgs& a, const LaunchCfg& cfg) {
+  return dispatch(Sched::RING, t, bf16_wire, c, a, cfg);
+}
+cudaError_t launch_allreduce_tree(ElemType t, bool bf16_wire, const DevComm& c, const CollArgs& a, const LaunchCfg& cfg) {
+  return dispatch(Sched::TREE, t, bf16_wire, c, a, cfg);
+}
+
+cudaError_t launch_allreduce_nvls(ElemType t, bool bf16_wire, bool staged, const DevComm& c, const CollArgs& a,
+                                  char* local_sym, char* mc_sym, const LaunchCfg& cfg) {
+  if (cfg.nlocal > 1) return cudaErrorNotSupported;  // no multicast object inside one GPU
+#define MCCL_NVLS(T, W)                                                                       \
+  (staged ? launch(nvls_kernel<T, W, true>, cfg, kThreads, c, a, local_sym, mc_sym)           \
+          : launch(nvls_kernel<T, W, false>, cfg, kThreads, c, a, local_sym, mc_sym))
+  switch (t) {
+    case ElemType::F32: return bf16_wire ? MCCL_NVLS(float, __nv_bfloat16) : MCCL_NVLS(float, float);
+    case ElemType::F16: return MCCL_NVLS(__half, __half);
+    case ElemType::BF16: return MCCL_NVLS(__nv_bfloat16, __nv_bfloat16);
+    default: return cudaErrorNotSupported;
+  }
+#undef MCCL_NVLS
+}
+
+cudaError_t launch_allreduce_symm(ElemType t, const DevComm& c, const CollArgs& a, const LaunchCfg& cfg) {
+  switch (t) {
+    case ElemType::F32: return launch(symm_allreduce_kernel<float>, cfg, kThreads, c, a);
+    case ElemType::F16: return launch(symm_allreduce_kernel<__half>, cfg, kThreads, c, a);
+    case ElemType::BF16: return launch(symm_allreduce_kernel<__nv_bfloat16>, cfg, kThreads, c, a);
+    case ElemType::F64: return launch(symm_allreduce_kernel<double>, cfg, kThreads, c, a);
+    case ElemType::I32: return launch(symm_allreduce_kernel<int32_t>, cfg, kThreads, c, a);
+    case ElemType::I64: return launch(symm_allreduce_kernel<int64_t>, cfg, kThreads, c, a);
+  }
+  return cudaErrorInvalidValue;
+}
+
+cudaError_t launch_allgather(const DevComm& c, const CollArgs& a, const LaunchCfg& cfg) {
+  return launch(allgather_kernel, cfg, kThreads, c, a);
+}
+cudaError_t launch_broadcast(const DevComm& c, const CollArgs& a, const LaunchCfg& cfg) {
+  return launch(broadcast_kernel, cfg, kThreads, c, a);
+}
+cudaError_t launch_alltoall(const DevComm& c, const A2AArgs& a, const LaunchCfg& cfg) {
+  return launch(alltoall_kernel, cfg, kThreads, c, a);
+}
+cudaError_t launch_barrier(const DevComm& c, const LaunchCfg& cfg) {
+  LaunchCfg one = cfg;
+  one.ctas = 1;
+  return launch(barrier_kernel, one, 32, c);
+}
+
+}  // namespace dev
+}  // namespace mccl

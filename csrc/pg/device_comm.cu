@@ -1,0 +1,426 @@
+#include "device_comm.hpp"
+
+#include <cuda_runtime_api.h>
+
+#include <algorithm>
+#include <cstring>
+
+#include "../core/errors.hpp"
+#include "../core/log.hpp"
+#include "../kernels/collectives.hpp"
+#include "../kernels/comm_device.cuh"
+#include "../symm/cu_driver.hpp"
+#include "../symm/symm_mesh.hpp"
+
+namespace mccl {
+
+namespace {
+
+dev::ElemType to_elem(DType t) {
+  switch (t) {
+    case DType::F32: return dev::ElemType::F32;
+    case DType::F16: return dev::ElemType::F16;
+    case DType::BF16: return dev::ElemType::BF16;
+    case DType::F64: return dev::ElemType::F64;
+    case DType::I32: return dev::ElemType::I32;
+    case DType::I64: return dev::ElemType::I64;
+    default: MCCL_CHECK_T(false, TensorError, "device collectives do not reduce dtype " << dtype_name(t));
+  }
+  return dev::ElemType::F32;
+}
+
+int to_dev_op(RedOp op, DType t) {
+  switch (op) {
+    case RedOp::SUM: return dev::OP_SUM;
+    case RedOp::AVG: return dev::OP_AVG;
+    case RedOp::MIN: return dev::OP_MIN;
+    case RedOp::MAX: return dev::OP_MAX;
+    case RedOp::PRODUCT: return dev::OP_PROD;
+    case RedOp::BAND: case RedOp::BOR: case RedOp::BXOR:
+      MCCL_CHECK_T(!dtype_is_float(t), TensorError, "bitwise reduce ops need an integer dtype");
+      return op == RedOp::BAND ? dev::OP_BAND : op == RedOp::BOR ? dev::OP_BOR : dev::OP_BXOR;
+    default: break;
+  }
+  MCCL_CHECK(false, "unsupported reduce op");
+  return 0;
+}
+
+const char* phase_name(int ph) {
+  switch (ph) {
+    case dev::PH_BARRIER: return "barrier";
+    case dev::PH_PUSH: return "push";
+    case dev::PH_REDUCE: return "reduce";
+    case dev::PH_GATHER: return "gather";
+    case dev::PH_RING: return "ring step";
+    case dev::PH_TREE: return "tree step";
+    case dev::PH_NVLS: return "nvls";
+    default: return "?";
+  }
+}
+
+}  // namespace
+
+struct DeviceComm::Impl {
+  std::shared_ptr<SymmAlloc> arena;  // two halves, multicast-bound when possible
+  std::shared_ptr<SymmAlloc> pads;   // kChannels signal pads
+  dev::RankState* state = nullptr;   // device: [nlocal][kChannels]
+  int* status_host = nullptr;        // pinned, mapped: [kMaxRanks]
+  int* status_dev = nullptr;
+  size_t half_bytes = 0;
+  unsigned long long timeout_ns = 0;
+  int max_ctas = 32;
+
+  dev::DevComm ctx(int world, int rank_base, int nlocal, int channel) const {
+    dev::DevComm c{};
+    c.world = world;
+    c.rank_base = rank_base;
+    for (int r = 0; r < world; ++r) {
+      c.arena[r] = static_cast<char*>(arena->ptrs[r]);
+      c.flags[r] = static_cast<uint32_t*>(pads->ptrs[r]) + static_cast<size_t>(channel) * dev::kFlagWordsPerChannel;
+    }
+    c.mc_arena = static_cast<char*>(arena->mc_ptr);
+    for (int v = 0; v < nlocal; ++v) {
+      c.state[v] = state + static_cast<size_t>(v) * dev::kChannels + channel;
+      c.status[v] = status_dev + v;
+    }
+    c.half_bytes = half_bytes;
+    c.timeout_ns = timeout_ns;
+    return c;
+  }
+};
+
+DeviceComm::DeviceComm(KVStore* store, int rank, int world, int device, const std::string& prefix, const EnvConfig& cfg,
+                       int64_t timeout_ms)
+    : rank_(rank), world_(world), device_(device), nlocal_(1), cfg_(cfg) {
+  mesh_.reset(new SymmMesh(store, rank, world, device, prefix, cfg, timeout_ms));
+  init_common();
+}
+
+DeviceComm::DeviceComm(int world, int device, const EnvConfig& cfg)
+    : rank_(0), world_(world), device_(device), nlocal_(world), cfg_(cfg) {
+  mesh_.reset(new SymmMesh(world, device));
+  init_common();
+}
+
+void DeviceComm::init_common() {
+  impl_.reset(new Impl());
+  MCCL_CUDA_CHECK(cudaSetDevice(device_));
+  size_t arena = static_cast<size_t>(std::max<int64_t>(cfg_.arena_bytes, 2 << 20));
+  impl_->arena = mesh_->alloc(arena, /*want_multicast=*/true);
+  impl_->half_bytes = (impl_->arena->bytes / 2) / 256 * 256;
+  impl_->pads = mesh_->alloc(static_cast<size_t>(dev::kChannels) * dev::kFlagWordsPerChannel * sizeof(uint32_t), false);
+  MCCL_CUDA_CHECK(cudaMalloc(&impl_->state, sizeof(dev::RankState) * dev::kChannels * nlocal_));
+  MCCL_CUDA_CHECK(cudaMemset(impl_->state, 0, sizeof(dev::RankState) * dev::kChannels * nlocal_));
+  MCCL_CUDA_CHECK(cudaHostAlloc(&impl_->status_host, sizeof(int) * dev::kMaxRanks, cudaHostAllocMapped));
+  std::memset(impl_->status_host, 0, sizeof(int) * dev::kMaxRanks);
+  MCCL_CUDA_CHECK(cudaHostGetDevicePointer(&impl_->status_dev, impl_->status_host, 0));
+  MCCL_CUDA_CHECK(cudaDeviceSynchronize());
+  impl_->timeout_ns = static_cast<unsigned long long>(std::max<int64_t>(cfg_.device_timeout_ms, 1)) * 1000000ull;
+  int cap = cfg_.max_ctas > 0 ? cfg_.max_ctas : 32;
+  impl_->max_ctas = std::min(cap, dev::kMaxCtas);
+  if (nlocal_ > 1) impl_->max_ctas = std::max(1, std::min(impl_->max_ctas, 96 / nlocal_));  // all virtual ranks co-resident
+  if (mesh_->mode() != SymmMesh::Mode::LOCAL) mesh_->store_barrier("devcomm-ready");
+}
+
+DeviceComm::~DeviceComm() {
+  if (impl_) {
+    if (impl_->state) cudaFree(impl_->state);
+    if (impl_->status_host) cudaFreeHost(impl_->status_host);
+  }
+}
+
+bool DeviceComm::nvls_available() const { return impl_->arena->mc_ptr != nullptr; }
+size_t DeviceComm::arena_bytes() const { return impl_->arena->bytes; }
+const char* DeviceComm::symm_mode() const { return mesh_->mode_name(); }
+
+int DeviceComm::status() const {
+  for (int v = 0; v < nlocal_; ++v) {
+    int s = *reinterpret_cast<volatile int*>(impl_->status_host + v);
+    if (s) return s;
+  }
+  return 0;
+}
+
+void DeviceComm::check_status() const {
+  int s = status();
+  if (!s) return;
+  int phase = (s >> 8) & 0xff, peer = s & 0xff;
+  MCCL_CHECK_T(false, TimeoutError,
+               "device wait timed out: rank " << rank_ << " waited for rank " << peer << " in phase '"
+                                              << phase_name(phase) << "' longer than "
+                                              << impl_->timeout_ns / 1000000ull << " ms; the group must be rebuilt");
+}
+
+void DeviceComm::clear_status() { std::memset(impl_->status_host, 0, sizeof(int) * dev::kMaxRanks); }
+
+void DeviceComm::inject_skip_signals(int count) {
+  MCCL_CUDA_CHECK(cudaSetDevice(device_));
+  MCCL_CUDA_CHECK(cudaDeviceSynchronize());
+  for (int ch = 0; ch < dev::kChannels; ++ch) {
+    uint32_t v = static_cast<uint32_t>(count);
+    MCCL_CUDA_CHECK(cudaMemcpy(&impl_->state[ch].skip_signals, &v, sizeof(v), cudaMemcpyHostToDevice));
+  }
+}
+
+void DeviceComm::set_device_timeout_ms(int64_t ms) {
+  impl_->timeout_ns = static_cast<unsigned long long>(std::max<int64_t>(ms, 1)) * 1000000ull;
+}
+
+std::shared_ptr<SymmAlloc> DeviceComm::symm_alloc(size_t bytes) { return mesh_->alloc(bytes, true); }
+
+// ------------------------------------------------------------------ helpers --
+namespace {
+int ctas_for(size_t bytes, int max_ctas) {
+  // one CTA moves 8 KB per pass; aim at >= 4 passes per CTA before adding CTAs
+  size_t want = (bytes + (32u << 10) - 1) / (32u << 10);
+  return static_cast<int>(std::max<size_t>(1, std::min<size_t>(want, static_cast<size_t>(max_ctas))));
+}
+}  // namespace
+
+Algo DeviceComm::decide_allreduce(Algo requested, size_t numel, DType t, RedOp op, WireDtype wire,
+                                  int64_t tree_below) const {
+  const bool bw = wire == WireDtype::BF16 && t == DType::F32;
+  const size_t wire_bytes = numel * (bw ? 2 : dtype_size(t));
+  const bool nvls_ok = nvls_available() && nlocal_ == 1 && (op == RedOp::SUM || op == RedOp::AVG) &&
+                       (t == DType::F32 || t == DType::F16 || t == DType::BF16);
+  Algo a = requested;
+  if (a == Algo::AUTO) {
+    if (static_cast<int64_t>(wire_bytes) <= tree_below) a = Algo::ONESHOT;
+    else a = nvls_ok ? Algo::NVLS : Algo::BUTTERFLY;
+  }
+  if (a == Algo::NVLS && !nvls_ok) a = Algo::BUTTERFLY;
+  if (a == Algo::RING && numel < static_cast<size_t>(world_)) a = Algo::TREE;
+  return a;
+}
+
+Algo DeviceComm::allreduce(const void* const* ins, void* const* outs, size_t numel, DType t, RedOp op, Algo requested,
+                           WireDtype wire, int64_t tree_below, void* stream) {
+  MCCL_CHECK(world_ >= 2, "device allreduce needs at least two ranks");
+  if (numel == 0) return Algo::ONESHOT;
+  const dev::ElemType et = to_elem(t);
+  const bool bw = wire == WireDtype::BF16 && t == DType::F32;
+  const size_t es = dtype_size(t), wes = bw ? 2 : es;
+  const Algo algo = decide_allreduce(requested, numel, t, op, wire, tree_below);
+  const size_t half = impl_->half_bytes;
+
+  // Largest piece (elements, multiple of 16*world) one launch can stage.
+  auto need = [&](long long n) -> size_t {
+    switch (algo) {
+      case Algo::ONESHOT: return dev::oneshot_bytes(n, world_, wes);
+      case Algo::RING: return dev::ring_bytes(n, world_, wes);
+      case Algo::TREE: return dev::tree_bytes(n, world_, wes);
+      case Algo::NVLS: return dev::nvls_bytes(n, world_, wes);
+      default: return dev::twoshot_bytes(n, world_, wes);
+    }
+  };
+  long long piece = static_cast<long long>(numel);
+  if (need(piece) > half) {
+    const long long unit = 16LL * world_;
+    // need() is linear in n up to padding: scale down, then trim.
+    piece = static_cast<long long>(static_cast<double>(half) / static_cast<double>(need(piece)) * piece);
+    piece = std::max<long long>(unit, piece / unit * unit);
+    while (piece > unit && need(piece) > half) piece -= unit;
+    MCCL_CHECK(need(piece) <= half, "arena of " << impl_->arena->bytes << " bytes is too small; raise MCCL_ARENA_MB");
+  }
+
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  for (long long done = 0; done < static_cast<long long>(numel); done += piece) {
+    const long long n = std::min<long long>(piece, static_cast<long long>(numel) - done);
+    dev::CollArgs a{};
+    for (int v = 0; v < nlocal_; ++v) {
+      a.in[v] = static_cast<const char*>(ins[v]) + static_cast<size_t>(done) * es;
+      a.out[v] = static_cast<char*>(outs[v]) + static_cast<size_t>(done) * es;
+    }
+    a.numel = n;
+    a.per = dev::chunk_elems(n, world_);
+    a.op = to_dev_op(op, t);
+    a.inv_world = 1.0f / static_cast<float>(world_);
+    dev::LaunchCfg cfg;
+    cfg.nlocal = nlocal_;
+    cfg.stream = st;
+    const bool whole = algo == Algo::ONESHOT || algo == Algo::TREE;  // these split the whole message over CTAs
+    cfg.ctas = ctas_for(static_cast<size_t>(n) * wes / (whole ? 1 : world_), impl_->max_ctas);
+    dev::DevComm c = impl_->ctx(world_, rank_, nlocal_, 0);
+    cudaError_t rc;
+    switch (algo) {
+      case Algo::ONESHOT: rc = dev::launch_allreduce_oneshot(et, bw, c, a, cfg); break;
+      case Algo::RING: rc = dev::launch_allreduce_ring(et, bw, c, a, cfg); break;
+      case Algo::TREE: rc = dev::launch_allreduce_tree(et, bw, c, a, cfg); break;
+      case Algo::NVLS: rc = dev::launch_allreduce_nvls(et, bw, true, c, a, nullptr, nullptr, cfg); break;
+      default: rc = dev::launch_allreduce_twoshot(et, bw, c, a, cfg); break;
+    }
+    MCCL_CHECK_T(rc == cudaSuccess, CudaError, "allreduce(" << algo_name(algo) << ") launch failed: " << cudaGetErrorString(rc));
+    ++launches_;
+  }
+  return algo;
+}
+
+Algo DeviceComm::allreduce_symm(const SymmAlloc& buf, size_t byte_offset, size_t numel, DType t, RedOp op, void* stream) {
+  MCCL_CHECK(world_ >= 2, "device allreduce needs at least two ranks");
+  MCCL_CHECK(op == RedOp::SUM || op == RedOp::AVG || buf.mc_ptr == nullptr, "in-switch reduction supports SUM and AVG");
+  const size_t es = dtype_size(t);
+  const long long per = dev::chunk_elems(static_cast<long long>(numel), world_);
+  MCCL_CHECK(byte_offset % 16 == 0, "symmetric allreduce: offset must be a multiple of 16 bytes");
+  MCCL_CHECK(byte_offset + static_cast<size_t>(per) * world_ * es <= buf.bytes,
+             "symmetric allreduce: region (padded to " << per * world_ << " elements) exceeds the allocation");
+  dev::CollArgs a{};
+  a.numel = static_cast<long long>(numel);
+  a.per = per;
+  a.op = to_dev_op(op, t);
+  a.inv_world = 1.0f / static_cast<float>(world_);
+  dev::LaunchCfg cfg;
+  cfg.nlocal = nlocal_;
+  cfg.stream = static_cast<cudaStream_t>(stream);
+  cfg.ctas = ctas_for(static_cast<size_t>(per) * es, impl_->max_ctas);
+  dev::DevComm c = impl_->ctx(world_, rank_, nlocal_, 1);
+  const bool nvls = buf.mc_ptr != nullptr && nlocal_ == 1 && (op == RedOp::SUM || op == RedOp::AVG) &&
+                    (t == DType::F32 || t == DType::F16 || t == DType::BF16);
+  cudaError_t rc;
+  if (nvls) {
+    rc = dev::launch_allreduce_nvls(to_elem(t), false, false, c, a, static_cast<char*>(buf.ptrs[rank_]) + byte_offset,
+                                    static_cast<char*>(buf.mc_ptr) + byte_offset, cfg);
+  } else {
+    for (int r = 0; r < world_; ++r) a.in[r] = static_cast<const char*>(buf.ptrs[r]) + byte_offset;
+    rc = dev::launch_allreduce_symm(to_elem(t), c, a, cfg);
+  }
+  MCCL_CHECK_T(rc == cudaSuccess, CudaError, "symmetric allreduce launch failed: " << cudaGetErrorString(rc));
+  ++launches_;
+  return nvls ? Algo::NVLS : Algo::BUTTERFLY;
+}
+
+void DeviceComm::reduce_scatter(const void* const* ins, void* const* outs, size_t numel, DType t, RedOp op,
+                                WireDtype wire, void* stream) {
+  MCCL_CHECK(world_ >= 2, "device reduce_scatter needs at least two ranks");
+  if (numel == 0) return;
+  const dev::ElemType et = to_elem(t);
+  const bool bw = wire == WireDtype::BF16 && t == DType::F32;
+  const size_t es = dtype_size(t), wes = bw ? 2 : es;
+  const size_t half = impl_->half_bytes;
+  // The arena holds world slots of `per` wire elements; longer chunks go in pieces.
+  const long long cap = static_cast<long long>(half / (static_cast<size_t>(world_) * wes)) / 16 * 16;
+  MCCL_CHECK(cap >= 16, "arena too small for reduce_scatter; raise MCCL_ARENA_MB");
+  const long long piece = std::min<long long>(static_cast<long long>(numel), cap);
+  for (long long done = 0; done < static_cast<long long>(numel); done += piece) {
+    const long long n = std::min<long long>(piece, static_cast<long long>(numel) - done);
+    // Piece [done, done+n) of every chunk: shifted base pointers, full chunk stride.
+    dev::CollArgs a{};
+    for (int v = 0; v < nlocal_; ++v) {
+      a.in[v] = static_cast<const char*>(ins[v]) + static_cast<size_t>(done) * es;
+      a.out[v] = static_cast<char*>(outs[v]) + static_cast<size_t>(done) * es;
+    }
+    a.numel = n;
+    a.stride = static_cast<long long>(numel);
+    a.per = (n + 15) / 16 * 16;
+    a.op = to_dev_op(op, t);
+    a.inv_world = 1.0f / static_cast<float>(world_);
+    dev::LaunchCfg cfg;
+    cfg.nlocal = nlocal_;
+    cfg.stream = static_cast<cudaStream_t>(stream);
+    cfg.ctas = ctas_for(static_cast<size_t>(n) * wes, impl_->max_ctas);
+    dev::DevComm c = impl_->ctx(world_, rank_, nlocal_, 0);
+    cudaError_t rc = dev::launch_reduce_scatter(et, bw, c, a, cfg);
+    MCCL_CHECK_T(rc == cudaSuccess, CudaError, "reduce_scatter launch failed: " << cudaGetErrorString(rc));
+    ++launches_;
+  }
+}
+
+void DeviceComm::allgather(const void* const* ins, void* const* outs, size_t nbytes, void* stream) {
+  MCCL_CHECK(world_ >= 2, "device allgather needs at least two ranks");
+  if (nbytes == 0) return;
+  const size_t half = impl_->half_bytes;
+  const size_t piece = std::min(nbytes, half / 16 * 16);
+  for (size_t done = 0; done < nbytes; done += piece) {
+    const size_t n = std::min(piece, nbytes - done);
+    // Piece k of every rank's block lands at out + r*nbytes + done: express it
+    // with shifted base pointers and the full block stride.
+    dev::CollArgs a{};
+    for (int v = 0; v < nlocal_; ++v) {
+      a.in[v] = static_cast<const char*>(ins[v]) + done;
+      a.out[v] = static_cast<char*>(outs[v]) + done;
+    }
+    a.numel = static_cast<long long>(n);
+    a.stride = static_cast<long long>(nbytes);  // distance between ranks' blocks in the output
+    dev::LaunchCfg cfg;
+    cfg.nlocal = nlocal_;
+    cfg.stream = static_cast<cudaStream_t>(stream);
+    cfg.ctas = ctas_for(n, impl_->max_ctas);
+    dev::DevComm c = impl_->ctx(world_, rank_, nlocal_, 0);
+    cudaError_t rc = dev::launch_allgather(c, a, cfg);
+    MCCL_CHECK_T(rc == cudaSuccess, CudaError, "allgather launch failed: " << cudaGetErrorString(rc));
+    ++launches_;
+  }
+}
+
+void DeviceComm::broadcast(void* const* datas, size_t nbytes, int root, void* stream) {
+  MCCL_CHECK(world_ >= 2, "device broadcast needs at least two ranks");
+  if (nbytes == 0) return;
+  const size_t half = impl_->half_bytes;
+  // each launch scatters a piece into world slices of at most `half` bytes
+  const size_t piece = std::min(nbytes, (half / 16 * 16) * static_cast<size_t>(world_) / 2);
+  for (size_t done = 0; done < nbytes; done += piece) {
+    const size_t n = std::min(piece, nbytes - done);
+    dev::CollArgs a{};
+    for (int v = 0; v < nlocal_; ++v) a.out[v] = static_cast<char*>(datas[v]) + done;
+    a.numel = static_cast<long long>(n);
+    a.root = root;
+    dev::LaunchCfg cfg;
+    cfg.nlocal = nlocal_;
+    cfg.stream = static_cast<cudaStream_t>(stream);
+    cfg.ctas = ctas_for(n / world_, impl_->max_ctas);
+    dev::DevComm c = impl_->ctx(world_, rank_, nlocal_, 0);
+    cudaError_t rc = dev::launch_broadcast(c, a, cfg);
+    MCCL_CHECK_T(rc == cudaSuccess, CudaError, "broadcast launch failed: " << cudaGetErrorString(rc));
+    ++launches_;
+  }
+}
+
+void DeviceComm::alltoallv(const void* const* ins, void* const* outs, const std::vector<std::vector<size_t>>& in_off,
+                           const std::vector<std::vector<size_t>>& in_len,
+                           const std::vector<std::vector<size_t>>& out_off,
+                           const std::vector<std::vector<size_t>>& out_len, void* stream) {
+  MCCL_CHECK(world_ >= 2, "device alltoall needs at least two ranks");
+  const size_t slot = (impl_->half_bytes / static_cast<size_t>(world_)) / 16 * 16;
+  size_t longest = 0;
+  for (int v = 0; v < nlocal_; ++v)
+    for (int p = 0; p < world_; ++p) longest = std::max({longest, in_len[v][p], out_len[v][p]});
+  // Every rank must run the same number of launches.  A rank only knows its
+  // own segment sizes, so segments longer than a slot are not split silently.
+  MCCL_CHECK(longest <= slot, "alltoall segment of " << longest << " bytes exceeds the " << slot
+                                                     << "-byte arena slot; raise MCCL_ARENA_MB");
+  dev::A2AArgs a{};
+  for (int v = 0; v < nlocal_; ++v) {
+    a.in[v] = ins[v];
+    a.out[v] = outs[v];
+    for (int p = 0; p < world_; ++p) {
+      a.in_off[v][p] = in_off[v][p];
+      a.in_len[v][p] = in_len[v][p];
+      a.out_off[v][p] = out_off[v][p];
+      a.out_len[v][p] = out_len[v][p];
+    }
+  }
+  a.slot_bytes = slot;
+  dev::LaunchCfg cfg;
+  cfg.nlocal = nlocal_;
+  cfg.stream = static_cast<cudaStream_t>(stream);
+  cfg.ctas = ctas_for(longest, impl_->max_ctas);
+  // The CTA count must agree across ranks although segment sizes differ: it
+  // is a function of the slot size only when sizes are uneven.
+  cfg.ctas = std::min(impl_->max_ctas, 16);
+  dev::DevComm c = impl_->ctx(world_, rank_, nlocal_, 0);
+  cudaError_t rc = dev::launch_alltoall(c, a, cfg);
+  MCCL_CHECK_T(rc == cudaSuccess, CudaError, "alltoall launch failed: " << cudaGetErrorString(rc));
+  ++launches_;
+}
+
+void DeviceComm::barrier(void* stream) {
+  if (world_ < 2) return;
+  dev::LaunchCfg cfg;
+  cfg.nlocal = nlocal_;
+  cfg.stream = static_cast<cudaStream_t>(stream);
+  dev::DevComm c = impl_->ctx(world_, rank_, nlocal_, 0);
+  cudaError_t rc = dev::launch_barrier(c, cfg);
+  MCCL_CHECK_T(rc == cudaSuccess, CudaError, "barrier launch failed: " << cudaGetErrorString(rc));
+  ++launches_;
+}
+
+}  // namespace mccl
