@@ -1,0 +1,75 @@
+// Host entry points of the model-operator kernels (sm_100a).  All launchers
+// enqueue on the given stream and return the launch status.  The reference has
+// no counterpart for these: its models run on stock PyTorch/MPS operators
+// (examples/ddp_utils.py:41-147); they exist here because the headline
+// benchmark is a training step, and on a B200 that step is bound by these
+// operators, not by the collectives.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+namespace mccl {
+namespace ops {
+
+// Number of operator kernels launched so far (all launchers below count).
+uint64_t launch_count();
+void count_launch(int n = 1);
+
+// ---- normalisation: y = (x - mean) * rstd * w + b  (LayerNorm, bias != null)
+//                     y = x * rstd * w                (RMSNorm, bias == null)
+// x, y: [rows, dim] bf16; w, b: fp32; mean / rstd: fp32 [rows] saved for backward.
+cudaError_t norm_fwd(const __nv_bfloat16* x, const float* w, const float* b, __nv_bfloat16* y, float* mean, float* rstd,
+                     int rows, int dim, float eps, cudaStream_t stream);
+// dx: [rows, dim] bf16; dw, db: fp32 [dim] (overwritten).
+cudaError_t norm_bwd(const __nv_bfloat16* dy, const __nv_bfloat16* x, const float* w, const float* mean, const float* rstd,
+                     __nv_bfloat16* dx, float* dw, float* db, int rows, int dim, bool layernorm, cudaStream_t stream);
+
+// ---- fused AdamW over flat fp32 buffers; step is a device scalar (float) so the
+// launch can be replayed from a CUDA graph.  p16 (optional) receives bf16(p).
+cudaError_t adamw_flat(float* p, const float* g, float* m, float* v, __nv_bfloat16* p16, long long n, float lr, float beta1,
+                       float beta2, float eps, float wd, const float* step, float grad_scale, cudaStream_t stream);
+
+// ---- softmax cross entropy, forward and backward in one pass over the logits:
+// loss_rows[t] = logsumexp(logits[t]) - logits[t, target[t]];
+// logits[t] is overwritten by (softmax - onehot) * grad_scale.
+cudaError_t cross_entropy_fwd_bwd(__nv_bfloat16* logits, const long long* targets, float* loss_rows, int rows, int vocab,
+                                  float grad_scale, cudaStream_t stream);
+
+// ---- out[c, r] = in[r, c] for a bf16 matrix [rows, cols].
+cudaError_t transpose_bf16(const __nv_bfloat16* in, __nv_bfloat16* out, int rows, int cols, cudaStream_t stream);
+// fp32 → bf16 cast of n elements.
+cudaError_t cast_f32_bf16(const float* in, __nv_bfloat16* out, long long n, cudaStream_t stream);
+// GELU backward on a pre-activation: dz = dy * gelu'(z).
+cudaError_t gelu_bwd(const __nv_bfloat16* dy, const __nv_bfloat16* z, __nv_bfloat16* dz, long long n, cudaStream_t stream);
+
+// ---- tcgen05 GEMM: D[M,N] = A[M,K] · B[N,K]^T (+ bias[N]) (GELU) ; A, B bf16 with K contiguous.
+enum GemmEpilogue : int {
+  EPI_NONE = 0,       // D = acc
+  EPI_BIAS = 1,       // D = acc + bias[n]
+  EPI_BIAS_GELU = 2,  // Z = acc + bias[n] (written to aux), D = gelu(Z)
+  EPI_GELU = 3,       // Z = acc (written to aux), D = gelu(Z)
+};
+struct GemmArgs {
+  const __nv_bfloat16* a = nullptr;  // [M, K], row stride lda (elements)
+  const __nv_bfloat16* b = nullptr;  // [N, K], row stride ldb
+  void* d = nullptr;                 // [M, N] bf16 or fp32, row stride ldd
+  __nv_bfloat16* aux = nullptr;      // [M, N] pre-activation (GELU epilogues)
+  const float* bias = nullptr;       // [N]
+  int m = 0, n = 0, k = 0;
+  int lda = 0, ldb = 0, ldd = 0;
+  bool d_fp32 = false;
+  bool accumulate = false;           // D += result (fp32 output only)
+  int epilogue = EPI_NONE;
+};
+// Returns cudaErrorNotSupported for shapes the kernel does not cover
+// (K % 64 != 0, N % 8 != 0, unaligned pointers); the caller falls back.
+cudaError_t gemm_bf16_tn(const GemmArgs& args, cudaStream_t stream);
+// Non-zero when a pipeline wait inside a GEMM kernel ran out (kernel returned early).
+int gemm_error_flag();
+
+}  // namespace ops
+}  // namespace mccl

@@ -51,6 +51,20 @@ def _cutlass_include() -> list[str]:
     return []
 
 
+def _stdcxx_ldflags() -> list[str]:
+    """Links the shared libstdc++ explicitly.
+
+    Some toolchain wrappers resolve -lstdc++ to the static archive; a second,
+    private copy of the C++ runtime inside the extension has uninitialised
+    locale state and crashes on the first stream insertion.  Naming the shared
+    object first keeps a single C++ runtime in the process.
+    """
+    for d in ("/usr/lib/x86_64-linux-gnu", "/usr/lib/aarch64-linux-gnu", "/usr/lib64"):
+        if os.path.exists(os.path.join(d, "libstdc++.so.6")):
+            return [f"-L{d}", "-l:libstdc++.so.6"]
+    return []
+
+
 def build(verbose: bool = False) -> str:
     """Compiles the extension and returns the path of ``_C.so``."""
     from torch.utils.cpp_extension import load
@@ -63,7 +77,7 @@ def build(verbose: bool = False) -> str:
         extra_cflags=CXX_FLAGS,
         extra_cuda_cflags=CUDA_FLAGS,
         extra_include_paths=[CSRC],
-        extra_ldflags=["-ldl", "-lpthread"],
+        extra_ldflags=_stdcxx_ldflags() + ["-ldl", "-lpthread"],
         build_directory=BUILD_DIR,
         with_cuda=True,
         is_python_module=False,
@@ -89,7 +103,7 @@ def build_agent(verbose: bool = False) -> str | None:
     newest = max(os.path.getmtime(s) for s in srcs)
     if os.path.exists(out) and os.path.getmtime(out) >= newest:
         return out
-    cmd = ["g++", "-O2", "-std=c++17", "-pthread", "-I", CSRC, "-o", out] + srcs
+    cmd = ["g++", "-O2", "-std=c++17", "-pthread", "-I", CSRC, "-o", out] + srcs + _stdcxx_ldflags()
     if verbose:
         print(" ".join(cmd))
     subprocess.check_call(cmd)

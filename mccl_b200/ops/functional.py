@@ -1,0 +1,62 @@
+"""Differentiable operators.  CUDA tensors run the native kernels; the
+fallbacks below only serve CPU tensors (tests without a GPU)."""
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+
+from .. import _C
+
+_HAS = {name: hasattr(_C, name) for name in ("gemm_bf16", "norm_fwd", "norm_bwd", "adamw_flat", "ce_fwd_bwd")}
+_launches = 0
+
+
+def native_ops_available() -> dict:
+    return dict(_HAS)
+
+
+def launch_count() -> int:
+    """Number of this package's model-operator kernels launched so far in this process."""
+    native = _C.op_launch_count() if hasattr(_C, "op_launch_count") else 0
+    return native + _launches
+
+
+def norm(x: torch.Tensor, weight: torch.Tensor, bias, eps: float) -> torch.Tensor:
+    if x.is_cuda and _HAS["norm_fwd"]:
+        from .native import NormFn
+        return NormFn.apply(x, weight, bias, eps)
+    v = x.float()
+    if bias is not None:
+        return F.layer_norm(v, v.shape[-1:], weight, bias, eps).to(x.dtype)
+    return (v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps) * weight).to(x.dtype)
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, bias=None, act: str = "none") -> torch.Tensor:
+    if x.is_cuda and _HAS["gemm_bf16"]:
+        from .native import LinearFn
+        return LinearFn.apply(x, weight, bias, act)
+    y = F.linear(x, weight.to(x.dtype), None if bias is None else bias.to(x.dtype))
+    return F.gelu(y) if act == "gelu" else y
+
+
+def linear_cross_entropy(h: torch.Tensor, weight: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
+    """Mean cross entropy of (h @ weight.T) against targets; h [T, D] bf16, weight [V, D]."""
+    if h.is_cuda and _HAS["ce_fwd_bwd"] and _HAS["gemm_bf16"]:
+        from .native import LinearCrossEntropyFn
+        return LinearCrossEntropyFn.apply(h, weight, targets)
+    logits = F.linear(h, weight.to(h.dtype))
+    return F.cross_entropy(logits.float(), targets)
+
+
+def adamw_step(p, g, m, v, lr, beta1, beta2, eps, wd, step, p_bf16=None, grad_scale=1.0):
+    """In-place fused AdamW over flat fp32 tensors (optionally refreshing a bf16 copy of p)."""
+    if p.is_cuda and _HAS["adamw_flat"]:
+        _C.adamw_flat(p, g, m, v, p_bf16, lr, beta1, beta2, eps, wd, step, grad_scale)
+        return
+    g = g * grad_scale if grad_scale != 1.0 else g
+    m.mul_(beta1).add_(g, alpha=1 - beta1)
+    v.mul_(beta2).addcmul_(g, g, value=1 - beta2)
+    bc1, bc2 = 1 - beta1 ** step, 1 - beta2 ** step
+    p.mul_(1 - lr * wd).addcdiv_(m / bc1, (v / bc2).sqrt_().add_(eps), value=-lr)
+    if p_bf16 is not None:
+        p_bf16.copy_(p)

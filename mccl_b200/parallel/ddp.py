@@ -1,0 +1,41 @@
+"""Helpers for stock ``DistributedDataParallel`` on backend "mccl".
+
+DDP needs nothing special: ``DDP(model)`` over a group created with
+``backend="mccl"`` all-reduces its gradient buckets through the backend, as
+with the reference (README.md:27-35).  ``bf16_wire_hook`` is a DDP
+communication hook that sends fp32 gradient buckets as bf16 on the wire with
+fp32 accumulation and the 1/world scale fused into the same kernel, which is
+what ``MCCL_WIRE_DTYPE=bf16`` selects globally.
+"""
+from __future__ import annotations
+
+import contextlib
+import os
+
+import torch
+import torch.distributed as dist
+
+
+@contextlib.contextmanager
+def wire_dtype(name: str):
+    """Temporarily sets ``MCCL_WIRE_DTYPE`` (the backend re-reads it on every allreduce)."""
+    old = os.environ.get("MCCL_WIRE_DTYPE")
+    if name:
+        os.environ["MCCL_WIRE_DTYPE"] = name
+    else:
+        os.environ.pop("MCCL_WIRE_DTYPE", None)
+    try:
+        yield
+    finally:
+        if old is None:
+            os.environ.pop("MCCL_WIRE_DTYPE", None)
+        else:
+            os.environ["MCCL_WIRE_DTYPE"] = old
+
+
+def bf16_wire_hook(group, bucket: dist.GradBucket) -> torch.futures.Future:
+    """``model.register_comm_hook(group, bf16_wire_hook)``: averaged gradients, bf16 on the wire."""
+    buf = bucket.buffer()
+    with wire_dtype("bf16" if buf.dtype == torch.float32 else ""):
+        work = dist.all_reduce(buf, op=dist.ReduceOp.AVG, group=group, async_op=True)
+    return work.get_future().then(lambda fut: fut.value()[0])

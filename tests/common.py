@@ -55,11 +55,13 @@ def _worker(rank: int, world: int, port: int, fn: Callable, kwargs: Dict[str, An
             backend="mccl", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world,
             timeout=__import__("datetime").timedelta(seconds=kwargs.pop("_timeout", 60)),
         )
+        skip_barrier = kwargs.pop("_skip_final_barrier", False)
         result = fn(rank, world, **kwargs)
         if use_cuda:
             torch.cuda.synchronize()
-        dist.barrier()
-        dist.destroy_process_group()
+        if not skip_barrier:
+            dist.barrier()
+            dist.destroy_process_group()
         queue.put((rank, "ok", result))
     except BaseException as e:  # noqa: BLE001
         queue.put((rank, "error", f"{type(e).__name__}: {e}\n{traceback.format_exc()}"))
