@@ -1,7 +1,225 @@
+// Python bindings of the model-operator kernels.  Every function checks its
+// operands, allocates outputs through torch, and launches on the current
+// CUDA stream of the operands' device (so the calls can be captured in a CUDA
+// graph).  There is no CPU fallback here: a CPU tensor is an error.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
 #include <torch/extension.h>
 
+#include "../core/errors.hpp"
+#include "../ops/ops.hpp"
 #include "bind.hpp"
 
+namespace py = pybind11;
+
 namespace mccl {
-void bind_ops(pybind11::module_& m) { (void)m; }
+
+namespace {
+
+void need_cuda(const at::Tensor& t, const char* what) {
+  MCCL_CHECK_TENSOR(t.defined() && t.is_cuda(), what << ": expected a CUDA tensor");
+}
+void need(const at::Tensor& t, at::ScalarType dt, const char* what) {
+  need_cuda(t, what);
+  MCCL_CHECK_TENSOR(t.scalar_type() == dt, what << ": expected dtype " << c10::toString(dt) << ", got "
+                                                << c10::toString(t.scalar_type()));
+  MCCL_CHECK_TENSOR(t.is_contiguous(), what << ": expected a contiguous tensor");
+}
+cudaStream_t stream_of(const at::Tensor& t) { return at::cuda::getCurrentCUDAStream(t.get_device()).stream(); }
+void check_launch(cudaError_t rc, const char* what) {
+  MCCL_CHECK_T(rc == cudaSuccess, CudaError, what << " failed: " << cudaGetErrorString(rc));
+}
+__nv_bfloat16* bf(const at::Tensor& t) { return reinterpret_cast<__nv_bfloat16*>(t.data_ptr()); }
+
+int parse_epilogue(const std::string& s, bool has_bias) {
+  if (s == "none") return has_bias ? ops::EPI_BIAS : ops::EPI_NONE;
+  if (s == "gelu") return has_bias ? ops::EPI_BIAS_GELU : ops::EPI_GELU;
+  MCCL_CHECK(false, "unknown GEMM epilogue '" << s << "'");
+  return 0;
+}
+
+}  // namespace
+
+void bind_ops(py::module_& m) {
+  m.def("op_launch_count", [] { return ops::launch_count(); });
+  m.def("gemm_error_flag", [] { return ops::gemm_error_flag(); });
+
+  // D[M,N] = A[M,K] · B[N,K]^T.  A and B are 2-D bf16 with unit inner stride
+  // (row strides may exceed K).  Returns (D, pre_activation or None).
+  m.def(
+      "gemm_bf16",
+      [](const at::Tensor& a, const at::Tensor& b, const c10::optional<at::Tensor>& bias, const std::string& epilogue,
+         bool out_fp32, const c10::optional<at::Tensor>& out, bool accumulate) {
+        need_cuda(a, "gemm(a)");
+        need_cuda(b, "gemm(b)");
+        MCCL_CHECK_TENSOR(a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16, "gemm: operands must be bf16");
+        MCCL_CHECK_TENSOR(a.dim() == 2 && b.dim() == 2 && a.size(1) == b.size(1), "gemm: shapes [M,K] x [N,K] expected");
+        MCCL_CHECK_TENSOR(a.stride(1) == 1 && b.stride(1) == 1, "gemm: K must be the contiguous dimension of both operands");
+        c10::cuda::CUDAGuard guard(a.device());
+        const int64_t M = a.size(0), N = b.size(0), K = a.size(1);
+        at::Tensor d;
+        if (out.has_value()) {
+          d = *out;
+          need_cuda(d, "gemm(out)");
+          MCCL_CHECK_TENSOR(d.dim() == 2 && d.size(0) == M && d.size(1) == N && d.stride(1) == 1, "gemm: bad output shape");
+          MCCL_CHECK_TENSOR(d.scalar_type() == (out_fp32 ? at::kFloat : at::kBFloat16), "gemm: output dtype mismatch");
+        } else {
+          d = at::empty({M, N}, a.options().dtype(out_fp32 ? at::kFloat : at::kBFloat16));
+        }
+        ops::GemmArgs g;
+        g.a = bf(a);
+        g.b = bf(b);
+        g.d = d.data_ptr();
+        g.m = static_cast<int>(M);
+        g.n = static_cast<int>(N);
+        g.k = static_cast<int>(K);
+        g.lda = static_cast<int>(a.stride(0));
+        g.ldb = static_cast<int>(b.stride(0));
+        g.ldd = static_cast<int>(d.stride(0));
+        g.d_fp32 = out_fp32;
+        g.accumulate = accumulate;
+        at::Tensor bias_f;
+        if (bias.has_value() && bias->defined()) {
+          need(*bias, at::kFloat, "gemm(bias)");
+          MCCL_CHECK_TENSOR(bias->numel() == N, "gemm: bias must have N elements");
+          g.bias = bias->data_ptr<float>();
+        }
+        g.epilogue = parse_epilogue(epilogue, g.bias != nullptr);
+        at::Tensor aux;
+        if (g.epilogue == ops::EPI_BIAS_GELU || g.epilogue == ops::EPI_GELU) {
+          MCCL_CHECK_TENSOR(d.is_contiguous(), "gemm: GELU epilogue needs a contiguous output");
+          aux = at::empty({M, N}, a.options());
+          g.aux = bf(aux);
+        }
+        check_launch(ops::gemm_bf16_tn(g, stream_of(a)), "gemm_bf16");
+        return std::make_pair(d, aux.defined() ? c10::optional<at::Tensor>(aux) : c10::nullopt);
+      },
+      py::arg("a"), py::arg("b"), py::arg("bias") = py::none(), py::arg("epilogue") = "none", py::arg("out_fp32") = false,
+      py::arg("out") = py::none(), py::arg("accumulate") = false);
+
+  m.def(
+      "norm_fwd",
+      [](const at::Tensor& x, const at::Tensor& w, const c10::optional<at::Tensor>& b, double eps) {
+        need(x, at::kBFloat16, "norm(x)");
+        need(w, at::kFloat, "norm(weight)");
+        c10::cuda::CUDAGuard guard(x.device());
+        const int64_t dim = x.size(-1), rows = x.numel() / dim;
+        MCCL_CHECK_TENSOR(w.numel() == dim, "norm: weight must have `dim` elements");
+        const float* bp = nullptr;
+        if (b.has_value() && b->defined()) {
+          need(*b, at::kFloat, "norm(bias)");
+          bp = b->data_ptr<float>();
+        }
+        at::Tensor y = at::empty_like(x);
+        at::Tensor mean = at::empty({rows}, x.options().dtype(at::kFloat));
+        at::Tensor rstd = at::empty({rows}, x.options().dtype(at::kFloat));
+        check_launch(ops::norm_fwd(bf(x), w.data_ptr<float>(), bp, bf(y), mean.data_ptr<float>(), rstd.data_ptr<float>(),
+                                   static_cast<int>(rows), static_cast<int>(dim), static_cast<float>(eps), stream_of(x)),
+                     "norm_fwd");
+        return std::make_tuple(y, mean, rstd);
+      },
+      py::arg("x"), py::arg("weight"), py::arg("bias") = py::none(), py::arg("eps") = 1e-5);
+
+  m.def(
+      "norm_bwd",
+      [](const at::Tensor& dy, const at::Tensor& x, const at::Tensor& w, const at::Tensor& mean, const at::Tensor& rstd,
+         bool layernorm) {
+        need(dy, at::kBFloat16, "norm_bwd(dy)");
+        need(x, at::kBFloat16, "norm_bwd(x)");
+        need(w, at::kFloat, "norm_bwd(weight)");
+        need(mean, at::kFloat, "norm_bwd(mean)");
+        need(rstd, at::kFloat, "norm_bwd(rstd)");
+        c10::cuda::CUDAGuard guard(x.device());
+        const int64_t dim = x.size(-1), rows = x.numel() / dim;
+        at::Tensor dx = at::empty_like(x);
+        at::Tensor dw = at::empty({dim}, x.options().dtype(at::kFloat));
+        at::Tensor db = layernorm ? at::empty({dim}, x.options().dtype(at::kFloat)) : at::Tensor();
+        check_launch(ops::norm_bwd(bf(dy), bf(x), w.data_ptr<float>(), mean.data_ptr<float>(), rstd.data_ptr<float>(), bf(dx),
+                                   dw.data_ptr<float>(), layernorm ? db.data_ptr<float>() : nullptr, static_cast<int>(rows),
+                                   static_cast<int>(dim), layernorm, stream_of(x)),
+                     "norm_bwd");
+        return std::make_tuple(dx, dw, db.defined() ? c10::optional<at::Tensor>(db) : c10::nullopt);
+      });
+
+  m.def(
+      "adamw_flat",
+      [](at::Tensor p, const at::Tensor& g, at::Tensor mm, at::Tensor v, const c10::optional<at::Tensor>& p16, double lr,
+         double b1, double b2, double eps, double wd, const at::Tensor& step, double grad_scale) {
+        need(p, at::kFloat, "adamw(p)");
+        need(g, at::kFloat, "adamw(g)");
+        need(mm, at::kFloat, "adamw(m)");
+        need(v, at::kFloat, "adamw(v)");
+        need(step, at::kFloat, "adamw(step)");
+        MCCL_CHECK_TENSOR(g.numel() == p.numel() && mm.numel() == p.numel() && v.numel() == p.numel(), "adamw: size mismatch");
+        c10::cuda::CUDAGuard guard(p.device());
+        __nv_bfloat16* p16p = nullptr;
+        if (p16.has_value() && p16->defined()) {
+          need(*p16, at::kBFloat16, "adamw(p_bf16)");
+          MCCL_CHECK_TENSOR(p16->numel() == p.numel(), "adamw: bf16 copy size mismatch");
+          p16p = bf(*p16);
+        }
+        check_launch(ops::adamw_flat(p.data_ptr<float>(), g.data_ptr<float>(), mm.data_ptr<float>(), v.data_ptr<float>(), p16p,
+                                     p.numel(), static_cast<float>(lr), static_cast<float>(b1), static_cast<float>(b2),
+                                     static_cast<float>(eps), static_cast<float>(wd), step.data_ptr<float>(),
+                                     static_cast<float>(grad_scale), stream_of(p)),
+                     "adamw_flat");
+      },
+      py::arg("p"), py::arg("g"), py::arg("m"), py::arg("v"), py::arg("p_bf16") = py::none(), py::arg("lr") = 1e-3,
+      py::arg("beta1") = 0.9, py::arg("beta2") = 0.999, py::arg("eps") = 1e-8, py::arg("weight_decay") = 0.01,
+      py::arg("step") = at::Tensor(), py::arg("grad_scale") = 1.0);
+
+  m.def(
+      "ce_fwd_bwd",
+      [](at::Tensor logits, const at::Tensor& targets, double grad_scale) {
+        need(logits, at::kBFloat16, "cross_entropy(logits)");
+        need(targets, at::kLong, "cross_entropy(targets)");
+        MCCL_CHECK_TENSOR(logits.dim() == 2 && targets.numel() == logits.size(0), "cross_entropy: logits [T,V], targets [T]");
+        c10::cuda::CUDAGuard guard(logits.device());
+        at::Tensor loss_rows = at::empty({logits.size(0)}, logits.options().dtype(at::kFloat));
+        check_launch(ops::cross_entropy_fwd_bwd(bf(logits), reinterpret_cast<const long long*>(targets.data_ptr<int64_t>()),
+                                                loss_rows.data_ptr<float>(), static_cast<int>(logits.size(0)),
+                                                static_cast<int>(logits.size(1)), static_cast<float>(grad_scale),
+                                                stream_of(logits)),
+                     "cross_entropy");
+        return loss_rows;
+      },
+      py::arg("logits"), py::arg("targets"), py::arg("grad_scale") = 1.0,
+      "Returns per-row losses; overwrites logits with (softmax - onehot) * grad_scale.");
+
+  m.def("transpose_bf16", [](const at::Tensor& x) {
+    need(x, at::kBFloat16, "transpose(x)");
+    MCCL_CHECK_TENSOR(x.dim() == 2, "transpose: 2-D tensor expected");
+    c10::cuda::CUDAGuard guard(x.device());
+    at::Tensor y = at::empty({x.size(1), x.size(0)}, x.options());
+    check_launch(ops::transpose_bf16(bf(x), bf(y), static_cast<int>(x.size(0)), static_cast<int>(x.size(1)), stream_of(x)),
+                 "transpose");
+    return y;
+  });
+  m.def("transpose_bf16_out", [](const at::Tensor& x, at::Tensor y) {
+    need(x, at::kBFloat16, "transpose(x)");
+    need(y, at::kBFloat16, "transpose(out)");
+    MCCL_CHECK_TENSOR(x.dim() == 2 && y.numel() == x.numel(), "transpose: bad shapes");
+    c10::cuda::CUDAGuard guard(x.device());
+    check_launch(ops::transpose_bf16(bf(x), bf(y), static_cast<int>(x.size(0)), static_cast<int>(x.size(1)), stream_of(x)),
+                 "transpose");
+  });
+  m.def("cast_bf16", [](const at::Tensor& x, const c10::optional<at::Tensor>& out) {
+    need(x, at::kFloat, "cast(x)");
+    c10::cuda::CUDAGuard guard(x.device());
+    at::Tensor y = out.has_value() ? *out : at::empty_like(x, x.options().dtype(at::kBFloat16));
+    need(y, at::kBFloat16, "cast(out)");
+    check_launch(ops::cast_f32_bf16(x.data_ptr<float>(), bf(y), x.numel(), stream_of(x)), "cast");
+    return y;
+  }, py::arg("x"), py::arg("out") = py::none());
+  m.def("gelu_bwd", [](const at::Tensor& dy, const at::Tensor& z) {
+    need(dy, at::kBFloat16, "gelu_bwd(dy)");
+    need(z, at::kBFloat16, "gelu_bwd(z)");
+    MCCL_CHECK_TENSOR(dy.numel() == z.numel(), "gelu_bwd: size mismatch");
+    c10::cuda::CUDAGuard guard(dy.device());
+    at::Tensor dz = at::empty_like(dy);
+    check_launch(ops::gelu_bwd(bf(dy), bf(z), bf(dz), dy.numel(), stream_of(dy)), "gelu_bwd");
+    return dz;
+  });
+}
+
 }  // namespace mccl

@@ -1,0 +1,411 @@
+// Memory-bound model operators: normalisation (forward / backward), fused
+// AdamW, softmax cross entropy (forward + backward in one pass), transpose,
+// casts and the GELU derivative.  Every kernel moves 16 bytes per access and
+// reads each operand once from HBM (re-reads of a row hit L1/L2).
+#include <atomic>
+
+#include "ops.hpp"
+
+namespace mccl {
+namespace ops {
+
+namespace {
+std::atomic<uint64_t> g_launches{0};
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ void unpack8(const uint4& raw, float (&f)[8]) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 t = __bfloat1622float2(h[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  uint4 raw;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  return raw;
+}
+}  // namespace
+
+uint64_t launch_count() { return g_launches.load(); }
+void count_launch(int n) { g_launches.fetch_add(static_cast<uint64_t>(n)); }
+
+// ------------------------------------------------------------------- norm --
+// One warp per row; dim must be a multiple of 8.
+template <bool kLayerNorm>
+__global__ void __launch_bounds__(256) norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ w,
+                                                       const float* __restrict__ b, __nv_bfloat16* __restrict__ y,
+                                                       float* __restrict__ mean_out, float* __restrict__ rstd_out, int rows,
+                                                       int dim, float eps) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (warp >= rows) return;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<size_t>(warp) * dim);
+  const int vecs = dim >> 3;
+  float sum = 0.f;
+  for (int v = lane; v < vecs; v += 32) {
+    float f[8];
+    unpack8(xr[v], f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) sum += f[i];
+  }
+  const float mean = kLayerNorm ? warp_sum(sum) / dim : 0.f;
+  float sq = 0.f;
+  for (int v = lane; v < vecs; v += 32) {
+    float f[8];
+    unpack8(xr[v], f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) sq += (f[i] - mean) * (f[i] - mean);
+  }
+  const float rstd = rsqrtf(warp_sum(sq) / dim + eps);
+  if (lane == 0) {
+    mean_out[warp] = mean;
+    rstd_out[warp] = rstd;
+  }
+  uint4* yr = reinterpret_cast<uint4*>(y + static_cast<size_t>(warp) * dim);
+  for (int v = lane; v < vecs; v += 32) {
+    float f[8], o[8];
+    unpack8(xr[v], f);
+    const float4 w0 = reinterpret_cast<const float4*>(w)[2 * v], w1 = reinterpret_cast<const float4*>(w)[2 * v + 1];
+    const float ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+    float bb[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if (kLayerNorm) {
+      const float4 b0 = reinterpret_cast<const float4*>(b)[2 * v], b1 = reinterpret_cast<const float4*>(b)[2 * v + 1];
+      bb[0] = b0.x; bb[1] = b0.y; bb[2] = b0.z; bb[3] = b0.w; bb[4] = b1.x; bb[5] = b1.y; bb[6] = b1.z; bb[7] = b1.w;
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[i] = (f[i] - mean) * rstd * ww[i] + bb[i];
+    yr[v] = pack8(o);
+  }
+}
+
+template <bool kLayerNorm>
+__global__ void __launch_bounds__(256) norm_bwd_dx_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                                                          const float* __restrict__ w, const float* __restrict__ mean,
+                                                          const float* __restrict__ rstd, __nv_bfloat16* __restrict__ dx,
+                                                          int rows, int dim) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (warp >= rows) return;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<size_t>(warp) * dim);
+  const uint4* gr = reinterpret_cast<const uint4*>(dy + static_cast<size_t>(warp) * dim);
+  const int vecs = dim >> 3;
+  const float mu = mean[warp], rs = rstd[warp];
+  float c1 = 0.f, c2 = 0.f;  // sum(dy*w*xhat), sum(dy*w)
+  for (int v = lane; v < vecs; v += 32) {
+    float f[8], g[8];
+    unpack8(xr[v], f);
+    unpack8(gr[v], g);
+    const float4 w0 = reinterpret_cast<const float4*>(w)[2 * v], w1 = reinterpret_cast<const float4*>(w)[2 * v + 1];
+    const float ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float gw = g[i] * ww[i];
+      c1 += gw * (f[i] - mu) * rs;
+      c2 += gw;
+    }
+  }
+  c1 = warp_sum(c1) / dim;
+  c2 = kLayerNorm ? warp_sum(c2) / dim : 0.f;
+  uint4* dr = reinterpret_cast<uint4*>(dx + static_cast<size_t>(warp) * dim);
+  for (int v = lane; v < vecs; v += 32) {
+    float f[8], g[8], o[8];
+    unpack8(xr[v], f);
+    unpack8(gr[v], g);
+    const float4 w0 = reinterpret_cast<const float4*>(w)[2 * v], w1 = reinterpret_cast<const float4*>(w)[2 * v + 1];
+    const float ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[i] = rs * (g[i] * ww[i] - c2 - (f[i] - mu) * rs * c1);
+    dr[v] = pack8(o);
+  }
+}
+
+// dw[c] = sum_r dy[r,c] * xhat[r,c]; db[c] = sum_r dy[r,c].  Block = 32 columns x 8 row lanes.
+__global__ void __launch_bounds__(256) norm_bwd_wgrad_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                                                             const float* __restrict__ mean, const float* __restrict__ rstd,
+                                                             float* __restrict__ dw, float* __restrict__ db, int rows, int dim) {
+  __shared__ float sw[8][33], sb[8][33];
+  const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
+  const int col = blockIdx.x * 32 + cx;
+  float aw = 0.f, ab = 0.f;
+  if (col < dim) {
+    for (int r = ry; r < rows; r += 8) {
+      const float g = __bfloat162float(dy[static_cast<size_t>(r) * dim + col]);
+      const float xv = __bfloat162float(x[static_cast<size_t>(r) * dim + col]);
+      aw += g * (xv - mean[r]) * rstd[r];
+      ab += g;
+    }
+  }
+  sw[ry][cx] = aw;
+  sb[ry][cx] = ab;
+  __syncthreads();
+  if (ry == 0 && col < dim) {
+    float tw = 0.f, tb = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      tw += sw[i][cx];
+      tb += sb[i][cx];
+    }
+    dw[col] = tw;
+    if (db) db[col] = tb;
+  }
+}
+
+cudaError_t norm_fwd(const __nv_bfloat16* x, const float* w, const float* b, __nv_bfloat16* y, float* mean, float* rstd,
+                     int rows, int dim, float eps, cudaStream_t stream) {
+  if (dim % 8 != 0) return cudaErrorNotSupported;
+  const int blocks = (rows + 7) / 8;
+  if (b) norm_fwd_kernel<true><<<blocks, 256, 0, stream>>>(x, w, b, y, mean, rstd, rows, dim, eps);
+  else norm_fwd_kernel<false><<<blocks, 256, 0, stream>>>(x, w, b, y, mean, rstd, rows, dim, eps);
+  count_launch();
+  return cudaGetLastError();
+}
+
+cudaError_t norm_bwd(const __nv_bfloat16* dy, const __nv_bfloat16* x, const float* w, const float* mean, const float* rstd,
+                     __nv_bfloat16* dx, float* dw, float* db, int rows, int dim, bool layernorm, cudaStream_t stream) {
+  if (dim % 8 != 0) return cudaErrorNotSupported;
+  const int blocks = (rows + 7) / 8;
+  if (layernorm) norm_bwd_dx_kernel<true><<<blocks, 256, 0, stream>>>(dy, x, w, mean, rstd, dx, rows, dim);
+  else norm_bwd_dx_kernel<false><<<blocks, 256, 0, stream>>>(dy, x, w, mean, rstd, dx, rows, dim);
+  norm_bwd_wgrad_kernel<<<(dim + 31) / 32, 256, 0, stream>>>(dy, x, mean, rstd, dw, layernorm ? db : nullptr, rows, dim);
+  count_launch(2);
+  return cudaGetLastError();
+}
+
+// ------------------------------------------------------------------ AdamW --
+__global__ void __launch_bounds__(256) adamw_kernel(float* __restrict__ p, const float* __restrict__ g, float* __restrict__ m,
+                                                    float* __restrict__ v, __nv_bfloat16* __restrict__ p16, long long n4, long long n,
+                                                    float lr, float b1, float b2, float eps, float wd,
+                                                    const float* __restrict__ step_ptr, float gscale) {
+  const float step = *step_ptr;
+  const float bc1 = 1.f - powf(b1, step), bc2 = 1.f - powf(b2, step);
+  const float inv_bc1 = 1.f / bc1, inv_sqrt_bc2 = rsqrtf(bc2), decay = 1.f - lr * wd;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n4;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float4 pp = reinterpret_cast<float4*>(p)[i], gg = reinterpret_cast<const float4*>(g)[i];
+    float4 mm = reinterpret_cast<float4*>(m)[i], vv = reinterpret_cast<float4*>(v)[i];
+    float* P = &pp.x; float* G = &gg.x; float* M = &mm.x; float* V = &vv.x;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float gk = G[k] * gscale;
+      M[k] = b1 * M[k] + (1.f - b1) * gk;
+      V[k] = b2 * V[k] + (1.f - b2) * gk * gk;
+      const float denom = sqrtf(V[k]) * inv_sqrt_bc2 + eps;
+      P[k] = P[k] * decay - lr * (M[k] * inv_bc1) / denom;
+    }
+    reinterpret_cast<float4*>(p)[i] = pp;
+    reinterpret_cast<float4*>(m)[i] = mm;
+    reinterpret_cast<float4*>(v)[i] = vv;
+    if (p16) {
+      __nv_bfloat162 lo = __floats2bfloat162_rn(pp.x, pp.y), hi = __floats2bfloat162_rn(pp.z, pp.w);
+      uint2 packed;
+      packed.x = *reinterpret_cast<uint32_t*>(&lo);
+      packed.y = *reinterpret_cast<uint32_t*>(&hi);
+      reinterpret_cast<uint2*>(p16)[i] = packed;
+    }
+  }
+  // scalar tail (n not a multiple of 4)
+  if (blockIdx.x == 0) {
+    for (long long i = n4 * 4 + threadIdx.x; i < n; i += blockDim.x) {
+      const float gk = g[i] * gscale;
+      const float mk = b1 * m[i] + (1.f - b1) * gk, vk = b2 * v[i] + (1.f - b2) * gk * gk;
+      m[i] = mk;
+      v[i] = vk;
+      const float pk = p[i] * decay - lr * (mk * inv_bc1) / (sqrtf(vk) * inv_sqrt_bc2 + eps);
+      p[i] = pk;
+      if (p16) p16[i] = __float2bfloat16_rn(pk);
+    }
+  }
+}
+
+cudaError_t adamw_flat(float* p, const float* g, float* m, float* v, __nv_bfloat16* p16, long long n, float lr, float beta1,
+                       float beta2, float eps, float wd, const float* step, float grad_scale, cudaStream_t stream) {
+  if (n <= 0) return cudaSuccess;
+  if ((reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(m) |
+       reinterpret_cast<uintptr_t>(v)) & 15u)
+    return cudaErrorNotSupported;
+  const long long n4 = n / 4;
+  long long blocks = (n4 + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  if (blocks < 1) blocks = 1;
+  adamw_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(p, g, m, v, p16, n4, n, lr, beta1, beta2, eps, wd, step, grad_scale);
+  count_launch();
+  return cudaGetLastError();
+}
+
+// ---------------------------------------------------------- cross entropy --
+// One CTA per row.  Pass 1: running max and sum of exp (online softmax).
+// Pass 2: overwrite the row with (softmax - onehot) * scale.
+__global__ void __launch_bounds__(512) ce_kernel(__nv_bfloat16* __restrict__ logits, const long long* __restrict__ targets,
+                                                 float* __restrict__ loss_rows, int vocab, float scale) {
+  __shared__ float s_max[16], s_sum[16];
+  const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+  __nv_bfloat16* lr = logits + static_cast<size_t>(row) * vocab;
+  uint4* lv = reinterpret_cast<uint4*>(lr);
+  const int vecs = vocab >> 3;
+  float mx = -INFINITY, sm = 0.f;
+  for (int v = tid; v < vecs; v += blockDim.x) {
+    float f[8];
+    unpack8(lv[v], f);
+    float local = f[0];
+#pragma unroll
+    for (int i = 1; i < 8; ++i) local = fmaxf(local, f[i]);
+    if (local > mx) {
+      sm *= __expf(mx - local);
+      mx = local;
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) sm += __expf(f[i] - mx);
+  }
+  for (int c = vecs * 8 + tid; c < vocab; c += blockDim.x) {
+    const float f = __bfloat162float(lr[c]);
+    if (f > mx) {
+      sm *= __expf(mx - f);
+      mx = f;
+    }
+    sm += __expf(f - mx);
+  }
+  // combine (max, sum) pairs: warp, then block
+  const float wmx = warp_max(mx);
+  sm = warp_sum(sm * __expf(mx - wmx));
+  if (lane == 0) {
+    s_max[wid] = wmx;
+    s_sum[wid] = sm;
+  }
+  __syncthreads();
+  const int nw = blockDim.x >> 5;
+  float bmx = -INFINITY;
+  for (int i = 0; i < nw; ++i) bmx = fmaxf(bmx, s_max[i]);
+  float bsum = 0.f;
+  for (int i = 0; i < nw; ++i) bsum += s_sum[i] * __expf(s_max[i] - bmx);
+  const long long tgt = targets[row];
+  const bool ignore = tgt < 0 || tgt >= vocab;
+  if (tid == 0) loss_rows[row] = ignore ? 0.f : (logf(bsum) + bmx - __bfloat162float(lr[tgt]));
+  __syncthreads();  // the target logit is read before anyone overwrites it
+  const float inv = ignore ? 0.f : scale / bsum;
+  for (int v = tid; v < vecs; v += blockDim.x) {
+    float f[8], o[8];
+    unpack8(lv[v], f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      o[i] = __expf(f[i] - bmx) * inv;
+      if (!ignore && v * 8 + i == tgt) o[i] -= scale;
+    }
+    lv[v] = pack8(o);
+  }
+  for (int c = vecs * 8 + tid; c < vocab; c += blockDim.x) {
+    float o = __expf(__bfloat162float(lr[c]) - bmx) * inv;
+    if (!ignore && c == tgt) o -= scale;
+    lr[c] = __float2bfloat16_rn(o);
+  }
+}
+
+cudaError_t cross_entropy_fwd_bwd(__nv_bfloat16* logits, const long long* targets, float* loss_rows, int rows, int vocab,
+                                  float grad_scale, cudaStream_t stream) {
+  if (vocab % 8 != 0 || (reinterpret_cast<uintptr_t>(logits) & 15u)) return cudaErrorNotSupported;
+  ce_kernel<<<rows, 512, 0, stream>>>(logits, targets, loss_rows, vocab, grad_scale);
+  count_launch();
+  return cudaGetLastError();
+}
+
+// -------------------------------------------------------------- transpose --
+__global__ void __launch_bounds__(256) transpose_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out,
+                                                        int rows, int cols) {
+  __shared__ __nv_bfloat16 tile[64][66];
+  const int c0 = blockIdx.x * 64, r0 = blockIdx.y * 64;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
+  for (int rr = ty; rr < 64; rr += 8) {
+    const int r = r0 + rr;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int c = c0 + tx * 2 + h;
+      tile[rr][tx * 2 + h] = (r < rows && c < cols) ? in[static_cast<size_t>(r) * cols + c] : __float2bfloat16(0.f);
+    }
+  }
+  __syncthreads();
+  for (int cc = ty; cc < 64; cc += 8) {
+    const int c = c0 + cc;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int r = r0 + tx * 2 + h;
+      if (c < cols && r < rows) out[static_cast<size_t>(c) * rows + r] = tile[tx * 2 + h][cc];
+    }
+  }
+}
+
+cudaError_t transpose_bf16(const __nv_bfloat16* in, __nv_bfloat16* out, int rows, int cols, cudaStream_t stream) {
+  dim3 grid((cols + 63) / 64, (rows + 63) / 64);
+  transpose_kernel<<<grid, 256, 0, stream>>>(in, out, rows, cols);
+  count_launch();
+  return cudaGetLastError();
+}
+
+// ------------------------------------------------------------------ casts --
+__global__ void __launch_bounds__(256) cast_kernel(const float* __restrict__ in, __nv_bfloat16* __restrict__ out, long long n) {
+  const long long n4 = n / 4;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n4;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const float4 f = reinterpret_cast<const float4*>(in)[i];
+    __nv_bfloat162 lo = __floats2bfloat162_rn(f.x, f.y), hi = __floats2bfloat162_rn(f.z, f.w);
+    uint2 packed;
+    packed.x = *reinterpret_cast<uint32_t*>(&lo);
+    packed.y = *reinterpret_cast<uint32_t*>(&hi);
+    reinterpret_cast<uint2*>(out)[i] = packed;
+  }
+  if (blockIdx.x == 0)
+    for (long long i = n4 * 4 + threadIdx.x; i < n; i += blockDim.x) out[i] = __float2bfloat16_rn(in[i]);
+}
+
+cudaError_t cast_f32_bf16(const float* in, __nv_bfloat16* out, long long n, cudaStream_t stream) {
+  if (n <= 0) return cudaSuccess;
+  if ((reinterpret_cast<uintptr_t>(in) & 15u) || (reinterpret_cast<uintptr_t>(out) & 7u)) return cudaErrorNotSupported;
+  long long blocks = (n / 4 + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  if (blocks < 1) blocks = 1;
+  cast_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(in, out, n);
+  count_launch();
+  return cudaGetLastError();
+}
+
+// ------------------------------------------------------------- GELU bwd ---
+__global__ void __launch_bounds__(256) gelu_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ z,
+                                                       __nv_bfloat16* __restrict__ dz, long long n8) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n8;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float g[8], zz[8], o[8];
+    unpack8(reinterpret_cast<const uint4*>(dy)[i], g);
+    unpack8(reinterpret_cast<const uint4*>(z)[i], zz);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const float x = zz[k];
+      const float cdf = 0.5f * (1.f + erff(x * 0.70710678f));
+      const float pdf = 0.39894228f * __expf(-0.5f * x * x);
+      o[k] = g[k] * (cdf + x * pdf);
+    }
+    reinterpret_cast<uint4*>(dz)[i] = pack8(o);
+  }
+}
+
+cudaError_t gelu_bwd(const __nv_bfloat16* dy, const __nv_bfloat16* z, __nv_bfloat16* dz, long long n, cudaStream_t stream) {
+  if (n % 8 != 0) return cudaErrorNotSupported;
+  long long blocks = (n / 8 + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  if (blocks < 1) blocks = 1;
+  gelu_bwd_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(dy, z, dz, n / 8);
+  count_launch();
+  return cudaGetLastError();
+}
+
+}  // namespace ops
+}  // namespace mccl

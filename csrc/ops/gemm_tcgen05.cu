@@ -1,0 +1,273 @@
+// bf16 GEMM on the 5th-generation tensor cores: D[M,N] = A[M,K] · B[N,K]^T with
+// fused epilogues (bias, GELU with saved pre-activation, fp32 output with
+// accumulation for weight gradients).
+//
+// Structure per CTA (one 128 x BN output tile):
+//   warp 0      TMA producer: cp.async.bulk.tensor loads of the A (128 x 64)
+//               and B (BN x 64) k-blocks into a ring of swizzled smem stages
+//   warp 1      allocates tensor memory, issues tcgen05.mma (one thread), and
+//               releases each stage with tcgen05.commit
+//   warps 2-5   epilogue: tcgen05.ld of the fp32 accumulator (one TMEM lane
+//               quarter per warp), bias / activation, 16-byte global stores
+// Shared memory per CTA is kept under half an SM so two CTAs are resident and
+// one tile's epilogue overlaps the other's main loop.
+//
+// The reference has no GEMM of its own (no tensor-core code at all); this
+// kernel exists for the model operators and as the core the fused
+// all-gather→GEMM / GEMM→reduce-scatter tensor-parallel kernels build on.
+#include "ops.hpp"
+#include "tcgen05.cuh"
+
+#include "../symm/cu_driver.hpp"
+
+namespace mccl {
+namespace ops {
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 64;          // 64 bf16 = 128 bytes = one swizzle row
+constexpr int UMMA_K = 16;      // bf16 MMA consumes 32 bytes of K per instruction
+
+__device__ int g_gemm_error = 0;
+
+struct GemmDev {
+  void* d;
+  __nv_bfloat16* aux;
+  const float* bias;
+  int m, n, k;
+  int ldd;
+  int d_fp32;
+  int accumulate;
+  int epilogue;
+};
+
+template <int BN, int STAGES>
+struct SmemLayout {
+  static constexpr int kABytes = BM * BK * 2;
+  static constexpr int kBBytes = BN * BK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kTiles = STAGES * kStageBytes;
+  static constexpr int kBarriers = (2 * STAGES + 1) * 8 + 16;
+  static constexpr int kTotal = kTiles + kBarriers + 1024;  // slack for 1024-byte alignment
+};
+
+__device__ __forceinline__ float gelu_erf(float x) { return 0.5f * x * (1.f + erff(x * 0.70710678f)); }
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
+                                                        const __grid_constant__ CUtensorMap tma_b, GemmDev g) {
+  using L = SmemLayout<BN, STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint8_t* tiles = smem;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + L::kTiles);
+  uint64_t* empty = full + STAGES;
+  uint64_t* acc_ready = empty + STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_ready + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_blk = blockIdx.x, m_blk = blockIdx.y;
+  const int num_kb = g.k / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      tc::mbar_init(&full[s], 1);
+      tc::mbar_init(&empty[s], 1);
+    }
+    tc::mbar_init(acc_ready, 1);
+    tc::mbar_init_fence();
+    tc::tma_prefetch_desc(&tma_a);
+    tc::tma_prefetch_desc(&tma_b);
+  }
+  if (warp == 1) tc::tmem_alloc(tmem_slot, BN);
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------ TMA producer --
+    if (lane == 0) {
+      bool ok = true;
+      int issued = 0;
+      for (int kb = 0; kb < num_kb && ok; ++kb) {
+        const int s = kb % STAGES;
+        if (kb >= STAGES) ok = tc::mbar_wait(&empty[s], ((kb / STAGES) - 1) & 1);
+        if (!ok) break;
+        tc::mbar_expect_tx(&full[s], L::kStageBytes);
+        uint8_t* a_dst = tiles + s * L::kStageBytes;
+        tc::tma_load_2d(a_dst, &tma_a, &full[s], kb * BK, m_blk * BM);
+        tc::tma_load_2d(a_dst + L::kABytes, &tma_b, &full[s], kb * BK, n_blk * BN);
+        issued = kb + 1;
+      }
+      if (!ok) {
+        atomicExch(&g_gemm_error, 1);
+        // let the copies already in flight land before the CTA retires
+        for (int kb = (issued > STAGES ? issued - STAGES : 0); kb < issued; ++kb)
+          tc::mbar_wait(&full[kb % STAGES], (kb / STAGES) & 1, 1u << 20);
+      }
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------- MMA issuer --
+    if (lane == 0) {
+      constexpr uint32_t idesc = tc::idesc_bf16(BM, BN);
+      bool ok = true;
+      for (int kb = 0; kb < num_kb; ++kb) {
+        const int s = kb % STAGES;
+        ok = tc::mbar_wait(&full[s], (kb / STAGES) & 1);
+        if (!ok) break;
+        tc::fence_after_sync();
+        const uint8_t* a_tile = tiles + s * L::kStageBytes;
+        const uint64_t da = tc::smem_desc_k_sw128(a_tile);
+        const uint64_t db = tc::smem_desc_k_sw128(a_tile + L::kABytes);
+#pragma unroll
+        for (int k4 = 0; k4 < BK / UMMA_K; ++k4) {
+          // advancing K by 16 elements = 32 bytes inside the swizzled row: +2 in the 16-byte address field
+          tc::mma_bf16(tmem_base, da + 2 * k4, db + 2 * k4, idesc, (kb | k4) != 0);
+        }
+        tc::mma_commit(&empty[s]);  // frees the stage once these MMAs have read it
+      }
+      if (!ok) atomicExch(&g_gemm_error, 2);
+      tc::mma_commit(acc_ready);    // on the failure path this still releases the epilogue warps
+    }
+  } else {
+    // ----------------------------------------------------------- epilogue --
+    const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) belong to this warp
+    const bool ok = tc::mbar_wait(acc_ready, 0);
+    tc::fence_after_sync();
+    const int row = m_blk * BM + quarter * 32 + lane;
+    const bool failed = !ok || (*reinterpret_cast<volatile int*>(&g_gemm_error) != 0);
+    if (!ok && lane == 0) atomicExch(&g_gemm_error, 3);
+#pragma unroll 1
+    for (int c0 = 0; c0 < BN; c0 += 32) {
+      uint32_t r[32];
+      tc::tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(c0), r);
+      tc::tmem_ld_wait();
+      const int col0 = n_blk * BN + c0;
+      if (failed || row >= g.m || col0 >= g.n) continue;
+      float v[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+      const int ncols = (g.n - col0) < 32 ? (g.n - col0) : 32;  // multiple of 8
+      if (g.epilogue == EPI_BIAS || g.epilogue == EPI_BIAS_GELU) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (j < ncols) v[j] += __ldg(g.bias + col0 + j);
+      }
+      if (g.epilogue == EPI_BIAS_GELU || g.epilogue == EPI_GELU) {
+        __nv_bfloat16* zrow = g.aux + static_cast<size_t>(row) * g.ldd + col0;
+#pragma unroll
+        for (int j8 = 0; j8 < 4; ++j8) {
+          if (j8 * 8 < ncols) {
+            uint4 pk;
+            __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[j8 * 8 + 2 * i], v[j8 * 8 + 2 * i + 1]);
+            *reinterpret_cast<uint4*>(zrow + j8 * 8) = pk;
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = gelu_erf(v[j]);
+      }
+      if (g.d_fp32) {
+        float* drow = static_cast<float*>(g.d) + static_cast<size_t>(row) * g.ldd + col0;
+#pragma unroll
+        for (int j4 = 0; j4 < 8; ++j4) {
+          if (j4 * 4 < ncols) {
+            float4 o = make_float4(v[j4 * 4], v[j4 * 4 + 1], v[j4 * 4 + 2], v[j4 * 4 + 3]);
+            if (g.accumulate) {
+              const float4 old = *reinterpret_cast<const float4*>(drow + j4 * 4);
+              o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+            }
+            *reinterpret_cast<float4*>(drow + j4 * 4) = o;
+          }
+        }
+      } else {
+        __nv_bfloat16* drow = static_cast<__nv_bfloat16*>(g.d) + static_cast<size_t>(row) * g.ldd + col0;
+#pragma unroll
+        for (int j8 = 0; j8 < 4; ++j8) {
+          if (j8 * 8 < ncols) {
+            uint4 pk;
+            __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[j8 * 8 + 2 * i], v[j8 * 8 + 2 * i + 1]);
+            *reinterpret_cast<uint4*>(drow + j8 * 8) = pk;
+          }
+        }
+      }
+    }
+  }
+  tc::fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc::fence_after_sync();
+    tc::tmem_dealloc(tmem_base, BN);
+  }
+}
+
+bool encode_map(CUtensorMap* map, const void* base, int rows, int cols, int ld_elems, int box_rows) {
+  const CuDriver& cu = CuDriver::get();
+  if (!cu.loaded || !cu.TensorMapEncodeTiled) return false;
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld_elems) * 2};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(BK), static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult rc = cu.TensorMapEncodeTiled(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
+                                        estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return rc == CUDA_SUCCESS;
+}
+
+template <int BN, int STAGES>
+cudaError_t launch_cfg(const GemmArgs& a, cudaStream_t stream) {
+  using L = SmemLayout<BN, STAGES>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t rc = cudaFuncSetAttribute(gemm_bf16_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal);
+    if (rc != cudaSuccess) return rc;
+    configured = true;
+  }
+  CUtensorMap ma, mb;
+  if (!encode_map(&ma, a.a, a.m, a.k, a.lda, BM) || !encode_map(&mb, a.b, a.n, a.k, a.ldb, BN)) return cudaErrorNotSupported;
+  GemmDev g;
+  g.d = a.d;
+  g.aux = a.aux;
+  g.bias = a.bias;
+  g.m = a.m;
+  g.n = a.n;
+  g.k = a.k;
+  g.ldd = a.ldd;
+  g.d_fp32 = a.d_fp32 ? 1 : 0;
+  g.accumulate = a.accumulate ? 1 : 0;
+  g.epilogue = a.epilogue;
+  dim3 grid((a.n + BN - 1) / BN, (a.m + BM - 1) / BM);
+  gemm_bf16_kernel<BN, STAGES><<<grid, 192, L::kTotal, stream>>>(ma, mb, g);
+  count_launch();
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t gemm_bf16_tn(const GemmArgs& a, cudaStream_t stream) {
+  if (a.m <= 0 || a.n <= 0 || a.k <= 0) return cudaErrorInvalidValue;
+  if (a.k % BK != 0 || a.n % 8 != 0) return cudaErrorNotSupported;
+  if (a.lda % 8 != 0 || a.ldb % 8 != 0 || a.ldd % (a.d_fp32 ? 4 : 8) != 0) return cudaErrorNotSupported;
+  if ((reinterpret_cast<uintptr_t>(a.a) | reinterpret_cast<uintptr_t>(a.b) | reinterpret_cast<uintptr_t>(a.d)) & 15u)
+    return cudaErrorNotSupported;
+  if (a.aux && (reinterpret_cast<uintptr_t>(a.aux) & 15u)) return cudaErrorNotSupported;
+  if ((a.epilogue == EPI_BIAS || a.epilogue == EPI_BIAS_GELU) && !a.bias) return cudaErrorInvalidValue;
+  if ((a.epilogue == EPI_BIAS_GELU || a.epilogue == EPI_GELU) && (!a.aux || a.d_fp32)) return cudaErrorInvalidValue;
+  if (a.accumulate && !a.d_fp32) return cudaErrorInvalidValue;
+  // 128 x 128 tiles, 3 stages of 32 KB: two CTAs per SM.
+  return launch_cfg<128, 3>(a, stream);
+}
+
+int gemm_error_flag() {
+  int v = 0;
+  cudaMemcpyFromSymbol(&v, g_gemm_error, sizeof(int));
+  return v;
+}
+
+}  // namespace ops
+}  // namespace mccl

@@ -41,6 +41,7 @@ CuDriver build_table() {
     return d;
   }
   d.loaded = true;
+  resolve(lib, "cuTensorMapEncodeTiled", d.TensorMapEncodeTiled);
   bool mc = true;
   mc &= resolve(lib, "cuMulticastCreate", d.MulticastCreate);
   mc &= resolve(lib, "cuMulticastAddDevice", d.MulticastAddDevice);

@@ -1,0 +1,134 @@
+"""autograd Functions over the native kernels (CUDA tensors only)."""
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+
+from .. import _C
+
+
+def _bf16_weight(weight: torch.Tensor) -> torch.Tensor:
+    """bf16 copy of an fp32 parameter: the trainer keeps one up to date (`_bf16`), else cast now."""
+    w16 = getattr(weight, "_bf16", None)
+    if w16 is not None:
+        return w16
+    if weight.dtype == torch.bfloat16:
+        return weight
+    return _C.cast_bf16(weight.detach().contiguous())
+
+
+def _bf16_weight_t(weight: torch.Tensor, w16: torch.Tensor) -> torch.Tensor:
+    wt = getattr(weight, "_bf16_t", None)
+    return wt if wt is not None else _C.transpose_bf16(w16)
+
+
+def _gemm_ok(m: int, n: int, k: int) -> bool:
+    return k % 64 == 0 and n % 8 == 0 and m > 0
+
+
+class LinearFn(torch.autograd.Function):
+    """y = act(x @ W^T + b); W [N, K] fp32 master, x [..., K] bf16."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, act):
+        K, N = weight.shape[1], weight.shape[0]
+        x2 = x.reshape(-1, K)
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        M = x2.shape[0]
+        w16 = _bf16_weight(weight)
+        ctx.act, ctx.has_bias, ctx.native = act, bias is not None, _gemm_ok(M, N, K)
+        if ctx.native:
+            y, z = _C.gemm_bf16(x2, w16, bias, act)
+        else:
+            z = F.linear(x2, w16, None if bias is None else bias.to(x2.dtype))
+            y = F.gelu(z) if act == "gelu" else z
+            z = z if act == "gelu" else None
+        ctx.save_for_backward(x2, w16, z if z is not None else x2.new_empty(0))
+        ctx.weight = weight
+        return y.view(*x.shape[:-1], N)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w16, z = ctx.saved_tensors
+        weight = ctx.weight
+        N, K = w16.shape
+        M = x2.shape[0]
+        dy2 = dy.reshape(-1, N)
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dz = _C.gelu_bwd(dy2, z) if ctx.act == "gelu" else dy2
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            if _gemm_ok(M, K, N):
+                dx, _ = _C.gemm_bf16(dz, _bf16_weight_t(weight, w16))
+            else:
+                dx = dz @ w16
+            dx = dx.view(*dy.shape[:-1], K)
+        if ctx.needs_input_grad[1]:
+            if _gemm_ok(N, K, M):
+                dw, _ = _C.gemm_bf16(_C.transpose_bf16(dz), _C.transpose_bf16(x2), None, "none", True)
+            else:
+                dw = (dz.t() @ x2).float()
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = dz.sum(0, dtype=torch.float32)
+        return dx, dw, db, None
+
+
+class NormFn(torch.autograd.Function):
+    """LayerNorm (bias given) or RMSNorm (bias None) over the last dimension; fp32 weight / bias."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, eps):
+        xc = x if x.is_contiguous() else x.contiguous()
+        y, mean, rstd = _C.norm_fwd(xc, weight, bias, eps)
+        ctx.save_for_backward(xc, weight, mean, rstd)
+        ctx.layernorm = bias is not None
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, weight, mean, rstd = ctx.saved_tensors
+        dyc = dy if dy.is_contiguous() else dy.contiguous()
+        dx, dw, db = _C.norm_bwd(dyc, x, weight, mean, rstd, ctx.layernorm)
+        return dx, dw, db, None
+
+
+class LinearCrossEntropyFn(torch.autograd.Function):
+    """mean CE(h @ W^T, targets).  The backward of the loss with respect to the logits is
+    produced in the same pass that computes the loss, in place of the logits, assuming the
+    loss is what ``backward()`` is called on (upstream gradient 1)."""
+
+    @staticmethod
+    def forward(ctx, h, weight, targets):
+        T, D = h.shape
+        V = weight.shape[0]
+        hc = h if h.is_contiguous() else h.contiguous()
+        w16 = _bf16_weight(weight)
+        if _gemm_ok(T, V, D):
+            logits, _ = _C.gemm_bf16(hc, w16)
+        else:
+            logits = F.linear(hc, w16)
+        loss_rows = _C.ce_fwd_bwd(logits, targets.contiguous(), 1.0 / T)
+        ctx.save_for_backward(hc, w16, logits)   # logits now hold d(loss)/d(logits)
+        ctx.weight = weight
+        return loss_rows.mean()
+
+    @staticmethod
+    def backward(ctx, gout):
+        h, w16, dlogits = ctx.saved_tensors
+        weight = ctx.weight
+        T, D = h.shape
+        V = w16.shape[0]
+        dh = dw = None
+        if ctx.needs_input_grad[0]:
+            if _gemm_ok(T, D, V):
+                dh, _ = _C.gemm_bf16(dlogits, _bf16_weight_t(weight, w16))
+            else:
+                dh = dlogits @ w16
+        if ctx.needs_input_grad[1]:
+            if _gemm_ok(V, D, T):
+                dw, _ = _C.gemm_bf16(_C.transpose_bf16(dlogits), _C.transpose_bf16(h), None, "none", True)
+            else:
+                dw = (dlogits.t() @ h).float()
+        return dh, dw, None
