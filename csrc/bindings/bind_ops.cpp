@@ -91,7 +91,10 @@ void bind_ops(py::module_& m) {
           aux = at::empty({M, N}, a.options());
           g.aux = bf(aux);
         }
-        check_launch(ops::gemm_bf16_tn(g, stream_of(a)), "gemm_bf16");
+        cudaError_t rc = ops::gemm_bf16_tn(g, stream_of(a));
+        MCCL_CHECK_T(rc == cudaSuccess, CudaError,
+                     "gemm_bf16 [" << M << "x" << N << "x" << K << ", lda " << g.lda << ", ldb " << g.ldb << ", ldd " << g.ldd
+                                   << "] failed: " << cudaGetErrorString(rc) << " " << ops::gemm_last_reason());
         return std::make_pair(d, aux.defined() ? c10::optional<at::Tensor>(aux) : c10::nullopt);
       },
       py::arg("a"), py::arg("b"), py::arg("bias") = py::none(), py::arg("epilogue") = "none", py::arg("out_fp32") = false,

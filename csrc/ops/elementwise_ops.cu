@@ -278,7 +278,7 @@ __global__ void __launch_bounds__(512) ce_kernel(__nv_bfloat16* __restrict__ log
   }
   // combine (max, sum) pairs: warp, then block
   const float wmx = warp_max(mx);
-  sm = warp_sum(sm * __expf(mx - wmx));
+  sm = warp_sum(mx == -INFINITY ? 0.f : sm * __expf(mx - wmx));  // threads without elements hold (-inf, 0)
   if (lane == 0) {
     s_max[wid] = wmx;
     s_sum[wid] = sm;
@@ -288,7 +288,7 @@ __global__ void __launch_bounds__(512) ce_kernel(__nv_bfloat16* __restrict__ log
   float bmx = -INFINITY;
   for (int i = 0; i < nw; ++i) bmx = fmaxf(bmx, s_max[i]);
   float bsum = 0.f;
-  for (int i = 0; i < nw; ++i) bsum += s_sum[i] * __expf(s_max[i] - bmx);
+  for (int i = 0; i < nw; ++i) bsum += s_max[i] == -INFINITY ? 0.f : s_sum[i] * __expf(s_max[i] - bmx);
   const long long tgt = targets[row];
   const bool ignore = tgt < 0 || tgt >= vocab;
   if (tid == 0) loss_rows[row] = ignore ? 0.f : (logf(bsum) + bmx - __bfloat162float(lr[tgt]));

@@ -209,6 +209,9 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
 bool encode_map(CUtensorMap* map, const void* base, int rows, int cols, int ld_elems, int box_rows) {
   const CuDriver& cu = CuDriver::get();
   if (!cu.loaded || !cu.TensorMapEncodeTiled) return false;
+  int device = 0;
+  cudaGetDevice(&device);
+  cu.ensure_context(device);
   cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
   cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld_elems) * 2};
   cuuint32_t box[2] = {static_cast<cuuint32_t>(BK), static_cast<cuuint32_t>(box_rows)};
@@ -217,6 +220,12 @@ bool encode_map(CUtensorMap* map, const void* base, int rows, int cols, int ld_e
                                         estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return rc == CUDA_SUCCESS;
+}
+
+thread_local const char* t_reason = "";
+cudaError_t unsupported(const char* why) {
+  t_reason = why;
+  return cudaErrorNotSupported;
 }
 
 template <int BN, int STAGES>
@@ -229,7 +238,9 @@ cudaError_t launch_cfg(const GemmArgs& a, cudaStream_t stream) {
     configured = true;
   }
   CUtensorMap ma, mb;
-  if (!encode_map(&ma, a.a, a.m, a.k, a.lda, BM) || !encode_map(&mb, a.b, a.n, a.k, a.ldb, BN)) return cudaErrorNotSupported;
+  if (!encode_map(&ma, a.a, a.m, a.k, a.lda, BM) || !encode_map(&mb, a.b, a.n, a.k, a.ldb, BN))
+    return unsupported("cuTensorMapEncodeTiled rejected an operand");
+  (void)cudaGetLastError();  // a stale error of an earlier, unrelated call must not be blamed on this launch
   GemmDev g;
   g.d = a.d;
   g.aux = a.aux;
@@ -249,13 +260,17 @@ cudaError_t launch_cfg(const GemmArgs& a, cudaStream_t stream) {
 
 }  // namespace
 
+const char* gemm_last_reason() { return t_reason; }
+
 cudaError_t gemm_bf16_tn(const GemmArgs& a, cudaStream_t stream) {
+  t_reason = "";
   if (a.m <= 0 || a.n <= 0 || a.k <= 0) return cudaErrorInvalidValue;
-  if (a.k % BK != 0 || a.n % 8 != 0) return cudaErrorNotSupported;
-  if (a.lda % 8 != 0 || a.ldb % 8 != 0 || a.ldd % (a.d_fp32 ? 4 : 8) != 0) return cudaErrorNotSupported;
+  if (a.k % BK != 0 || a.n % 8 != 0) return unsupported("K must be a multiple of 64 and N a multiple of 8");
+  if (a.lda % 8 != 0 || a.ldb % 8 != 0 || a.ldd % (a.d_fp32 ? 4 : 8) != 0)
+    return unsupported("row strides must keep rows 16-byte aligned");
   if ((reinterpret_cast<uintptr_t>(a.a) | reinterpret_cast<uintptr_t>(a.b) | reinterpret_cast<uintptr_t>(a.d)) & 15u)
-    return cudaErrorNotSupported;
-  if (a.aux && (reinterpret_cast<uintptr_t>(a.aux) & 15u)) return cudaErrorNotSupported;
+    return unsupported("operand pointers must be 16-byte aligned");
+  if (a.aux && (reinterpret_cast<uintptr_t>(a.aux) & 15u)) return unsupported("aux pointer must be 16-byte aligned");
   if ((a.epilogue == EPI_BIAS || a.epilogue == EPI_BIAS_GELU) && !a.bias) return cudaErrorInvalidValue;
   if ((a.epilogue == EPI_BIAS_GELU || a.epilogue == EPI_GELU) && (!a.aux || a.d_fp32)) return cudaErrorInvalidValue;
   if (a.accumulate && !a.d_fp32) return cudaErrorInvalidValue;

@@ -68,6 +68,8 @@ struct GemmArgs {
 // Returns cudaErrorNotSupported for shapes the kernel does not cover
 // (K % 64 != 0, N % 8 != 0, unaligned pointers); the caller falls back.
 cudaError_t gemm_bf16_tn(const GemmArgs& args, cudaStream_t stream);
+// Why the last gemm_bf16_tn call on this thread returned cudaErrorNotSupported ("" otherwise).
+const char* gemm_last_reason();
 // Non-zero when a pipeline wait inside a GEMM kernel ran out (kernel returned early).
 int gemm_error_flag();
 

@@ -42,6 +42,9 @@ CuDriver build_table() {
   }
   d.loaded = true;
   resolve(lib, "cuTensorMapEncodeTiled", d.TensorMapEncodeTiled);
+  resolve(lib, "cuCtxGetCurrent", d.CtxGetCurrent);
+  resolve(lib, "cuCtxSetCurrent", d.CtxSetCurrent);
+  resolve(lib, "cuDevicePrimaryCtxRetain", d.DevicePrimaryCtxRetain);
   bool mc = true;
   mc &= resolve(lib, "cuMulticastCreate", d.MulticastCreate);
   mc &= resolve(lib, "cuMulticastAddDevice", d.MulticastAddDevice);
@@ -58,6 +61,17 @@ CuDriver build_table() {
 const CuDriver& CuDriver::get() {
   static const CuDriver table = build_table();
   return table;
+}
+
+void CuDriver::ensure_context(int device) const {
+  if (!CtxGetCurrent || !CtxSetCurrent || !DevicePrimaryCtxRetain || !DeviceGet) return;
+  CUcontext ctx = nullptr;
+  if (CtxGetCurrent(&ctx) == CUDA_SUCCESS && ctx != nullptr) return;
+  CUdevice dev;
+  if (DeviceGet(&dev, device) != CUDA_SUCCESS) return;
+  // The primary context is never released by this process, so the extra
+  // reference taken here costs nothing.
+  if (DevicePrimaryCtxRetain(&ctx, dev) == CUDA_SUCCESS) CtxSetCurrent(ctx);
 }
 
 std::string CuDriver::error_string(CUresult r) const {

@@ -39,6 +39,14 @@ struct CuDriver {
   CUresult (*MulticastUnbind)(CUmemGenericAllocationHandle, CUdevice, size_t, size_t) = nullptr;
   CUresult (*MulticastGetGranularity)(size_t*, const CUmulticastObjectProp*, CUmulticastGranularity_flags) = nullptr;
 
+  CUresult (*CtxGetCurrent)(CUcontext*) = nullptr;
+  CUresult (*CtxSetCurrent)(CUcontext) = nullptr;
+  CUresult (*DevicePrimaryCtxRetain)(CUcontext*, CUdevice) = nullptr;
+  // Driver calls need a context bound to the calling thread; threads that have
+  // only used cached allocations so far (autograd workers) may have none yet.
+  // Binds the primary context of `device` when the thread has no context.
+  void ensure_context(int device) const;
+
   // TMA descriptors (optional; absent only on very old drivers)
   CUresult (*TensorMapEncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                    const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
