@@ -45,18 +45,24 @@ void bind_ops(py::module_& m) {
   m.def("gemm_error_flag", [] { return ops::gemm_error_flag(); });
 
   // D[M,N] = A[M,K] · B[N,K]^T.  A and B are 2-D bf16 with unit inner stride
-  // (row strides may exceed K).  Returns (D, pre_activation or None).
+  // (row strides may exceed the row length).  With a_t (b_t) the operand is
+  // passed as stored [K, M] ([K, N]) and read MN-major, so no transposed copy is
+  // needed for weight-gradient and input-gradient products.
+  // Returns (D, pre_activation or None).
   m.def(
       "gemm_bf16",
       [](const at::Tensor& a, const at::Tensor& b, const c10::optional<at::Tensor>& bias, const std::string& epilogue,
-         bool out_fp32, const c10::optional<at::Tensor>& out, bool accumulate) {
+         bool out_fp32, const c10::optional<at::Tensor>& out, bool accumulate, bool a_t, bool b_t) {
         need_cuda(a, "gemm(a)");
         need_cuda(b, "gemm(b)");
         MCCL_CHECK_TENSOR(a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16, "gemm: operands must be bf16");
-        MCCL_CHECK_TENSOR(a.dim() == 2 && b.dim() == 2 && a.size(1) == b.size(1), "gemm: shapes [M,K] x [N,K] expected");
-        MCCL_CHECK_TENSOR(a.stride(1) == 1 && b.stride(1) == 1, "gemm: K must be the contiguous dimension of both operands");
+        MCCL_CHECK_TENSOR(a.dim() == 2 && b.dim() == 2, "gemm: 2-D operands expected");
+        MCCL_CHECK_TENSOR(a.stride(1) == 1 && b.stride(1) == 1, "gemm: operands need unit inner stride");
         c10::cuda::CUDAGuard guard(a.device());
-        const int64_t M = a.size(0), N = b.size(0), K = a.size(1);
+        // a_t: a is stored [K, M]; b_t: b is stored [K, N].
+        const int64_t M = a_t ? a.size(1) : a.size(0), K = a_t ? a.size(0) : a.size(1);
+        const int64_t N = b_t ? b.size(1) : b.size(0);
+        MCCL_CHECK_TENSOR((b_t ? b.size(0) : b.size(1)) == K, "gemm: contraction sizes differ");
         at::Tensor d;
         if (out.has_value()) {
           d = *out;
@@ -78,6 +84,8 @@ void bind_ops(py::module_& m) {
         g.ldd = static_cast<int>(d.stride(0));
         g.d_fp32 = out_fp32;
         g.accumulate = accumulate;
+        g.a_mn_major = a_t;
+        g.b_mn_major = b_t;
         at::Tensor bias_f;
         if (bias.has_value() && bias->defined()) {
           need(*bias, at::kFloat, "gemm(bias)");
@@ -98,7 +106,7 @@ void bind_ops(py::module_& m) {
         return std::make_pair(d, aux.defined() ? c10::optional<at::Tensor>(aux) : c10::nullopt);
       },
       py::arg("a"), py::arg("b"), py::arg("bias") = py::none(), py::arg("epilogue") = "none", py::arg("out_fp32") = false,
-      py::arg("out") = py::none(), py::arg("accumulate") = false);
+      py::arg("out") = py::none(), py::arg("accumulate") = false, py::arg("a_t") = false, py::arg("b_t") = false);
 
   m.def(
       "norm_fwd",
@@ -137,8 +145,10 @@ void bind_ops(py::module_& m) {
         at::Tensor dx = at::empty_like(x);
         at::Tensor dw = at::empty({dim}, x.options().dtype(at::kFloat));
         at::Tensor db = layernorm ? at::empty({dim}, x.options().dtype(at::kFloat)) : at::Tensor();
+        at::Tensor scratch = at::empty({2 * ops::colsum_slabs(static_cast<int>(rows)) * dim}, x.options().dtype(at::kFloat));
         check_launch(ops::norm_bwd(bf(dy), bf(x), w.data_ptr<float>(), mean.data_ptr<float>(), rstd.data_ptr<float>(), bf(dx),
-                                   dw.data_ptr<float>(), layernorm ? db.data_ptr<float>() : nullptr, static_cast<int>(rows),
+                                   dw.data_ptr<float>(), layernorm ? db.data_ptr<float>() : nullptr, scratch.data_ptr<float>(),
+                                   static_cast<int>(rows),
                                    static_cast<int>(dim), layernorm, stream_of(x)),
                      "norm_bwd");
         return std::make_tuple(dx, dw, db.defined() ? c10::optional<at::Tensor>(db) : c10::nullopt);
@@ -189,6 +199,16 @@ void bind_ops(py::module_& m) {
       py::arg("logits"), py::arg("targets"), py::arg("grad_scale") = 1.0,
       "Returns per-row losses; overwrites logits with (softmax - onehot) * grad_scale.");
 
+  m.def("colsum_bf16", [](const at::Tensor& x) {
+    need(x, at::kBFloat16, "colsum(x)");
+    MCCL_CHECK_TENSOR(x.dim() == 2, "colsum: 2-D tensor expected");
+    c10::cuda::CUDAGuard guard(x.device());
+    const int rows = static_cast<int>(x.size(0)), dim = static_cast<int>(x.size(1));
+    at::Tensor out = at::empty({dim}, x.options().dtype(at::kFloat));
+    at::Tensor scratch = at::empty({ops::colsum_slabs(rows) * dim}, x.options().dtype(at::kFloat));
+    check_launch(ops::colsum_bf16(bf(x), out.data_ptr<float>(), scratch.data_ptr<float>(), rows, dim, stream_of(x)), "colsum");
+    return out;
+  });
   m.def("transpose_bf16", [](const at::Tensor& x) {
     need(x, at::kBFloat16, "transpose(x)");
     MCCL_CHECK_TENSOR(x.dim() == 2, "transpose: 2-D tensor expected");

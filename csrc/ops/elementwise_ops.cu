@@ -131,36 +131,75 @@ __global__ void __launch_bounds__(256) norm_bwd_dx_kernel(const __nv_bfloat16* _
   }
 }
 
-// dw[c] = sum_r dy[r,c] * xhat[r,c]; db[c] = sum_r dy[r,c].  Block = 32 columns x 8 row lanes.
-__global__ void __launch_bounds__(256) norm_bwd_wgrad_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+// Column reductions over the rows: dw[c] = sum_r dy[r,c] * xhat[r,c] and
+// db[c] = sum_r dy[r,c] (kNorm), or just the column sum (bias gradients).
+// Stage 1: a block of 32 x 8 threads covers 256 columns (8 per thread, one
+// 16-byte load per row) and a slab of kSlabRows rows, and writes one partial
+// row.  Stage 2 adds the partial rows in a fixed order, so the result does not
+// depend on scheduling.
+constexpr int kSlabRows = 64;
+
+template <bool kNorm>
+__global__ void __launch_bounds__(256) colsum_partial_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                                                              const float* __restrict__ mean, const float* __restrict__ rstd,
-                                                             float* __restrict__ dw, float* __restrict__ db, int rows, int dim) {
-  __shared__ float sw[8][33], sb[8][33];
-  const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
-  const int col = blockIdx.x * 32 + cx;
-  float aw = 0.f, ab = 0.f;
+                                                             float* __restrict__ part_w, float* __restrict__ part_b, int rows,
+                                                             int dim) {
+  __shared__ float sw[8][32][9], sb[8][32][9];
+  const int cg = threadIdx.x & 31, ry = threadIdx.x >> 5;
+  const int col = blockIdx.x * 256 + cg * 8;
+  const int r0 = blockIdx.y * kSlabRows;
+  const int r1 = min(r0 + kSlabRows, rows);
+  float aw[8] = {0, 0, 0, 0, 0, 0, 0, 0}, ab[8] = {0, 0, 0, 0, 0, 0, 0, 0};
   if (col < dim) {
-    for (int r = ry; r < rows; r += 8) {
-      const float g = __bfloat162float(dy[static_cast<size_t>(r) * dim + col]);
-      const float xv = __bfloat162float(x[static_cast<size_t>(r) * dim + col]);
-      aw += g * (xv - mean[r]) * rstd[r];
-      ab += g;
+    for (int r = r0 + ry; r < r1; r += 8) {
+      float g[8];
+      unpack8(*reinterpret_cast<const uint4*>(dy + static_cast<size_t>(r) * dim + col), g);
+      if (kNorm) {
+        float xv[8];
+        unpack8(*reinterpret_cast<const uint4*>(x + static_cast<size_t>(r) * dim + col), xv);
+        const float mu = mean[r], rs = rstd[r];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) aw[i] += g[i] * (xv[i] - mu) * rs;
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ab[i] += g[i];
     }
   }
-  sw[ry][cx] = aw;
-  sb[ry][cx] = ab;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    sw[ry][cg][i] = aw[i];
+    sb[ry][cg][i] = ab[i];
+  }
   __syncthreads();
-  if (ry == 0 && col < dim) {
+  // 256 threads, 256 columns: thread t finishes column t of this block
+  const int c = threadIdx.x, ccg = c >> 3, ci = c & 7;
+  if (blockIdx.x * 256 + c < dim) {
     float tw = 0.f, tb = 0.f;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      tw += sw[i][cx];
-      tb += sb[i][cx];
+    for (int k = 0; k < 8; ++k) {
+      tw += sw[k][ccg][ci];
+      tb += sb[k][ccg][ci];
     }
-    dw[col] = tw;
-    if (db) db[col] = tb;
+    const size_t o = static_cast<size_t>(blockIdx.y) * dim + blockIdx.x * 256 + c;
+    if (kNorm) part_w[o] = tw;
+    if (part_b) part_b[o] = tb;
   }
 }
+
+__global__ void __launch_bounds__(256) colsum_final_kernel(const float* __restrict__ part_w, const float* __restrict__ part_b,
+                                                           float* __restrict__ dw, float* __restrict__ db, int slabs, int dim) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= dim) return;
+  float tw = 0.f, tb = 0.f;
+  for (int s = 0; s < slabs; ++s) {
+    if (part_w) tw += part_w[static_cast<size_t>(s) * dim + c];
+    if (part_b) tb += part_b[static_cast<size_t>(s) * dim + c];
+  }
+  if (dw) dw[c] = tw;
+  if (db) db[c] = tb;
+}
+
+int colsum_slabs(int rows) { return (rows + kSlabRows - 1) / kSlabRows; }
 
 cudaError_t norm_fwd(const __nv_bfloat16* x, const float* w, const float* b, __nv_bfloat16* y, float* mean, float* rstd,
                      int rows, int dim, float eps, cudaStream_t stream) {
@@ -173,12 +212,28 @@ cudaError_t norm_fwd(const __nv_bfloat16* x, const float* w, const float* b, __n
 }
 
 cudaError_t norm_bwd(const __nv_bfloat16* dy, const __nv_bfloat16* x, const float* w, const float* mean, const float* rstd,
-                     __nv_bfloat16* dx, float* dw, float* db, int rows, int dim, bool layernorm, cudaStream_t stream) {
+                     __nv_bfloat16* dx, float* dw, float* db, float* scratch, int rows, int dim, bool layernorm,
+                     cudaStream_t stream) {
   if (dim % 8 != 0) return cudaErrorNotSupported;
   const int blocks = (rows + 7) / 8;
   if (layernorm) norm_bwd_dx_kernel<true><<<blocks, 256, 0, stream>>>(dy, x, w, mean, rstd, dx, rows, dim);
   else norm_bwd_dx_kernel<false><<<blocks, 256, 0, stream>>>(dy, x, w, mean, rstd, dx, rows, dim);
-  norm_bwd_wgrad_kernel<<<(dim + 31) / 32, 256, 0, stream>>>(dy, x, mean, rstd, dw, layernorm ? db : nullptr, rows, dim);
+  const int slabs = colsum_slabs(rows);
+  float* part_w = scratch;
+  float* part_b = layernorm ? scratch + static_cast<size_t>(slabs) * dim : nullptr;
+  dim3 grid((dim + 255) / 256, slabs);
+  colsum_partial_kernel<true><<<grid, 256, 0, stream>>>(dy, x, mean, rstd, part_w, part_b, rows, dim);
+  colsum_final_kernel<<<(dim + 255) / 256, 256, 0, stream>>>(part_w, part_b, dw, layernorm ? db : nullptr, slabs, dim);
+  count_launch(3);
+  return cudaGetLastError();
+}
+
+cudaError_t colsum_bf16(const __nv_bfloat16* in, float* out, float* scratch, int rows, int dim, cudaStream_t stream) {
+  if (dim % 8 != 0 || (reinterpret_cast<uintptr_t>(in) & 15u)) return cudaErrorNotSupported;
+  const int slabs = colsum_slabs(rows);
+  dim3 grid((dim + 255) / 256, slabs);
+  colsum_partial_kernel<false><<<grid, 256, 0, stream>>>(in, nullptr, nullptr, nullptr, nullptr, scratch, rows, dim);
+  colsum_final_kernel<<<(dim + 255) / 256, 256, 0, stream>>>(nullptr, scratch, nullptr, out, slabs, dim);
   count_launch(2);
   return cudaGetLastError();
 }

@@ -54,7 +54,10 @@ struct SmemLayout {
 
 __device__ __forceinline__ float gelu_erf(float x) { return 0.5f * x * (1.f + erff(x * 0.70710678f)); }
 
-template <int BN, int STAGES>
+// kAMn / kBMn: the operand is stored with its M (or N) index contiguous, i.e. as a
+// [K, M] (or [K, N]) row-major matrix; the tile is then fetched as 64-wide column
+// groups of BK rows each and described to the tensor core as MN-major.
+template <int BN, int STAGES, bool kAMn, bool kBMn>
 __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
                                                         const __grid_constant__ CUtensorMap tma_b, GemmDev g) {
   using L = SmemLayout<BN, STAGES>;
@@ -97,8 +100,20 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
         if (!ok) break;
         tc::mbar_expect_tx(&full[s], L::kStageBytes);
         uint8_t* a_dst = tiles + s * L::kStageBytes;
-        tc::tma_load_2d(a_dst, &tma_a, &full[s], kb * BK, m_blk * BM);
-        tc::tma_load_2d(a_dst + L::kABytes, &tma_b, &full[s], kb * BK, n_blk * BN);
+        if (kAMn) {
+#pragma unroll
+          for (int gq = 0; gq < BM / 64; ++gq)
+            tc::tma_load_2d(a_dst + gq * (BK * 128), &tma_a, &full[s], m_blk * BM + gq * 64, kb * BK);
+        } else {
+          tc::tma_load_2d(a_dst, &tma_a, &full[s], kb * BK, m_blk * BM);
+        }
+        if (kBMn) {
+#pragma unroll
+          for (int gq = 0; gq < BN / 64; ++gq)
+            tc::tma_load_2d(a_dst + L::kABytes + gq * (BK * 128), &tma_b, &full[s], n_blk * BN + gq * 64, kb * BK);
+        } else {
+          tc::tma_load_2d(a_dst + L::kABytes, &tma_b, &full[s], kb * BK, n_blk * BN);
+        }
         issued = kb + 1;
       }
       if (!ok) {
@@ -111,7 +126,7 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
   } else if (warp == 1) {
     // -------------------------------------------------------- MMA issuer --
     if (lane == 0) {
-      constexpr uint32_t idesc = tc::idesc_bf16(BM, BN);
+      constexpr uint32_t idesc = tc::idesc_bf16(BM, BN, kAMn, kBMn);
       bool ok = true;
       for (int kb = 0; kb < num_kb; ++kb) {
         const int s = kb % STAGES;
@@ -119,13 +134,14 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
         if (!ok) break;
         tc::fence_after_sync();
         const uint8_t* a_tile = tiles + s * L::kStageBytes;
-        const uint64_t da = tc::smem_desc_k_sw128(a_tile);
-        const uint64_t db = tc::smem_desc_k_sw128(a_tile + L::kABytes);
+        const uint64_t da = kAMn ? tc::smem_desc_mn_sw128(a_tile, BK * 128) : tc::smem_desc_k_sw128(a_tile);
+        const uint64_t db = kBMn ? tc::smem_desc_mn_sw128(a_tile + L::kABytes, BK * 128) : tc::smem_desc_k_sw128(a_tile + L::kABytes);
+        // Advancing K by 16 elements: K-major = 32 bytes inside the swizzled row (+2 in the
+        // 16-byte address field); MN-major = 16 rows of 128 bytes (+128).
+        constexpr uint64_t a_step = kAMn ? (16 * 128) >> 4 : 2, b_step = kBMn ? (16 * 128) >> 4 : 2;
 #pragma unroll
-        for (int k4 = 0; k4 < BK / UMMA_K; ++k4) {
-          // advancing K by 16 elements = 32 bytes inside the swizzled row: +2 in the 16-byte address field
-          tc::mma_bf16(tmem_base, da + 2 * k4, db + 2 * k4, idesc, (kb | k4) != 0);
-        }
+        for (int k4 = 0; k4 < BK / UMMA_K; ++k4)
+          tc::mma_bf16(tmem_base, da + a_step * k4, db + b_step * k4, idesc, (kb | k4) != 0);
         tc::mma_commit(&empty[s]);  // frees the stage once these MMAs have read it
       }
       if (!ok) atomicExch(&g_gemm_error, 2);
@@ -206,6 +222,8 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
   }
 }
 
+// K-major operand [rows = M or N, cols = K]: box = 64 (K) x box_rows.
+// MN-major operand [rows = K, cols = M or N]: box = 64 (M/N) x 64 (K).
 bool encode_map(CUtensorMap* map, const void* base, int rows, int cols, int ld_elems, int box_rows) {
   const CuDriver& cu = CuDriver::get();
   if (!cu.loaded || !cu.TensorMapEncodeTiled) return false;
@@ -228,18 +246,20 @@ cudaError_t unsupported(const char* why) {
   return cudaErrorNotSupported;
 }
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, bool kAMn, bool kBMn>
 cudaError_t launch_cfg(const GemmArgs& a, cudaStream_t stream) {
   using L = SmemLayout<BN, STAGES>;
   static bool configured = false;
   if (!configured) {
-    cudaError_t rc = cudaFuncSetAttribute(gemm_bf16_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal);
+    cudaError_t rc = cudaFuncSetAttribute(gemm_bf16_kernel<BN, STAGES, kAMn, kBMn>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          L::kTotal);
     if (rc != cudaSuccess) return rc;
     configured = true;
   }
   CUtensorMap ma, mb;
-  if (!encode_map(&ma, a.a, a.m, a.k, a.lda, BM) || !encode_map(&mb, a.b, a.n, a.k, a.ldb, BN))
-    return unsupported("cuTensorMapEncodeTiled rejected an operand");
+  const bool oka = kAMn ? encode_map(&ma, a.a, a.k, a.m, a.lda, BK) : encode_map(&ma, a.a, a.m, a.k, a.lda, BM);
+  const bool okb = kBMn ? encode_map(&mb, a.b, a.k, a.n, a.ldb, BK) : encode_map(&mb, a.b, a.n, a.k, a.ldb, BN);
+  if (!oka || !okb) return unsupported("cuTensorMapEncodeTiled rejected an operand");
   (void)cudaGetLastError();  // a stale error of an earlier, unrelated call must not be blamed on this launch
   GemmDev g;
   g.d = a.d;
@@ -253,7 +273,7 @@ cudaError_t launch_cfg(const GemmArgs& a, cudaStream_t stream) {
   g.accumulate = a.accumulate ? 1 : 0;
   g.epilogue = a.epilogue;
   dim3 grid((a.n + BN - 1) / BN, (a.m + BM - 1) / BM);
-  gemm_bf16_kernel<BN, STAGES><<<grid, 192, L::kTotal, stream>>>(ma, mb, g);
+  gemm_bf16_kernel<BN, STAGES, kAMn, kBMn><<<grid, 192, L::kTotal, stream>>>(ma, mb, g);
   count_launch();
   return cudaGetLastError();
 }
@@ -274,8 +294,10 @@ cudaError_t gemm_bf16_tn(const GemmArgs& a, cudaStream_t stream) {
   if ((a.epilogue == EPI_BIAS || a.epilogue == EPI_BIAS_GELU) && !a.bias) return cudaErrorInvalidValue;
   if ((a.epilogue == EPI_BIAS_GELU || a.epilogue == EPI_GELU) && (!a.aux || a.d_fp32)) return cudaErrorInvalidValue;
   if (a.accumulate && !a.d_fp32) return cudaErrorInvalidValue;
+  if (a.a_mn_major && a.m % 8 != 0) return unsupported("an MN-major A needs M to be a multiple of 8");
   // 128 x 128 tiles, 3 stages of 32 KB: two CTAs per SM.
-  return launch_cfg<128, 3>(a, stream);
+  if (a.a_mn_major) return a.b_mn_major ? launch_cfg<128, 3, true, true>(a, stream) : launch_cfg<128, 3, true, false>(a, stream);
+  return a.b_mn_major ? launch_cfg<128, 3, false, true>(a, stream) : launch_cfg<128, 3, false, false>(a, stream);
 }
 
 int gemm_error_flag() {

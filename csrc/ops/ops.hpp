@@ -24,9 +24,14 @@ void count_launch(int n = 1);
 // x, y: [rows, dim] bf16; w, b: fp32; mean / rstd: fp32 [rows] saved for backward.
 cudaError_t norm_fwd(const __nv_bfloat16* x, const float* w, const float* b, __nv_bfloat16* y, float* mean, float* rstd,
                      int rows, int dim, float eps, cudaStream_t stream);
-// dx: [rows, dim] bf16; dw, db: fp32 [dim] (overwritten).
+// dx: [rows, dim] bf16; dw, db: fp32 [dim] (overwritten).  scratch: fp32,
+// 2 * colsum_slabs(rows) * dim elements (partial column sums).
 cudaError_t norm_bwd(const __nv_bfloat16* dy, const __nv_bfloat16* x, const float* w, const float* mean, const float* rstd,
-                     __nv_bfloat16* dx, float* dw, float* db, int rows, int dim, bool layernorm, cudaStream_t stream);
+                     __nv_bfloat16* dx, float* dw, float* db, float* scratch, int rows, int dim, bool layernorm,
+                     cudaStream_t stream);
+// out[c] = sum over rows of in[r, c] (bias gradients).  scratch: colsum_slabs(rows) * dim floats.
+cudaError_t colsum_bf16(const __nv_bfloat16* in, float* out, float* scratch, int rows, int dim, cudaStream_t stream);
+int colsum_slabs(int rows);
 
 // ---- fused AdamW over flat fp32 buffers; step is a device scalar (float) so the
 // launch can be replayed from a CUDA graph.  p16 (optional) receives bf16(p).
@@ -54,8 +59,10 @@ enum GemmEpilogue : int {
   EPI_GELU = 3,       // Z = acc (written to aux), D = gelu(Z)
 };
 struct GemmArgs {
-  const __nv_bfloat16* a = nullptr;  // [M, K], row stride lda (elements)
-  const __nv_bfloat16* b = nullptr;  // [N, K], row stride ldb
+  const __nv_bfloat16* a = nullptr;  // [M, K], row stride lda (elements); a_mn_major: stored [K, M]
+  const __nv_bfloat16* b = nullptr;  // [N, K], row stride ldb;            b_mn_major: stored [K, N]
+  bool a_mn_major = false;
+  bool b_mn_major = false;
   void* d = nullptr;                 // [M, N] bf16 or fp32, row stride ldd
   __nv_bfloat16* aux = nullptr;      // [M, N] pre-activation (GELU epilogues)
   const float* bias = nullptr;       // [N]

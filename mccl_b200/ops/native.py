@@ -17,11 +17,6 @@ def _bf16_weight(weight: torch.Tensor) -> torch.Tensor:
     return _C.cast_bf16(weight.detach().contiguous())
 
 
-def _bf16_weight_t(weight: torch.Tensor, w16: torch.Tensor) -> torch.Tensor:
-    wt = getattr(weight, "_bf16_t", None)
-    return wt if wt is not None else _C.transpose_bf16(w16)
-
-
 def _gemm_ok(m: int, n: int, k: int) -> bool:
     return k % 64 == 0 and n % 8 == 0 and m > 0
 
@@ -61,17 +56,19 @@ class LinearFn(torch.autograd.Function):
         dx = dw = db = None
         if ctx.needs_input_grad[0]:
             if _gemm_ok(M, K, N):
-                dx, _ = _C.gemm_bf16(dz, _bf16_weight_t(weight, w16))
+                # dx[M,K] = dz[M,N] · W[N,K]: W is the B operand stored [contraction, K], read MN-major
+                dx, _ = _C.gemm_bf16(dz, w16, None, "none", False, None, False, False, True)
             else:
                 dx = dz @ w16
             dx = dx.view(*dy.shape[:-1], K)
         if ctx.needs_input_grad[1]:
-            if _gemm_ok(N, K, M):
-                dw, _ = _C.gemm_bf16(_C.transpose_bf16(dz), _C.transpose_bf16(x2), None, "none", True)
+            if _gemm_ok(N, K, M) and N % 8 == 0:
+                # dW[N,K] = dz^T · x: both operands stored [tokens, features], read MN-major
+                dw, _ = _C.gemm_bf16(dz, x2, None, "none", True, None, False, True, True)
             else:
                 dw = (dz.t() @ x2).float()
         if ctx.has_bias and ctx.needs_input_grad[2]:
-            db = dz.sum(0, dtype=torch.float32)
+            db = _C.colsum_bf16(dz) if N % 8 == 0 else dz.sum(0, dtype=torch.float32)
         return dx, dw, db, None
 
 
@@ -123,12 +120,12 @@ class LinearCrossEntropyFn(torch.autograd.Function):
         dh = dw = None
         if ctx.needs_input_grad[0]:
             if _gemm_ok(T, D, V):
-                dh, _ = _C.gemm_bf16(dlogits, _bf16_weight_t(weight, w16))
+                dh, _ = _C.gemm_bf16(dlogits, w16, None, "none", False, None, False, False, True)
             else:
                 dh = dlogits @ w16
         if ctx.needs_input_grad[1]:
-            if _gemm_ok(V, D, T):
-                dw, _ = _C.gemm_bf16(_C.transpose_bf16(dlogits), _C.transpose_bf16(h), None, "none", True)
+            if _gemm_ok(V, D, T) and V % 8 == 0:
+                dw, _ = _C.gemm_bf16(dlogits, h, None, "none", True, None, False, True, True)
             else:
                 dw = (dlogits.t() @ h).float()
         return dh, dw, None

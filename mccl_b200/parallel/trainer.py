@@ -109,28 +109,18 @@ class DDPTrainer:
             self._param_bucket[p] = bi
             if self.world > 1:
                 p.register_post_accumulate_grad_hook(self._on_grad_ready)
-        # bf16 working copies of the parameters (refreshed by the optimizer kernel) and
-        # transposed copies of the matrices (the backward GEMMs want K contiguous).
+        # bf16 working copies of the parameters, refreshed by the optimizer kernel (the GEMMs
+        # read them in either orientation, so no transposed copies are kept).
         self.flat_p16 = None
-        self._transposed = []
         if self.device.type == "cuda" and ops.native_ops_available().get("adamw_flat"):
             self.flat_p16 = _C.cast_bf16(self.flat_p)
             for p, off in zip(order, offsets):
                 p._bf16 = self.flat_p16[off:off + p.numel()].view_as(p)
-                if p.dim() == 2 and p.shape[0] % 8 == 0 and p.shape[1] % 8 == 0 and not isinstance(p, torch.nn.UninitializedParameter):
-                    p._bf16_t = torch.empty(p.shape[1], p.shape[0], device=self.device, dtype=torch.bfloat16)
-                    self._transposed.append(p)
-            self._refresh_transposes()
-
-    def _refresh_transposes(self) -> None:
-        for p in self._transposed:
-            _C.transpose_bf16_out(p._bf16, p._bf16_t)
 
     def _sync_initial_params(self, group) -> None:
         dist.broadcast(self.flat_p, src=dist.get_global_rank(group, 0) if group is not None else 0, group=group)
         if self.flat_p16 is not None:
             _C.cast_bf16(self.flat_p, self.flat_p16)
-            self._refresh_transposes()
         torch.cuda.synchronize(self.device)
 
     # ------------------------------------------------------- communication --
@@ -164,8 +154,6 @@ class DDPTrainer:
         self.step_t.add_(1.0)
         ops.adamw_step(self.flat_p, self.flat_g, self.m, self.v, self.lr, self.betas[0], self.betas[1], self.eps,
                        self.wd, self.step_t, p_bf16=self.flat_p16)
-        if self.flat_p16 is not None:
-            self._refresh_transposes()
         return loss.detach()
 
     def _capture(self, tokens: torch.Tensor, targets: torch.Tensor) -> None:

@@ -37,6 +37,23 @@ def test_gemm_matches_fp32_reference(M, N, K):
     assert C.gemm_error_flag() == 0
 
 
+@pytest.mark.parametrize("a_t,b_t", [(True, False), (False, True), (True, True)])
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (512, 384, 256), (2048, 512, 4096), (200, 72, 128)])
+def test_gemm_mn_major_operands(a_t, b_t, M, N, K):
+    """Operands stored [K, M] / [K, N] are read MN-major: same product, no transposed copy."""
+    C = _C()
+    torch.manual_seed(M * 3 + N * 5 + K)
+    a = torch.randn(M, K, device="cuda").bfloat16()
+    b = torch.randn(N, K, device="cuda").bfloat16()
+    ref = a.float() @ b.float().t()
+    aa = a.t().contiguous() if a_t else a
+    bb = b.t().contiguous() if b_t else b
+    d, _ = C.gemm_bf16(aa, bb, None, "none", True, None, False, a_t, b_t)
+    torch.cuda.synchronize()
+    assert C.gemm_error_flag() == 0
+    assert _rel(d, ref) < 1e-5 * max(1, K // 64), (_rel(d, ref), a_t, b_t)
+
+
 def test_gemm_epilogues_and_strides():
     C = _C()
     torch.manual_seed(1)
@@ -125,6 +142,8 @@ def test_cross_entropy_forward_backward(T, V):
 
 def test_transpose_cast_gelu_bwd():
     C = _C()
+    cs = torch.randn(1000, 520, device="cuda").bfloat16()
+    assert _rel(C.colsum_bf16(cs), cs.float().sum(0)) < 1e-5
     x = torch.randn(300, 520, device="cuda").bfloat16()
     assert torch.equal(C.transpose_bf16(x), x.t().contiguous())
     f = torch.randn(1001, device="cuda")[1:].contiguous() if False else torch.randn(1004, device="cuda")
