@@ -52,7 +52,8 @@ void bind_ops(py::module_& m) {
   m.def(
       "gemm_bf16",
       [](const at::Tensor& a, const at::Tensor& b, const c10::optional<at::Tensor>& bias, const std::string& epilogue,
-         bool out_fp32, const c10::optional<at::Tensor>& out, bool accumulate, bool a_t, bool b_t) {
+         bool out_fp32, const c10::optional<at::Tensor>& out, bool accumulate, bool a_t, bool b_t,
+         const c10::optional<at::Tensor>& residual) {
         need_cuda(a, "gemm(a)");
         need_cuda(b, "gemm(b)");
         MCCL_CHECK_TENSOR(a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16, "gemm: operands must be bf16");
@@ -99,6 +100,11 @@ void bind_ops(py::module_& m) {
           aux = at::empty({M, N}, a.options());
           g.aux = bf(aux);
         }
+        if (residual.has_value() && residual->defined()) {
+          need(*residual, at::kBFloat16, "gemm(residual)");
+          MCCL_CHECK_TENSOR(residual->numel() == M * N && d.is_contiguous(), "gemm: residual must be a contiguous [M, N] tensor");
+          g.residual = bf(*residual);
+        }
         cudaError_t rc = ops::gemm_bf16_tn(g, stream_of(a));
         MCCL_CHECK_T(rc == cudaSuccess, CudaError,
                      "gemm_bf16 [" << M << "x" << N << "x" << K << ", lda " << g.lda << ", ldb " << g.ldb << ", ldd " << g.ldd
@@ -106,7 +112,8 @@ void bind_ops(py::module_& m) {
         return std::make_pair(d, aux.defined() ? c10::optional<at::Tensor>(aux) : c10::nullopt);
       },
       py::arg("a"), py::arg("b"), py::arg("bias") = py::none(), py::arg("epilogue") = "none", py::arg("out_fp32") = false,
-      py::arg("out") = py::none(), py::arg("accumulate") = false, py::arg("a_t") = false, py::arg("b_t") = false);
+      py::arg("out") = py::none(), py::arg("accumulate") = false, py::arg("a_t") = false, py::arg("b_t") = false,
+      py::arg("residual") = py::none());
 
   m.def(
       "norm_fwd",
@@ -134,7 +141,7 @@ void bind_ops(py::module_& m) {
   m.def(
       "norm_bwd",
       [](const at::Tensor& dy, const at::Tensor& x, const at::Tensor& w, const at::Tensor& mean, const at::Tensor& rstd,
-         bool layernorm) {
+         bool layernorm, const c10::optional<at::Tensor>& dw_out, const c10::optional<at::Tensor>& db_out) {
         need(dy, at::kBFloat16, "norm_bwd(dy)");
         need(x, at::kBFloat16, "norm_bwd(x)");
         need(w, at::kFloat, "norm_bwd(weight)");
@@ -143,8 +150,12 @@ void bind_ops(py::module_& m) {
         c10::cuda::CUDAGuard guard(x.device());
         const int64_t dim = x.size(-1), rows = x.numel() / dim;
         at::Tensor dx = at::empty_like(x);
-        at::Tensor dw = at::empty({dim}, x.options().dtype(at::kFloat));
-        at::Tensor db = layernorm ? at::empty({dim}, x.options().dtype(at::kFloat)) : at::Tensor();
+        // dw_out / db_out: write the parameter gradients straight into these fp32 buffers
+        at::Tensor dw = dw_out.has_value() ? *dw_out : at::empty({dim}, x.options().dtype(at::kFloat));
+        at::Tensor db = !layernorm ? at::Tensor() : (db_out.has_value() ? *db_out : at::empty({dim}, x.options().dtype(at::kFloat)));
+        need(dw, at::kFloat, "norm_bwd(dw)");
+        if (layernorm) need(db, at::kFloat, "norm_bwd(db)");
+        MCCL_CHECK_TENSOR(dw.numel() == dim && (!layernorm || db.numel() == dim), "norm_bwd: gradient buffers must have `dim` elements");
         at::Tensor scratch = at::empty({2 * ops::colsum_slabs(static_cast<int>(rows)) * dim}, x.options().dtype(at::kFloat));
         check_launch(ops::norm_bwd(bf(dy), bf(x), w.data_ptr<float>(), mean.data_ptr<float>(), rstd.data_ptr<float>(), bf(dx),
                                    dw.data_ptr<float>(), layernorm ? db.data_ptr<float>() : nullptr, scratch.data_ptr<float>(),
@@ -152,7 +163,9 @@ void bind_ops(py::module_& m) {
                                    static_cast<int>(dim), layernorm, stream_of(x)),
                      "norm_bwd");
         return std::make_tuple(dx, dw, db.defined() ? c10::optional<at::Tensor>(db) : c10::nullopt);
-      });
+      },
+      py::arg("dy"), py::arg("x"), py::arg("weight"), py::arg("mean"), py::arg("rstd"), py::arg("layernorm"),
+      py::arg("dw_out") = py::none(), py::arg("db_out") = py::none());
 
   m.def(
       "adamw_flat",
@@ -199,16 +212,18 @@ void bind_ops(py::module_& m) {
       py::arg("logits"), py::arg("targets"), py::arg("grad_scale") = 1.0,
       "Returns per-row losses; overwrites logits with (softmax - onehot) * grad_scale.");
 
-  m.def("colsum_bf16", [](const at::Tensor& x) {
+  m.def("colsum_bf16", [](const at::Tensor& x, const c10::optional<at::Tensor>& out_opt) {
     need(x, at::kBFloat16, "colsum(x)");
     MCCL_CHECK_TENSOR(x.dim() == 2, "colsum: 2-D tensor expected");
     c10::cuda::CUDAGuard guard(x.device());
     const int rows = static_cast<int>(x.size(0)), dim = static_cast<int>(x.size(1));
-    at::Tensor out = at::empty({dim}, x.options().dtype(at::kFloat));
+    at::Tensor out = out_opt.has_value() ? *out_opt : at::empty({dim}, x.options().dtype(at::kFloat));
+    need(out, at::kFloat, "colsum(out)");
+    MCCL_CHECK_TENSOR(out.numel() == dim, "colsum: output must have one element per column");
     at::Tensor scratch = at::empty({ops::colsum_slabs(rows) * dim}, x.options().dtype(at::kFloat));
     check_launch(ops::colsum_bf16(bf(x), out.data_ptr<float>(), scratch.data_ptr<float>(), rows, dim, stream_of(x)), "colsum");
     return out;
-  });
+  }, py::arg("x"), py::arg("out") = py::none());
   m.def("transpose_bf16", [](const at::Tensor& x) {
     need(x, at::kBFloat16, "transpose(x)");
     MCCL_CHECK_TENSOR(x.dim() == 2, "transpose: 2-D tensor expected");

@@ -186,17 +186,33 @@ __global__ void __launch_bounds__(256) colsum_partial_kernel(const __nv_bfloat16
   }
 }
 
+// 32 columns x 8 slab lanes per block: thread (c, l) adds slabs l, l+8, ... of column c,
+// then the 8 lanes are combined in a fixed order.
 __global__ void __launch_bounds__(256) colsum_final_kernel(const float* __restrict__ part_w, const float* __restrict__ part_b,
                                                            float* __restrict__ dw, float* __restrict__ db, int slabs, int dim) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= dim) return;
+  __shared__ float sw[8][33], sb[8][33];
+  const int cx = threadIdx.x & 31, ly = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + cx;
   float tw = 0.f, tb = 0.f;
-  for (int s = 0; s < slabs; ++s) {
-    if (part_w) tw += part_w[static_cast<size_t>(s) * dim + c];
-    if (part_b) tb += part_b[static_cast<size_t>(s) * dim + c];
+  if (c < dim) {
+    for (int s = ly; s < slabs; s += 8) {
+      if (part_w) tw += part_w[static_cast<size_t>(s) * dim + c];
+      if (part_b) tb += part_b[static_cast<size_t>(s) * dim + c];
+    }
   }
-  if (dw) dw[c] = tw;
-  if (db) db[c] = tb;
+  sw[ly][cx] = tw;
+  sb[ly][cx] = tb;
+  __syncthreads();
+  if (ly == 0 && c < dim) {
+    float aw = 0.f, ab = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      aw += sw[k][cx];
+      ab += sb[k][cx];
+    }
+    if (dw) dw[c] = aw;
+    if (db) db[c] = ab;
+  }
 }
 
 int colsum_slabs(int rows) { return (rows + kSlabRows - 1) / kSlabRows; }
@@ -223,7 +239,7 @@ cudaError_t norm_bwd(const __nv_bfloat16* dy, const __nv_bfloat16* x, const floa
   float* part_b = layernorm ? scratch + static_cast<size_t>(slabs) * dim : nullptr;
   dim3 grid((dim + 255) / 256, slabs);
   colsum_partial_kernel<true><<<grid, 256, 0, stream>>>(dy, x, mean, rstd, part_w, part_b, rows, dim);
-  colsum_final_kernel<<<(dim + 255) / 256, 256, 0, stream>>>(part_w, part_b, dw, layernorm ? db : nullptr, slabs, dim);
+  colsum_final_kernel<<<(dim + 31) / 32, 256, 0, stream>>>(part_w, part_b, dw, layernorm ? db : nullptr, slabs, dim);
   count_launch(3);
   return cudaGetLastError();
 }
@@ -233,7 +249,7 @@ cudaError_t colsum_bf16(const __nv_bfloat16* in, float* out, float* scratch, int
   const int slabs = colsum_slabs(rows);
   dim3 grid((dim + 255) / 256, slabs);
   colsum_partial_kernel<false><<<grid, 256, 0, stream>>>(in, nullptr, nullptr, nullptr, nullptr, scratch, rows, dim);
-  colsum_final_kernel<<<(dim + 255) / 256, 256, 0, stream>>>(nullptr, scratch, nullptr, out, slabs, dim);
+  colsum_final_kernel<<<(dim + 31) / 32, 256, 0, stream>>>(nullptr, scratch, nullptr, out, slabs, dim);
   count_launch(2);
   return cudaGetLastError();
 }

@@ -35,6 +35,7 @@ struct GemmDev {
   void* d;
   __nv_bfloat16* aux;
   const float* bias;
+  const __nv_bfloat16* residual;
   int m, n, k;
   int ldd;
   int d_fp32;
@@ -186,6 +187,22 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = gelu_erf(v[j]);
       }
+      if (g.residual) {
+        const __nv_bfloat16* rrow = g.residual + static_cast<size_t>(row) * g.ldd + col0;
+#pragma unroll
+        for (int j8 = 0; j8 < 4; ++j8) {
+          if (j8 * 8 < ncols) {
+            const uint4 pk = *reinterpret_cast<const uint4*>(rrow + j8 * 8);
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&pk);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const float2 t = __bfloat1622float2(h[i]);
+              v[j8 * 8 + 2 * i] += t.x;
+              v[j8 * 8 + 2 * i + 1] += t.y;
+            }
+          }
+        }
+      }
       if (g.d_fp32) {
         float* drow = static_cast<float*>(g.d) + static_cast<size_t>(row) * g.ldd + col0;
 #pragma unroll
@@ -265,6 +282,7 @@ cudaError_t launch_cfg(const GemmArgs& a, cudaStream_t stream) {
   g.d = a.d;
   g.aux = a.aux;
   g.bias = a.bias;
+  g.residual = a.residual;
   g.m = a.m;
   g.n = a.n;
   g.k = a.k;
@@ -294,6 +312,7 @@ cudaError_t gemm_bf16_tn(const GemmArgs& a, cudaStream_t stream) {
   if ((a.epilogue == EPI_BIAS || a.epilogue == EPI_BIAS_GELU) && !a.bias) return cudaErrorInvalidValue;
   if ((a.epilogue == EPI_BIAS_GELU || a.epilogue == EPI_GELU) && (!a.aux || a.d_fp32)) return cudaErrorInvalidValue;
   if (a.accumulate && !a.d_fp32) return cudaErrorInvalidValue;
+  if (a.residual && (reinterpret_cast<uintptr_t>(a.residual) & 15u)) return unsupported("residual pointer must be 16-byte aligned");
   if (a.a_mn_major && a.m % 8 != 0) return unsupported("an MN-major A needs M to be a multiple of 8");
   // 128 x 128 tiles, 3 stages of 32 KB: two CTAs per SM.
   if (a.a_mn_major) return a.b_mn_major ? launch_cfg<128, 3, true, true>(a, stream) : launch_cfg<128, 3, true, false>(a, stream);

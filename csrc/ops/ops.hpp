@@ -66,6 +66,7 @@ struct GemmArgs {
   void* d = nullptr;                 // [M, N] bf16 or fp32, row stride ldd
   __nv_bfloat16* aux = nullptr;      // [M, N] pre-activation (GELU epilogues)
   const float* bias = nullptr;       // [N]
+  const __nv_bfloat16* residual = nullptr;  // [M, N] added after bias / activation, row stride ldd
   int m = 0, n = 0, k = 0;
   int lda = 0, ldb = 0, ldd = 0;
   bool d_fp32 = false;

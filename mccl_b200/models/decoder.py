@@ -102,12 +102,13 @@ class Linear(nn.Module):
         self.weight = nn.Parameter(torch.empty(d_out, d_in).normal_(0.0, std))
         self.bias = nn.Parameter(torch.zeros(d_out)) if bias else None
 
-    def forward(self, x: torch.Tensor, native: bool, act: str = "none") -> torch.Tensor:
+    def forward(self, x: torch.Tensor, native: bool, act: str = "none", residual=None) -> torch.Tensor:
         if native:
             from .. import ops
-            return ops.linear(x, self.weight, self.bias, act)
+            return ops.linear(x, self.weight, self.bias, act, residual)
         y = F.linear(x, self.weight.to(x.dtype), None if self.bias is None else self.bias.to(x.dtype))
-        return F.gelu(y) if act == "gelu" else y
+        y = F.gelu(y) if act == "gelu" else y
+        return y if residual is None else y + residual
 
 
 class Block(nn.Module):
@@ -136,14 +137,14 @@ class Block(nn.Module):
         if rope is not None:
             q, k = apply_rope(q, *rope), apply_rope(k, *rope)
         a = F.scaled_dot_product_attention(q, k, v, is_causal=True)
-        x = x + self.proj(a.transpose(1, 2).reshape(B, S, D), native)
+        x = self.proj(a.transpose(1, 2).reshape(B, S, D), native, residual=x)
         h = self.ln2(x, native)
         if cfg.act == "swiglu":
             g, u = self.gate_up(h, native).chunk(2, dim=-1)
             h = F.silu(g) * u
         else:
             h = self.up(h, native, act="gelu")
-        return x + self.down(h, native)
+        return self.down(h, native, residual=x)
 
 
 class Decoder(nn.Module):
@@ -159,6 +160,9 @@ class Decoder(nn.Module):
         self.blocks = nn.ModuleList(Block(cfg) for _ in range(cfg.n_layers))
         self.ln_f = Norm(cfg)
         self.head = None if cfg.tied else Linear(cfg.d_model, cfg.vocab, False, 0.02)
+        if cfg.tied:
+            # the embedding lookup contributes to this gradient through autograd as well
+            self.tok.weight._shared_grad = True
 
     def _native(self, x: torch.Tensor) -> bool:
         if self.native is not None:

@@ -31,12 +31,14 @@ def norm(x: torch.Tensor, weight: torch.Tensor, bias, eps: float) -> torch.Tenso
     return (v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps) * weight).to(x.dtype)
 
 
-def linear(x: torch.Tensor, weight: torch.Tensor, bias=None, act: str = "none") -> torch.Tensor:
+def linear(x: torch.Tensor, weight: torch.Tensor, bias=None, act: str = "none", residual=None) -> torch.Tensor:
+    """act(x @ W^T + b) + residual, in one kernel on CUDA."""
     if x.is_cuda and _HAS["gemm_bf16"]:
         from .native import LinearFn
-        return LinearFn.apply(x, weight, bias, act)
+        return LinearFn.apply(x, weight, bias, act, residual)
     y = F.linear(x, weight.to(x.dtype), None if bias is None else bias.to(x.dtype))
-    return F.gelu(y) if act == "gelu" else y
+    y = F.gelu(y) if act == "gelu" else y
+    return y if residual is None else y + residual
 
 
 def linear_cross_entropy(h: torch.Tensor, weight: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:

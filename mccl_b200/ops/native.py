@@ -17,6 +17,22 @@ def _bf16_weight(weight: torch.Tensor) -> torch.Tensor:
     return _C.cast_bf16(weight.detach().contiguous())
 
 
+def _sink(p: torch.Tensor):
+    """fp32 buffer a trainer wants this parameter's gradient written into (or None)."""
+    return getattr(p, "_grad_sink", None)
+
+
+def _notify(p: torch.Tensor) -> None:
+    """Tells the trainer that p's gradient is complete (it was written in place, so autograd's
+    own accumulation hook will not fire).  Parameters whose gradient has further contributions
+    from autograd (tied embeddings) are marked `_shared_grad` and notified by autograd instead."""
+    if getattr(p, "_shared_grad", False):
+        return
+    cb = getattr(p, "_grad_ready", None)
+    if cb is not None:
+        cb()
+
+
 def _gemm_ok(m: int, n: int, k: int) -> bool:
     return k % 64 == 0 and n % 8 == 0 and m > 0
 
@@ -25,7 +41,7 @@ class LinearFn(torch.autograd.Function):
     """y = act(x @ W^T + b); W [N, K] fp32 master, x [..., K] bf16."""
 
     @staticmethod
-    def forward(ctx, x, weight, bias, act):
+    def forward(ctx, x, weight, bias, act, residual=None):
         K, N = weight.shape[1], weight.shape[0]
         x2 = x.reshape(-1, K)
         if not x2.is_contiguous():
@@ -33,14 +49,22 @@ class LinearFn(torch.autograd.Function):
         M = x2.shape[0]
         w16 = _bf16_weight(weight)
         ctx.act, ctx.has_bias, ctx.native = act, bias is not None, _gemm_ok(M, N, K)
+        res2 = None
+        if residual is not None:
+            res2 = residual.reshape(-1, N)
+            if not res2.is_contiguous():
+                res2 = res2.contiguous()
+        ctx.has_residual = residual is not None
         if ctx.native:
-            y, z = _C.gemm_bf16(x2, w16, bias, act)
+            y, z = _C.gemm_bf16(x2, w16, bias, act, False, None, False, False, False, res2)
         else:
             z = F.linear(x2, w16, None if bias is None else bias.to(x2.dtype))
             y = F.gelu(z) if act == "gelu" else z
             z = z if act == "gelu" else None
+            if res2 is not None:
+                y = y + res2
         ctx.save_for_backward(x2, w16, z if z is not None else x2.new_empty(0))
-        ctx.weight = weight
+        ctx.weight, ctx.bias = weight, bias
         return y.view(*x.shape[:-1], N)
 
     @staticmethod
@@ -62,14 +86,28 @@ class LinearFn(torch.autograd.Function):
                 dx = dz @ w16
             dx = dx.view(*dy.shape[:-1], K)
         if ctx.needs_input_grad[1]:
+            sink = _sink(weight)
             if _gemm_ok(N, K, M) and N % 8 == 0:
                 # dW[N,K] = dz^T · x: both operands stored [tokens, features], read MN-major
-                dw, _ = _C.gemm_bf16(dz, x2, None, "none", True, None, False, True, True)
+                if sink is not None:
+                    _C.gemm_bf16(dz, x2, None, "none", True, sink, True, True, True)
+                    _notify(weight)
+                else:
+                    dw, _ = _C.gemm_bf16(dz, x2, None, "none", True, None, False, True, True)
             else:
                 dw = (dz.t() @ x2).float()
         if ctx.has_bias and ctx.needs_input_grad[2]:
-            db = _C.colsum_bf16(dz) if N % 8 == 0 else dz.sum(0, dtype=torch.float32)
-        return dx, dw, db, None
+            bsink = _sink(ctx.bias)
+            if N % 8 == 0:
+                if bsink is not None:
+                    _C.colsum_bf16(dz, bsink)
+                    _notify(ctx.bias)
+                else:
+                    db = _C.colsum_bf16(dz)
+            else:
+                db = dz.sum(0, dtype=torch.float32)
+        dres = dy if ctx.has_residual else None
+        return dx, dw, db, None, dres
 
 
 class NormFn(torch.autograd.Function):
@@ -81,12 +119,21 @@ class NormFn(torch.autograd.Function):
         y, mean, rstd = _C.norm_fwd(xc, weight, bias, eps)
         ctx.save_for_backward(xc, weight, mean, rstd)
         ctx.layernorm = bias is not None
+        ctx.weight, ctx.bias = weight, bias
         return y
 
     @staticmethod
     def backward(ctx, dy):
         x, weight, mean, rstd = ctx.saved_tensors
         dyc = dy if dy.is_contiguous() else dy.contiguous()
+        wsink, bsink = _sink(ctx.weight), (_sink(ctx.bias) if ctx.bias is not None else None)
+        if wsink is not None and (not ctx.layernorm or bsink is not None):
+            # single use per step: the sinks were zeroed at the start of the step
+            dx, _, _ = _C.norm_bwd(dyc, x, weight, mean, rstd, ctx.layernorm, wsink, bsink)
+            _notify(ctx.weight)
+            if ctx.bias is not None:
+                _notify(ctx.bias)
+            return dx, None, None, None
         dx, dw, db = _C.norm_bwd(dyc, x, weight, mean, rstd, ctx.layernorm)
         return dx, dw, db, None
 
@@ -124,8 +171,13 @@ class LinearCrossEntropyFn(torch.autograd.Function):
             else:
                 dh = dlogits @ w16
         if ctx.needs_input_grad[1]:
+            sink = _sink(weight)
             if _gemm_ok(V, D, T) and V % 8 == 0:
-                dw, _ = _C.gemm_bf16(dlogits, h, None, "none", True, None, False, True, True)
+                if sink is not None:
+                    _C.gemm_bf16(dlogits, h, None, "none", True, sink, True, True, True)
+                    _notify(weight)
+                else:
+                    dw, _ = _C.gemm_bf16(dlogits, h, None, "none", True, None, False, True, True)
             else:
                 dw = (dlogits.t() @ h).float()
         return dh, dw, None

@@ -107,7 +107,11 @@ class DDPTrainer:
             p.data = view
             p.grad = self.flat_g[off:off + p.numel()].view_as(p)
             self._param_bucket[p] = bi
+            # native operators write gradients straight into the flat buffer ...
+            p._grad_sink = p.grad
             if self.world > 1:
+                # ... and say so; gradients that come back through autograd fire its hook instead
+                p._grad_ready = (lambda q=p: self._on_grad_ready(q))
                 p.register_post_accumulate_grad_hook(self._on_grad_ready)
         # bf16 working copies of the parameters, refreshed by the optimizer kernel (the GEMMs
         # read them in either orientation, so no transposed copies are kept).
