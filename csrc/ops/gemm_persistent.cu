@@ -1,0 +1,299 @@
+// Persistent bf16 GEMM for sm_100a: one CTA per SM walks a list of 128 x BN
+// output tiles.  The accumulator is double-buffered in tensor memory, so the
+// epilogue of tile i (tcgen05.ld, bias / activation, stores) runs while the
+// tensor cores already work on tile i+1, and the barrier / TMEM set-up cost is
+// paid once per SM instead of once per tile.
+//
+//   warp 0      TMA producer (one thread): A / B k-blocks into a ring of stages
+//   warp 1      TMEM owner and tcgen05.mma issuer (one thread)
+//   warps 2-5   epilogue, one TMEM lane quarter each
+//
+// The same kernel carries the tensor-parallel fusions (see tp_gemm.cu):
+//   all-gather → GEMM   the A operand arrives in row chunks; the producer waits
+//                       for a chunk's flag before it loads tiles of that chunk
+//   GEMM → reduce-scatter  output row chunks belong to different ranks; the
+//                       epilogue stores each tile into its owner's staging slot
+// Tiles are visited chunk by chunk starting with this rank's own chunk, so
+// compute on data that is already local overlaps the NVLink transfers.
+#include "gemm_common.cuh"
+#include "gemm_persistent.cuh"
+
+namespace mccl {
+namespace ops {
+
+namespace {
+
+template <int BN, int STAGES>
+struct PLayout {
+  static constexpr int kABytes = BM * BK * 2;
+  static constexpr int kBBytes = BN * BK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kTiles = STAGES * kStageBytes;
+  static constexpr int kBarriers = (2 * STAGES + 4) * 8 + 16;
+  static constexpr int kTotal = kTiles + kBarriers + 1024;
+};
+
+// Bounded wait that also gives up when another role of this CTA has failed.
+__device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  for (uint32_t i = 0; i < (1u << 22); ++i) {
+    if (tc::mbar_try_wait(bar, parity)) return true;
+    if ((i & 255u) == 255u && *abort_flag) return false;
+  }
+  return false;
+}
+
+// Spin on a flag word in global memory written by another CTA of this GPU (chunk
+// arrival in the all-gather fusion).  Bounded; false on timeout.
+__device__ __forceinline__ bool wait_flag_geq(const uint32_t* flag, uint32_t value, volatile int* abort_flag) {
+  for (uint32_t i = 0; i < (1u << 24); ++i) {
+    uint32_t v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+    if (static_cast<int32_t>(v - value) >= 0) return true;
+    if ((i & 255u) == 255u && *abort_flag) return false;
+    __nanosleep(64);
+  }
+  return false;
+}
+
+template <int BN, int STAGES, bool kAMn, bool kBMn>
+__global__ void __launch_bounds__(192, 1) gemm_persistent_kernel(const __grid_constant__ CUtensorMap tma_a,
+                                                                 const __grid_constant__ CUtensorMap tma_b, GemmDev g,
+                                                                 FusedDev f) {
+  using L = PLayout<BN, STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint8_t* tiles = smem;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + L::kTiles);
+  uint64_t* empty = full + STAGES;
+  uint64_t* acc_full = empty + STAGES;   // [2]
+  uint64_t* acc_empty = acc_full + 2;    // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m_tiles = (g.m + BM - 1) / BM, n_tiles = (g.n + BN - 1) / BN;
+  const int total_tiles = m_tiles * n_tiles;
+  const int num_kb = g.k / BK;
+  // Row-chunk rotation: tile order starts at this rank's own chunk (fusions only).
+  const int m_rot = f.mode != FUSE_NONE ? (f.rank * (f.chunk_rows / BM)) % m_tiles : 0;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      tc::mbar_init(&full[s], 1);
+      tc::mbar_init(&empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      tc::mbar_init(&acc_full[b], 1);
+      tc::mbar_init(&acc_empty[b], 4);
+    }
+    *abort_flag = 0;
+    tc::mbar_init_fence();
+    tc::tma_prefetch_desc(&tma_a);
+    tc::tma_prefetch_desc(&tma_b);
+  }
+  if (warp == 1) tc::tmem_alloc(tmem_slot, 2 * BN);
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  auto tile_coords = [&](int t, int& m_blk, int& n_blk) {
+    n_blk = t % n_tiles;
+    m_blk = (t / n_tiles + m_rot) % m_tiles;
+  };
+
+  if (warp == 0) {
+    // ------------------------------------------------------ TMA producer --
+    if (lane == 0) {
+      bool ok = true;
+      uint32_t it = 0;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        int m_blk, n_blk;
+        tile_coords(t, m_blk, n_blk);
+        if (f.mode == FUSE_ALLGATHER_A) {
+          const int chunk = (m_blk * BM) / f.chunk_rows;
+          if (chunk != f.rank) ok = wait_flag_geq(f.chunk_flags + chunk, f.epoch, abort_flag);
+          if (!ok) break;
+        }
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          if (it >= STAGES) ok = wait_or_abort(&empty[s], ((it / STAGES) - 1) & 1, abort_flag);
+          if (!ok) break;
+          tc::mbar_expect_tx(&full[s], L::kStageBytes);
+          uint8_t* a_dst = tiles + s * L::kStageBytes;
+          if (kAMn) {
+#pragma unroll
+            for (int gq = 0; gq < BM / 64; ++gq)
+              tc::tma_load_2d(a_dst + gq * (BK * 128), &tma_a, &full[s], m_blk * BM + gq * 64, kb * BK);
+          } else {
+            tc::tma_load_2d(a_dst, &tma_a, &full[s], kb * BK, m_blk * BM);
+          }
+          if (kBMn) {
+#pragma unroll
+            for (int gq = 0; gq < BN / 64; ++gq)
+              tc::tma_load_2d(a_dst + L::kABytes + gq * (BK * 128), &tma_b, &full[s], n_blk * BN + gq * 64, kb * BK);
+          } else {
+            tc::tma_load_2d(a_dst + L::kABytes, &tma_b, &full[s], kb * BK, n_blk * BN);
+          }
+        }
+      }
+      if (!ok) {
+        *abort_flag = 1;
+        atomicExch(g.err, 1);
+        // copies already issued must land before the CTA retires
+        const uint32_t first = it > STAGES ? it - STAGES : 0;
+        for (uint32_t j = first; j < it; ++j) tc::mbar_wait(&full[j % STAGES], (j / STAGES) & 1, 1u << 20);
+      }
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------- MMA issuer --
+    if (lane == 0) {
+      constexpr uint32_t idesc = tc::idesc_bf16(BM, BN, kAMn, kBMn);
+      constexpr uint64_t a_step = kAMn ? (16 * 128) >> 4 : 2, b_step = kBMn ? (16 * 128) >> 4 : 2;
+      bool ok = true;
+      uint32_t it = 0;
+      int i = 0;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++i) {
+        const int buf = i & 1;
+        if (i >= 2) {
+          ok = wait_or_abort(&acc_empty[buf], ((i >> 1) - 1) & 1, abort_flag);
+          if (!ok) break;
+          tc::fence_after_sync();
+        }
+        const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(buf * BN);
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          ok = wait_or_abort(&full[s], (it / STAGES) & 1, abort_flag);
+          if (!ok) break;
+          tc::fence_after_sync();
+          const uint8_t* a_tile = tiles + s * L::kStageBytes;
+          const uint64_t da = kAMn ? tc::smem_desc_mn_sw128(a_tile, BK * 128) : tc::smem_desc_k_sw128(a_tile);
+          const uint64_t db = kBMn ? tc::smem_desc_mn_sw128(a_tile + L::kABytes, BK * 128) : tc::smem_desc_k_sw128(a_tile + L::kABytes);
+#pragma unroll
+          for (int k4 = 0; k4 < BK / UMMA_K; ++k4)
+            tc::mma_bf16(tmem_d, da + a_step * k4, db + b_step * k4, idesc, (kb | k4) != 0);
+          tc::mma_commit(&empty[s]);
+        }
+        if (!ok) break;
+        tc::mma_commit(&acc_full[buf]);
+      }
+      if (!ok) {
+        *abort_flag = 1;
+        atomicExch(g.err, 2);
+      }
+    }
+  } else {
+    // ----------------------------------------------------------- epilogue --
+    const int quarter = warp & 3;
+    bool ok = true;
+    int i = 0;
+    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++i) {
+      int m_blk, n_blk;
+      tile_coords(t, m_blk, n_blk);
+      const int buf = i & 1;
+      ok = wait_or_abort(&acc_full[buf], (i >> 1) & 1, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc::fence_after_sync();
+      const int row = m_blk * BM + quarter * 32 + lane;
+      GemmDev gt = g;
+      if (f.mode == FUSE_REDUCE_SCATTER_D) {
+        // the tile's rows belong to rank `owner`: store into that rank's staging slot for this rank
+        const int owner = (m_blk * BM) / f.chunk_rows;
+        gt.d = static_cast<char*>(f.d_owner[owner]) -
+               static_cast<size_t>(owner) * f.chunk_rows * g.ldd * (g.d_fp32 ? 4 : 2);
+      }
+      const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(buf * BN) + (static_cast<uint32_t>(quarter * 32) << 16);
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t r[32];
+        tc::tmem_ld_32x32(tmem_d + static_cast<uint32_t>(c0), r);
+        tc::tmem_ld_wait();
+        if (c0 + 32 >= BN) {
+          // every column of this buffer is in registers: hand it back to the MMA warp
+          tc::fence_before_sync();
+          if (lane == 0) tc::mbar_arrive(&acc_empty[buf]);
+        }
+        const int col0 = n_blk * BN + c0;
+        if (row < g.m && col0 < g.n) epilogue_store(gt, row, col0, r);
+      }
+    }
+    if (!ok && lane == 0) {
+      *abort_flag = 1;
+      atomicExch(g.err, 3);
+    }
+  }
+  tc::fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc::fence_after_sync();
+    tc::tmem_dealloc(tmem_base, 2 * BN);
+  }
+}
+
+int sm_count() {
+  static int n = 0;
+  if (!n) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+  }
+  return n;
+}
+
+template <int BN, int STAGES, bool kAMn, bool kBMn>
+cudaError_t launch_persistent_cfg(const GemmArgs& a, const FusedDev& f, int max_ctas, cudaStream_t stream) {
+  using L = PLayout<BN, STAGES>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t rc = cudaFuncSetAttribute(gemm_persistent_kernel<BN, STAGES, kAMn, kBMn>,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal);
+    if (rc != cudaSuccess) return rc;
+    configured = true;
+  }
+  CUtensorMap ma, mb;
+  const bool oka = kAMn ? encode_map(&ma, a.a, a.k, a.m, a.lda, BK) : encode_map(&ma, a.a, a.m, a.k, a.lda, BM);
+  const bool okb = kBMn ? encode_map(&mb, a.b, a.k, a.n, a.ldb, BK) : encode_map(&mb, a.b, a.n, a.k, a.ldb, BN);
+  if (!oka || !okb) return cudaErrorNotSupported;
+  (void)cudaGetLastError();
+  GemmDev g;
+  g.d = a.d;
+  g.aux = a.aux;
+  g.bias = a.bias;
+  g.residual = a.residual;
+  g.m = a.m;
+  g.n = a.n;
+  g.k = a.k;
+  g.ldd = a.ldd;
+  g.d_fp32 = a.d_fp32 ? 1 : 0;
+  g.accumulate = a.accumulate ? 1 : 0;
+  g.epilogue = a.epilogue;
+  g.err = gemm_error_device_ptr();
+  if (!g.err) return cudaErrorNotSupported;
+  const int tiles = ((a.m + BM - 1) / BM) * ((a.n + BN - 1) / BN);
+  int ctas = sm_count();
+  if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
+  if (tiles < ctas) ctas = tiles;
+  gemm_persistent_kernel<BN, STAGES, kAMn, kBMn><<<ctas, 192, L::kTotal, stream>>>(ma, mb, g, f);
+  count_launch();
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t launch_gemm_persistent(const GemmArgs& a, const FusedDev& f, int max_ctas, cudaStream_t stream) {
+  // Wide tiles when they still give every SM work; otherwise 128 x 128.
+  const long long tiles256 = static_cast<long long>((a.m + BM - 1) / BM) * ((a.n + 255) / 256);
+  const bool wide = a.n % 256 == 0 && tiles256 >= sm_count();
+#define MCCL_PGEMM(BN, ST)                                                                                      \
+  (a.a_mn_major ? (a.b_mn_major ? launch_persistent_cfg<BN, ST, true, true>(a, f, max_ctas, stream)             \
+                                : launch_persistent_cfg<BN, ST, true, false>(a, f, max_ctas, stream))           \
+                : (a.b_mn_major ? launch_persistent_cfg<BN, ST, false, true>(a, f, max_ctas, stream)            \
+                                : launch_persistent_cfg<BN, ST, false, false>(a, f, max_ctas, stream)))
+  return wide ? MCCL_PGEMM(256, 4) : MCCL_PGEMM(128, 6);
+#undef MCCL_PGEMM
+}
+
+}  // namespace ops
+}  // namespace mccl

@@ -15,33 +15,16 @@
 // The reference has no GEMM of its own (no tensor-core code at all); this
 // kernel exists for the model operators and as the core the fused
 // all-gather→GEMM / GEMM→reduce-scatter tensor-parallel kernels build on.
-#include "ops.hpp"
-#include "tcgen05.cuh"
+#include "gemm_common.cuh"
+#include "gemm_persistent.cuh"
 
-#include "../symm/cu_driver.hpp"
+#include <cstdlib>
+#include <string>
 
 namespace mccl {
 namespace ops {
 
 namespace {
-
-constexpr int BM = 128;
-constexpr int BK = 64;          // 64 bf16 = 128 bytes = one swizzle row
-constexpr int UMMA_K = 16;      // bf16 MMA consumes 32 bytes of K per instruction
-
-__device__ int g_gemm_error = 0;
-
-struct GemmDev {
-  void* d;
-  __nv_bfloat16* aux;
-  const float* bias;
-  const __nv_bfloat16* residual;
-  int m, n, k;
-  int ldd;
-  int d_fp32;
-  int accumulate;
-  int epilogue;
-};
 
 template <int BN, int STAGES>
 struct SmemLayout {
@@ -52,8 +35,6 @@ struct SmemLayout {
   static constexpr int kBarriers = (2 * STAGES + 1) * 8 + 16;
   static constexpr int kTotal = kTiles + kBarriers + 1024;  // slack for 1024-byte alignment
 };
-
-__device__ __forceinline__ float gelu_erf(float x) { return 0.5f * x * (1.f + erff(x * 0.70710678f)); }
 
 // kAMn / kBMn: the operand is stored with its M (or N) index contiguous, i.e. as a
 // [K, M] (or [K, N]) row-major matrix; the tile is then fetched as 64-wide column
@@ -118,7 +99,7 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
         issued = kb + 1;
       }
       if (!ok) {
-        atomicExch(&g_gemm_error, 1);
+        atomicExch(g.err, 1);
         // let the copies already in flight land before the CTA retires
         for (int kb = (issued > STAGES ? issued - STAGES : 0); kb < issued; ++kb)
           tc::mbar_wait(&full[kb % STAGES], (kb / STAGES) & 1, 1u << 20);
@@ -145,7 +126,7 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
           tc::mma_bf16(tmem_base, da + a_step * k4, db + b_step * k4, idesc, (kb | k4) != 0);
         tc::mma_commit(&empty[s]);  // frees the stage once these MMAs have read it
       }
-      if (!ok) atomicExch(&g_gemm_error, 2);
+      if (!ok) atomicExch(g.err, 2);
       tc::mma_commit(acc_ready);    // on the failure path this still releases the epilogue warps
     }
   } else {
@@ -154,8 +135,8 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
     const bool ok = tc::mbar_wait(acc_ready, 0);
     tc::fence_after_sync();
     const int row = m_blk * BM + quarter * 32 + lane;
-    const bool failed = !ok || (*reinterpret_cast<volatile int*>(&g_gemm_error) != 0);
-    if (!ok && lane == 0) atomicExch(&g_gemm_error, 3);
+    const bool failed = !ok || (*reinterpret_cast<volatile int*>(g.err) != 0);
+    if (!ok && lane == 0) atomicExch(g.err, 3);
 #pragma unroll 1
     for (int c0 = 0; c0 < BN; c0 += 32) {
       uint32_t r[32];
@@ -163,72 +144,7 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
       tc::tmem_ld_wait();
       const int col0 = n_blk * BN + c0;
       if (failed || row >= g.m || col0 >= g.n) continue;
-      float v[32];
-#pragma unroll
-      for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-      const int ncols = (g.n - col0) < 32 ? (g.n - col0) : 32;  // multiple of 8
-      if (g.epilogue == EPI_BIAS || g.epilogue == EPI_BIAS_GELU) {
-#pragma unroll
-        for (int j = 0; j < 32; ++j)
-          if (j < ncols) v[j] += __ldg(g.bias + col0 + j);
-      }
-      if (g.epilogue == EPI_BIAS_GELU || g.epilogue == EPI_GELU) {
-        __nv_bfloat16* zrow = g.aux + static_cast<size_t>(row) * g.ldd + col0;
-#pragma unroll
-        for (int j8 = 0; j8 < 4; ++j8) {
-          if (j8 * 8 < ncols) {
-            uint4 pk;
-            __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[j8 * 8 + 2 * i], v[j8 * 8 + 2 * i + 1]);
-            *reinterpret_cast<uint4*>(zrow + j8 * 8) = pk;
-          }
-        }
-#pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = gelu_erf(v[j]);
-      }
-      if (g.residual) {
-        const __nv_bfloat16* rrow = g.residual + static_cast<size_t>(row) * g.ldd + col0;
-#pragma unroll
-        for (int j8 = 0; j8 < 4; ++j8) {
-          if (j8 * 8 < ncols) {
-            const uint4 pk = *reinterpret_cast<const uint4*>(rrow + j8 * 8);
-            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&pk);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const float2 t = __bfloat1622float2(h[i]);
-              v[j8 * 8 + 2 * i] += t.x;
-              v[j8 * 8 + 2 * i + 1] += t.y;
-            }
-          }
-        }
-      }
-      if (g.d_fp32) {
-        float* drow = static_cast<float*>(g.d) + static_cast<size_t>(row) * g.ldd + col0;
-#pragma unroll
-        for (int j4 = 0; j4 < 8; ++j4) {
-          if (j4 * 4 < ncols) {
-            float4 o = make_float4(v[j4 * 4], v[j4 * 4 + 1], v[j4 * 4 + 2], v[j4 * 4 + 3]);
-            if (g.accumulate) {
-              const float4 old = *reinterpret_cast<const float4*>(drow + j4 * 4);
-              o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
-            }
-            *reinterpret_cast<float4*>(drow + j4 * 4) = o;
-          }
-        }
-      } else {
-        __nv_bfloat16* drow = static_cast<__nv_bfloat16*>(g.d) + static_cast<size_t>(row) * g.ldd + col0;
-#pragma unroll
-        for (int j8 = 0; j8 < 4; ++j8) {
-          if (j8 * 8 < ncols) {
-            uint4 pk;
-            __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[j8 * 8 + 2 * i], v[j8 * 8 + 2 * i + 1]);
-            *reinterpret_cast<uint4*>(drow + j8 * 8) = pk;
-          }
-        }
-      }
+      epilogue_store(g, row, col0, r);
     }
   }
   tc::fence_before_sync();
@@ -237,24 +153,6 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
     tc::fence_after_sync();
     tc::tmem_dealloc(tmem_base, BN);
   }
-}
-
-// K-major operand [rows = M or N, cols = K]: box = 64 (K) x box_rows.
-// MN-major operand [rows = K, cols = M or N]: box = 64 (M/N) x 64 (K).
-bool encode_map(CUtensorMap* map, const void* base, int rows, int cols, int ld_elems, int box_rows) {
-  const CuDriver& cu = CuDriver::get();
-  if (!cu.loaded || !cu.TensorMapEncodeTiled) return false;
-  int device = 0;
-  cudaGetDevice(&device);
-  cu.ensure_context(device);
-  cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
-  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld_elems) * 2};
-  cuuint32_t box[2] = {static_cast<cuuint32_t>(BK), static_cast<cuuint32_t>(box_rows)};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult rc = cu.TensorMapEncodeTiled(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
-                                        estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return rc == CUDA_SUCCESS;
 }
 
 thread_local const char* t_reason = "";
@@ -290,6 +188,8 @@ cudaError_t launch_cfg(const GemmArgs& a, cudaStream_t stream) {
   g.d_fp32 = a.d_fp32 ? 1 : 0;
   g.accumulate = a.accumulate ? 1 : 0;
   g.epilogue = a.epilogue;
+  g.err = gemm_error_device_ptr();
+  if (!g.err) return unsupported("no device error word");
   dim3 grid((a.n + BN - 1) / BN, (a.m + BM - 1) / BM);
   gemm_bf16_kernel<BN, STAGES, kAMn, kBMn><<<grid, 192, L::kTotal, stream>>>(ma, mb, g);
   count_launch();
@@ -314,9 +214,33 @@ cudaError_t gemm_bf16_tn(const GemmArgs& a, cudaStream_t stream) {
   if (a.accumulate && !a.d_fp32) return cudaErrorInvalidValue;
   if (a.residual && (reinterpret_cast<uintptr_t>(a.residual) & 15u)) return unsupported("residual pointer must be 16-byte aligned");
   if (a.a_mn_major && a.m % 8 != 0) return unsupported("an MN-major A needs M to be a multiple of 8");
+  // Default: persistent kernel (one CTA per SM, double-buffered accumulator).
+  // MCCL_GEMM_KERNEL=tile selects the one-tile-per-CTA kernel below.
+  static const bool tile_kernel = [] {
+    const char* v = std::getenv("MCCL_GEMM_KERNEL");
+    return v && std::string(v) == "tile";
+  }();
+  if (!tile_kernel) {
+    cudaError_t rc = launch_gemm_persistent(a, FusedDev{}, 0, stream);
+    if (rc == cudaErrorNotSupported) return unsupported("cuTensorMapEncodeTiled rejected an operand");
+    return rc;
+  }
   // 128 x 128 tiles, 3 stages of 32 KB: two CTAs per SM.
   if (a.a_mn_major) return a.b_mn_major ? launch_cfg<128, 3, true, true>(a, stream) : launch_cfg<128, 3, true, false>(a, stream);
   return a.b_mn_major ? launch_cfg<128, 3, false, true>(a, stream) : launch_cfg<128, 3, false, false>(a, stream);
+}
+
+namespace {
+__device__ int g_gemm_error = 0;
+}
+
+int* gemm_error_device_ptr() {
+  static int* ptr = nullptr;
+  if (!ptr) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_gemm_error) == cudaSuccess) ptr = static_cast<int*>(p);
+  }
+  return ptr;
 }
 
 int gemm_error_flag() {
