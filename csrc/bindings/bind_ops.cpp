@@ -141,7 +141,7 @@ void bind_ops(py::module_& m) {
   m.def(
       "norm_bwd",
       [](const at::Tensor& dy, const at::Tensor& x, const at::Tensor& w, const at::Tensor& mean, const at::Tensor& rstd,
-         bool layernorm, const c10::optional<at::Tensor>& dw_out, const c10::optional<at::Tensor>& db_out) {
+         bool layernorm, const c10::optional<at::Tensor>& dw_out, const c10::optional<at::Tensor>& db_out, bool accumulate) {
         need(dy, at::kBFloat16, "norm_bwd(dy)");
         need(x, at::kBFloat16, "norm_bwd(x)");
         need(w, at::kFloat, "norm_bwd(weight)");
@@ -156,16 +156,20 @@ void bind_ops(py::module_& m) {
         need(dw, at::kFloat, "norm_bwd(dw)");
         if (layernorm) need(db, at::kFloat, "norm_bwd(db)");
         MCCL_CHECK_TENSOR(dw.numel() == dim && (!layernorm || db.numel() == dim), "norm_bwd: gradient buffers must have `dim` elements");
-        at::Tensor scratch = at::empty({2 * ops::colsum_slabs(static_cast<int>(rows)) * dim}, x.options().dtype(at::kFloat));
+        // accumulate: add into dw / db (one pass, atomics) instead of overwriting them (two passes, fixed order)
+        at::Tensor scratch;
+        if (!accumulate)
+          scratch = at::empty({2 * ops::colsum_slabs(static_cast<int>(rows)) * dim}, x.options().dtype(at::kFloat));
         check_launch(ops::norm_bwd(bf(dy), bf(x), w.data_ptr<float>(), mean.data_ptr<float>(), rstd.data_ptr<float>(), bf(dx),
-                                   dw.data_ptr<float>(), layernorm ? db.data_ptr<float>() : nullptr, scratch.data_ptr<float>(),
+                                   dw.data_ptr<float>(), layernorm ? db.data_ptr<float>() : nullptr,
+                                   accumulate ? nullptr : scratch.data_ptr<float>(),
                                    static_cast<int>(rows),
                                    static_cast<int>(dim), layernorm, stream_of(x)),
                      "norm_bwd");
         return std::make_tuple(dx, dw, db.defined() ? c10::optional<at::Tensor>(db) : c10::nullopt);
       },
       py::arg("dy"), py::arg("x"), py::arg("weight"), py::arg("mean"), py::arg("rstd"), py::arg("layernorm"),
-      py::arg("dw_out") = py::none(), py::arg("db_out") = py::none());
+      py::arg("dw_out") = py::none(), py::arg("db_out") = py::none(), py::arg("accumulate") = false);
 
   m.def(
       "adamw_flat",
@@ -212,7 +216,7 @@ void bind_ops(py::module_& m) {
       py::arg("logits"), py::arg("targets"), py::arg("grad_scale") = 1.0,
       "Returns per-row losses; overwrites logits with (softmax - onehot) * grad_scale.");
 
-  m.def("colsum_bf16", [](const at::Tensor& x, const c10::optional<at::Tensor>& out_opt) {
+  m.def("colsum_bf16", [](const at::Tensor& x, const c10::optional<at::Tensor>& out_opt, bool accumulate) {
     need(x, at::kBFloat16, "colsum(x)");
     MCCL_CHECK_TENSOR(x.dim() == 2, "colsum: 2-D tensor expected");
     c10::cuda::CUDAGuard guard(x.device());
@@ -220,10 +224,14 @@ void bind_ops(py::module_& m) {
     at::Tensor out = out_opt.has_value() ? *out_opt : at::empty({dim}, x.options().dtype(at::kFloat));
     need(out, at::kFloat, "colsum(out)");
     MCCL_CHECK_TENSOR(out.numel() == dim, "colsum: output must have one element per column");
-    at::Tensor scratch = at::empty({ops::colsum_slabs(rows) * dim}, x.options().dtype(at::kFloat));
-    check_launch(ops::colsum_bf16(bf(x), out.data_ptr<float>(), scratch.data_ptr<float>(), rows, dim, stream_of(x)), "colsum");
+    MCCL_CHECK_TENSOR(!accumulate || out_opt.has_value(), "colsum: accumulate needs an output to add into");
+    at::Tensor scratch;
+    if (!accumulate) scratch = at::empty({ops::colsum_slabs(rows) * dim}, x.options().dtype(at::kFloat));
+    check_launch(ops::colsum_bf16(bf(x), out.data_ptr<float>(), accumulate ? nullptr : scratch.data_ptr<float>(), rows, dim,
+                                  stream_of(x)),
+                 "colsum");
     return out;
-  }, py::arg("x"), py::arg("out") = py::none());
+  }, py::arg("x"), py::arg("out") = py::none(), py::arg("accumulate") = false);
   m.def("transpose_bf16", [](const at::Tensor& x) {
     need(x, at::kBFloat16, "transpose(x)");
     MCCL_CHECK_TENSOR(x.dim() == 2, "transpose: 2-D tensor expected");

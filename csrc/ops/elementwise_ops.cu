@@ -143,7 +143,7 @@ template <bool kNorm>
 __global__ void __launch_bounds__(256) colsum_partial_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                                                              const float* __restrict__ mean, const float* __restrict__ rstd,
                                                              float* __restrict__ part_w, float* __restrict__ part_b, int rows,
-                                                             int dim) {
+                                                             int dim, int atomic) {
   __shared__ float sw[8][32][9], sb[8][32][9];
   const int cg = threadIdx.x & 31, ry = threadIdx.x >> 5;
   const int col = blockIdx.x * 256 + cg * 8;
@@ -180,9 +180,15 @@ __global__ void __launch_bounds__(256) colsum_partial_kernel(const __nv_bfloat16
       tw += sw[k][ccg][ci];
       tb += sb[k][ccg][ci];
     }
-    const size_t o = static_cast<size_t>(blockIdx.y) * dim + blockIdx.x * 256 + c;
-    if (kNorm) part_w[o] = tw;
-    if (part_b) part_b[o] = tb;
+    if (atomic) {
+      // single pass: add this slab's sums straight into the (pre-zeroed or accumulating) outputs
+      if (kNorm) atomicAdd(part_w + blockIdx.x * 256 + c, tw);
+      if (part_b) atomicAdd(part_b + blockIdx.x * 256 + c, tb);
+    } else {
+      const size_t o = static_cast<size_t>(blockIdx.y) * dim + blockIdx.x * 256 + c;
+      if (kNorm) part_w[o] = tw;
+      if (part_b) part_b[o] = tb;
+    }
   }
 }
 
@@ -235,10 +241,16 @@ cudaError_t norm_bwd(const __nv_bfloat16* dy, const __nv_bfloat16* x, const floa
   if (layernorm) norm_bwd_dx_kernel<true><<<blocks, 256, 0, stream>>>(dy, x, w, mean, rstd, dx, rows, dim);
   else norm_bwd_dx_kernel<false><<<blocks, 256, 0, stream>>>(dy, x, w, mean, rstd, dx, rows, dim);
   const int slabs = colsum_slabs(rows);
+  dim3 grid((dim + 255) / 256, slabs);
+  if (!scratch) {
+    // no scratch: dw / db accumulate the slab sums atomically (they must hold the value to add to)
+    colsum_partial_kernel<true><<<grid, 256, 0, stream>>>(dy, x, mean, rstd, dw, layernorm ? db : nullptr, rows, dim, 1);
+    count_launch(2);
+    return cudaGetLastError();
+  }
   float* part_w = scratch;
   float* part_b = layernorm ? scratch + static_cast<size_t>(slabs) * dim : nullptr;
-  dim3 grid((dim + 255) / 256, slabs);
-  colsum_partial_kernel<true><<<grid, 256, 0, stream>>>(dy, x, mean, rstd, part_w, part_b, rows, dim);
+  colsum_partial_kernel<true><<<grid, 256, 0, stream>>>(dy, x, mean, rstd, part_w, part_b, rows, dim, 0);
   colsum_final_kernel<<<(dim + 31) / 32, 256, 0, stream>>>(part_w, part_b, dw, layernorm ? db : nullptr, slabs, dim);
   count_launch(3);
   return cudaGetLastError();
@@ -248,7 +260,12 @@ cudaError_t colsum_bf16(const __nv_bfloat16* in, float* out, float* scratch, int
   if (dim % 8 != 0 || (reinterpret_cast<uintptr_t>(in) & 15u)) return cudaErrorNotSupported;
   const int slabs = colsum_slabs(rows);
   dim3 grid((dim + 255) / 256, slabs);
-  colsum_partial_kernel<false><<<grid, 256, 0, stream>>>(in, nullptr, nullptr, nullptr, nullptr, scratch, rows, dim);
+  if (!scratch) {
+    colsum_partial_kernel<false><<<grid, 256, 0, stream>>>(in, nullptr, nullptr, nullptr, nullptr, out, rows, dim, 1);
+    count_launch();
+    return cudaGetLastError();
+  }
+  colsum_partial_kernel<false><<<grid, 256, 0, stream>>>(in, nullptr, nullptr, nullptr, nullptr, scratch, rows, dim, 0);
   colsum_final_kernel<<<(dim + 31) / 32, 256, 0, stream>>>(nullptr, scratch, nullptr, out, slabs, dim);
   count_launch(2);
   return cudaGetLastError();

@@ -25,6 +25,7 @@ struct GemmDev {
   int d_fp32;
   int accumulate;
   int epilogue;
+  int atomic_add;  // fp32 output accumulated with red.global.add (split-K partial sums)
   int* err;  // device word set non-zero when a pipeline wait runs out
 };
 
@@ -37,72 +38,76 @@ __device__ __forceinline__ float gelu_erf(float x) { return 0.5f * x * (1.f + er
 // Finishes 32 consecutive accumulator columns [col0, col0 + 32) of one output
 // row: r holds the raw fp32 bits read from tensor memory.
 __device__ __forceinline__ void epilogue_store(const GemmDev& g, int row, int col0, const uint32_t (&r)[32]) {
-        float v[32];
-  #pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-        const int ncols = (g.n - col0) < 32 ? (g.n - col0) : 32;  // multiple of 8
-        if (g.epilogue == EPI_BIAS || g.epilogue == EPI_BIAS_GELU) {
-  #pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (j < ncols) v[j] += __ldg(g.bias + col0 + j);
+  float v[32];
+#pragma unroll
+  for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+  const int ncols = (g.n - col0) < 32 ? (g.n - col0) : 32;  // multiple of 8
+  if (g.epilogue == EPI_BIAS || g.epilogue == EPI_BIAS_GELU) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (j < ncols) v[j] += __ldg(g.bias + col0 + j);
+  }
+  if (g.epilogue == EPI_BIAS_GELU || g.epilogue == EPI_GELU) {
+    __nv_bfloat16* zrow = g.aux + static_cast<size_t>(row) * g.ldd + col0;
+#pragma unroll
+    for (int j8 = 0; j8 < 4; ++j8) {
+      if (j8 * 8 < ncols) {
+        uint4 pk;
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[j8 * 8 + 2 * i], v[j8 * 8 + 2 * i + 1]);
+        *reinterpret_cast<uint4*>(zrow + j8 * 8) = pk;
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = gelu_erf(v[j]);
+  }
+  if (g.residual) {
+    const __nv_bfloat16* rrow = g.residual + static_cast<size_t>(row) * g.ldd + col0;
+#pragma unroll
+    for (int j8 = 0; j8 < 4; ++j8) {
+      if (j8 * 8 < ncols) {
+        const uint4 pk = *reinterpret_cast<const uint4*>(rrow + j8 * 8);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&pk);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 t = __bfloat1622float2(h[i]);
+          v[j8 * 8 + 2 * i] += t.x;
+          v[j8 * 8 + 2 * i + 1] += t.y;
         }
-        if (g.epilogue == EPI_BIAS_GELU || g.epilogue == EPI_GELU) {
-          __nv_bfloat16* zrow = g.aux + static_cast<size_t>(row) * g.ldd + col0;
-  #pragma unroll
-          for (int j8 = 0; j8 < 4; ++j8) {
-            if (j8 * 8 < ncols) {
-              uint4 pk;
-              __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
-  #pragma unroll
-              for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[j8 * 8 + 2 * i], v[j8 * 8 + 2 * i + 1]);
-              *reinterpret_cast<uint4*>(zrow + j8 * 8) = pk;
-            }
-          }
-  #pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = gelu_erf(v[j]);
+      }
+    }
+  }
+  if (g.d_fp32) {
+    float* drow = static_cast<float*>(g.d) + static_cast<size_t>(row) * g.ldd + col0;
+#pragma unroll
+    for (int j4 = 0; j4 < 8; ++j4) {
+      if (j4 * 4 < ncols) {
+        float4 o = make_float4(v[j4 * 4], v[j4 * 4 + 1], v[j4 * 4 + 2], v[j4 * 4 + 3]);
+        if (g.atomic_add) {
+          atomicAdd(reinterpret_cast<float4*>(drow + j4 * 4), o);
+          continue;
         }
-        if (g.residual) {
-          const __nv_bfloat16* rrow = g.residual + static_cast<size_t>(row) * g.ldd + col0;
-  #pragma unroll
-          for (int j8 = 0; j8 < 4; ++j8) {
-            if (j8 * 8 < ncols) {
-              const uint4 pk = *reinterpret_cast<const uint4*>(rrow + j8 * 8);
-              const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&pk);
-  #pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                const float2 t = __bfloat1622float2(h[i]);
-                v[j8 * 8 + 2 * i] += t.x;
-                v[j8 * 8 + 2 * i + 1] += t.y;
-              }
-            }
-          }
+        if (g.accumulate) {
+          const float4 old = *reinterpret_cast<const float4*>(drow + j4 * 4);
+          o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
         }
-        if (g.d_fp32) {
-          float* drow = static_cast<float*>(g.d) + static_cast<size_t>(row) * g.ldd + col0;
-  #pragma unroll
-          for (int j4 = 0; j4 < 8; ++j4) {
-            if (j4 * 4 < ncols) {
-              float4 o = make_float4(v[j4 * 4], v[j4 * 4 + 1], v[j4 * 4 + 2], v[j4 * 4 + 3]);
-              if (g.accumulate) {
-                const float4 old = *reinterpret_cast<const float4*>(drow + j4 * 4);
-                o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
-              }
-              *reinterpret_cast<float4*>(drow + j4 * 4) = o;
-            }
-          }
-        } else {
-          __nv_bfloat16* drow = static_cast<__nv_bfloat16*>(g.d) + static_cast<size_t>(row) * g.ldd + col0;
-  #pragma unroll
-          for (int j8 = 0; j8 < 4; ++j8) {
-            if (j8 * 8 < ncols) {
-              uint4 pk;
-              __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
-  #pragma unroll
-              for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[j8 * 8 + 2 * i], v[j8 * 8 + 2 * i + 1]);
-              *reinterpret_cast<uint4*>(drow + j8 * 8) = pk;
-            }
-          }
-        }
+        *reinterpret_cast<float4*>(drow + j4 * 4) = o;
+      }
+    }
+  } else {
+    __nv_bfloat16* drow = static_cast<__nv_bfloat16*>(g.d) + static_cast<size_t>(row) * g.ldd + col0;
+#pragma unroll
+    for (int j8 = 0; j8 < 4; ++j8) {
+      if (j8 * 8 < ncols) {
+        uint4 pk;
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[j8 * 8 + 2 * i], v[j8 * 8 + 2 * i + 1]);
+        *reinterpret_cast<uint4*>(drow + j8 * 8) = pk;
+      }
+    }
+  }
 }
 
 // K-major operand [rows = M or N, cols = K]: box = 64 (K) x box_rows.

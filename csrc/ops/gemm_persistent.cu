@@ -18,6 +18,8 @@
 #include "gemm_common.cuh"
 #include "gemm_persistent.cuh"
 
+#include <cstdlib>
+
 namespace mccl {
 namespace ops {
 
@@ -72,8 +74,11 @@ __global__ void __launch_bounds__(192, 1) gemm_persistent_kernel(const __grid_co
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m_tiles = (g.m + BM - 1) / BM, n_tiles = (g.n + BN - 1) / BN;
-  const int total_tiles = m_tiles * n_tiles;
-  const int num_kb = g.k / BK;
+  // Split-K: a work item is (tile, k-slice); slices of one tile run on different SMs
+  // at the same time and add their partial sums into the fp32 output.
+  const int splits = f.k_splits > 1 ? f.k_splits : 1;
+  const int total_tiles = m_tiles * n_tiles * splits;
+  const int num_kb = (g.k / BK) / splits;
   // Row-chunk rotation: tile order starts at this rank's own chunk (fusions only).
   const int m_rot = f.mode != FUSE_NONE ? (f.rank * (f.chunk_rows / BM)) % m_tiles : 0;
 
@@ -97,7 +102,9 @@ __global__ void __launch_bounds__(192, 1) gemm_persistent_kernel(const __grid_co
   tc::fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
-  auto tile_coords = [&](int t, int& m_blk, int& n_blk) {
+  auto tile_coords = [&](int w, int& m_blk, int& n_blk, int& kb0) {
+    const int t = w / splits;
+    kb0 = (w % splits) * num_kb;
     n_blk = t % n_tiles;
     m_blk = (t / n_tiles + m_rot) % m_tiles;
   };
@@ -108,8 +115,8 @@ __global__ void __launch_bounds__(192, 1) gemm_persistent_kernel(const __grid_co
       bool ok = true;
       uint32_t it = 0;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-        int m_blk, n_blk;
-        tile_coords(t, m_blk, n_blk);
+        int m_blk, n_blk, kb0;
+        tile_coords(t, m_blk, n_blk, kb0);
         if (f.mode == FUSE_ALLGATHER_A) {
           const int chunk = (m_blk * BM) / f.chunk_rows;
           if (chunk != f.rank) ok = wait_flag_geq(f.chunk_flags + chunk, f.epoch, abort_flag);
@@ -124,16 +131,16 @@ __global__ void __launch_bounds__(192, 1) gemm_persistent_kernel(const __grid_co
           if (kAMn) {
 #pragma unroll
             for (int gq = 0; gq < BM / 64; ++gq)
-              tc::tma_load_2d(a_dst + gq * (BK * 128), &tma_a, &full[s], m_blk * BM + gq * 64, kb * BK);
+              tc::tma_load_2d(a_dst + gq * (BK * 128), &tma_a, &full[s], m_blk * BM + gq * 64, (kb0 + kb) * BK);
           } else {
-            tc::tma_load_2d(a_dst, &tma_a, &full[s], kb * BK, m_blk * BM);
+            tc::tma_load_2d(a_dst, &tma_a, &full[s], (kb0 + kb) * BK, m_blk * BM);
           }
           if (kBMn) {
 #pragma unroll
             for (int gq = 0; gq < BN / 64; ++gq)
-              tc::tma_load_2d(a_dst + L::kABytes + gq * (BK * 128), &tma_b, &full[s], n_blk * BN + gq * 64, kb * BK);
+              tc::tma_load_2d(a_dst + L::kABytes + gq * (BK * 128), &tma_b, &full[s], n_blk * BN + gq * 64, (kb0 + kb) * BK);
           } else {
-            tc::tma_load_2d(a_dst + L::kABytes, &tma_b, &full[s], kb * BK, n_blk * BN);
+            tc::tma_load_2d(a_dst + L::kABytes, &tma_b, &full[s], (kb0 + kb) * BK, n_blk * BN);
           }
         }
       }
@@ -188,8 +195,8 @@ __global__ void __launch_bounds__(192, 1) gemm_persistent_kernel(const __grid_co
     bool ok = true;
     int i = 0;
     for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++i) {
-      int m_blk, n_blk;
-      tile_coords(t, m_blk, n_blk);
+      int m_blk, n_blk, kb0;
+      tile_coords(t, m_blk, n_blk, kb0);
       const int buf = i & 1;
       ok = wait_or_abort(&acc_full[buf], (i >> 1) & 1, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
@@ -242,8 +249,31 @@ int sm_count() {
   return n;
 }
 
+// Number of k-slices that minimises ceil(items / SMs) * (k-blocks per item + fixed
+// per-item cost).  Only fp32 outputs can be split (partial sums are added atomically).
+int choose_splits(int tiles, int num_kb, int sms) {
+  auto cost = [&](int s) {
+    const long long rounds = (static_cast<long long>(tiles) * s + sms - 1) / sms;
+    return rounds * (num_kb / s + 8 + (s > 1 ? 8 : 0));  // atomics make a split item's epilogue dearer
+  };
+  int best = 1;
+  long long best_cost = cost(1);
+  for (int s = 2; s <= 16; s *= 2) {
+    if (num_kb % s != 0 || num_kb / s < 4) break;
+    const long long c = cost(s);
+    if (c * 5 < best_cost * 4 && c < (best == 1 ? best_cost : best_cost)) {  // at least 20 % better than no split
+      if (best == 1 || c < best_cost) {
+        best = s;
+        best_cost = c;
+      }
+    }
+  }
+  return best;
+}
+
 template <int BN, int STAGES, bool kAMn, bool kBMn>
-cudaError_t launch_persistent_cfg(const GemmArgs& a, const FusedDev& f, int max_ctas, cudaStream_t stream) {
+cudaError_t launch_persistent_cfg(const GemmArgs& a, const FusedDev& f_in, int max_ctas, cudaStream_t stream) {
+  FusedDev f = f_in;
   using L = PLayout<BN, STAGES>;
   static bool configured = false;
   if (!configured) {
@@ -269,9 +299,29 @@ cudaError_t launch_persistent_cfg(const GemmArgs& a, const FusedDev& f, int max_
   g.d_fp32 = a.d_fp32 ? 1 : 0;
   g.accumulate = a.accumulate ? 1 : 0;
   g.epilogue = a.epilogue;
+  g.atomic_add = 0;
   g.err = gemm_error_device_ptr();
   if (!g.err) return cudaErrorNotSupported;
-  const int tiles = ((a.m + BM - 1) / BM) * ((a.n + BN - 1) / BN);
+  int tiles = ((a.m + BM - 1) / BM) * ((a.n + BN - 1) / BN);
+  f.k_splits = 1;
+  static const bool allow_split = [] {
+    const char* v = std::getenv("MCCL_GEMM_SPLITK");
+    return !(v && v[0] == '0');
+  }();
+  if (allow_split && a.d_fp32 && a.epilogue == EPI_NONE && !a.residual && f.mode == FUSE_NONE) {
+    const int splits = choose_splits(tiles, a.k / BK, sm_count());
+    if (splits > 1) {
+      if (!a.accumulate) {
+        // partial sums are added into the output: start from zero
+        if (a.ldd != a.n) goto no_split;
+        cudaMemsetAsync(a.d, 0, static_cast<size_t>(a.m) * a.n * sizeof(float), stream);
+      }
+      f.k_splits = splits;
+      g.atomic_add = 1;
+      tiles *= splits;
+    }
+  }
+no_split:
   int ctas = sm_count();
   if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
   if (tiles < ctas) ctas = tiles;

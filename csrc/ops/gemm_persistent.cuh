@@ -24,7 +24,8 @@ struct FusedDev {
   int chunk_rows = 0;                    // rows per rank chunk, a multiple of 128
   const uint32_t* chunk_flags = nullptr; // all-gather: chunk c has landed when chunk_flags[c] >= epoch
   uint32_t epoch = 0;
-  void* d_owner[8] = {};                 // reduce-scatter: where this rank's partial rows of chunk c go
+  void* d_owner[8] = {};
+  int k_splits = 1;                      // split-K factor (set by the launcher)                 // reduce-scatter: where this rank's partial rows of chunk c go
 };
 
 // max_ctas <= 0: one CTA per SM.  The fusions pass a smaller number to leave

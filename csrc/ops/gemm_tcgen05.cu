@@ -188,6 +188,7 @@ cudaError_t launch_cfg(const GemmArgs& a, cudaStream_t stream) {
   g.d_fp32 = a.d_fp32 ? 1 : 0;
   g.accumulate = a.accumulate ? 1 : 0;
   g.epilogue = a.epilogue;
+  g.atomic_add = 0;
   g.err = gemm_error_device_ptr();
   if (!g.err) return unsupported("no device error word");
   dim3 grid((a.n + BN - 1) / BN, (a.m + BM - 1) / BM);

@@ -24,12 +24,14 @@ void count_launch(int n = 1);
 // x, y: [rows, dim] bf16; w, b: fp32; mean / rstd: fp32 [rows] saved for backward.
 cudaError_t norm_fwd(const __nv_bfloat16* x, const float* w, const float* b, __nv_bfloat16* y, float* mean, float* rstd,
                      int rows, int dim, float eps, cudaStream_t stream);
-// dx: [rows, dim] bf16; dw, db: fp32 [dim] (overwritten).  scratch: fp32,
-// 2 * colsum_slabs(rows) * dim elements (partial column sums).
+// dx: [rows, dim] bf16; dw, db: fp32 [dim].  With scratch (fp32, 2 * colsum_slabs(rows) * dim
+// elements) dw / db are overwritten by a two-stage, order-fixed reduction; with scratch == nullptr
+// the slab sums are added to dw / db atomically in one pass.
 cudaError_t norm_bwd(const __nv_bfloat16* dy, const __nv_bfloat16* x, const float* w, const float* mean, const float* rstd,
                      __nv_bfloat16* dx, float* dw, float* db, float* scratch, int rows, int dim, bool layernorm,
                      cudaStream_t stream);
-// out[c] = sum over rows of in[r, c] (bias gradients).  scratch: colsum_slabs(rows) * dim floats.
+// out[c] = sum over rows of in[r, c] (bias gradients).  scratch: colsum_slabs(rows) * dim floats,
+// or nullptr to add into out atomically in one pass.
 cudaError_t colsum_bf16(const __nv_bfloat16* in, float* out, float* scratch, int rows, int dim, cudaStream_t stream);
 int colsum_slabs(int rows);
 

@@ -100,7 +100,7 @@ class LinearFn(torch.autograd.Function):
             bsink = _sink(ctx.bias)
             if N % 8 == 0:
                 if bsink is not None:
-                    _C.colsum_bf16(dz, bsink)
+                    _C.colsum_bf16(dz, bsink, True)
                     _notify(ctx.bias)
                 else:
                     db = _C.colsum_bf16(dz)
@@ -128,8 +128,8 @@ class NormFn(torch.autograd.Function):
         dyc = dy if dy.is_contiguous() else dy.contiguous()
         wsink, bsink = _sink(ctx.weight), (_sink(ctx.bias) if ctx.bias is not None else None)
         if wsink is not None and (not ctx.layernorm or bsink is not None):
-            # single use per step: the sinks were zeroed at the start of the step
-            dx, _, _ = _C.norm_bwd(dyc, x, weight, mean, rstd, ctx.layernorm, wsink, bsink)
+            # the sinks were zeroed at the start of the step; the kernel adds into them
+            dx, _, _ = _C.norm_bwd(dyc, x, weight, mean, rstd, ctx.layernorm, wsink, bsink, True)
             _notify(ctx.weight)
             if ctx.bias is not None:
                 _notify(ctx.bias)
