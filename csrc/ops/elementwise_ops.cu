@@ -497,3 +497,72 @@ cudaError_t gelu_bwd(const __nv_bfloat16* dy, const __nv_bfloat16* z, __nv_bfloa
 
 }  // namespace ops
 }  // namespace mccl
+
+// ---------------------------------------------------------------------------
+// Allocation-free column sum (see noalloc.h for who needs it and the rules).
+// The partial sums live in an array that is part of this library's device
+// image.  Host code may not use the array's name as a pointer: the address the
+// kernels need is looked up once per device with cudaGetSymbolAddress.
+// ---------------------------------------------------------------------------
+#include <cstdio>
+
+#include "noalloc.h"
+
+namespace {
+
+static __device__ __align__(256) float g_noalloc_scratch[MCCL_NOALLOC_SCRATCH_FLOATS];
+
+constexpr int kNoallocMaxDevices = 64;
+float* g_noalloc_scratch_ptr[kNoallocMaxDevices] = {};
+thread_local char t_noalloc_error[256] = "";
+
+// Device address of the scratch array on the current device (looked up on first use).
+float* noalloc_scratch_for_current_device() {
+  int device = -1;
+  cudaError_t rc = cudaGetDevice(&device);
+  if (rc != cudaSuccess || device < 0 || device >= kNoallocMaxDevices) {
+    std::snprintf(t_noalloc_error, sizeof(t_noalloc_error), "cannot identify the current device: %s",
+                  rc == cudaSuccess ? "index out of range" : cudaGetErrorString(rc));
+    return nullptr;
+  }
+  if (!g_noalloc_scratch_ptr[device]) {
+    float* ptr = nullptr;
+    rc = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_noalloc_scratch);
+    if (rc != cudaSuccess || !ptr) {
+      std::snprintf(t_noalloc_error, sizeof(t_noalloc_error), "cudaGetSymbolAddress failed on device %d: %s", device,
+                    cudaGetErrorString(rc));
+      return nullptr;
+    }
+    g_noalloc_scratch_ptr[device] = ptr;
+  }
+  return g_noalloc_scratch_ptr[device];
+}
+
+}  // namespace
+
+extern "C" const char* mccl_noalloc_last_error(void) { return t_noalloc_error; }
+
+extern "C" int mccl_colsum_bf16_noalloc(const void* in_bf16, float* out, int rows, int dim, void* stream) {
+  t_noalloc_error[0] = 0;
+  if (!in_bf16 || !out || rows <= 0 || dim <= 0 || dim % 8 != 0 || (reinterpret_cast<uintptr_t>(in_bf16) & 15u)) {
+    std::snprintf(t_noalloc_error, sizeof(t_noalloc_error),
+                  "bad argument: need non-null pointers, rows > 0, dim a positive multiple of 8 and a 16-byte aligned input");
+    return MCCL_NOALLOC_BAD_ARGUMENT;
+  }
+  const long long need = static_cast<long long>(mccl::ops::colsum_slabs(rows)) * dim;
+  if (need > MCCL_NOALLOC_SCRATCH_FLOATS) {
+    std::snprintf(t_noalloc_error, sizeof(t_noalloc_error),
+                  "problem too large for the fixed scratch array: ceil(rows/64)*dim = %lld floats, limit %d", need,
+                  MCCL_NOALLOC_SCRATCH_FLOATS);
+    return MCCL_NOALLOC_TOO_LARGE;
+  }
+  float* scratch = noalloc_scratch_for_current_device();
+  if (!scratch) return MCCL_NOALLOC_CUDA_ERROR;
+  cudaError_t rc = mccl::ops::colsum_bf16(static_cast<const __nv_bfloat16*>(in_bf16), out, scratch, rows, dim,
+                                          static_cast<cudaStream_t>(stream));
+  if (rc != cudaSuccess) {
+    std::snprintf(t_noalloc_error, sizeof(t_noalloc_error), "kernel launch failed: %s", cudaGetErrorString(rc));
+    return MCCL_NOALLOC_CUDA_ERROR;
+  }
+  return MCCL_NOALLOC_OK;
+}
