@@ -18,6 +18,7 @@
 #include "collectives.hpp"
 
 #include <cstdio>
+#include <type_traits>
 
 #include "comm_device.cuh"
 
@@ -101,18 +102,29 @@ __global__ void __launch_bounds__(kThreads) twoshot_kernel(DevComm c, CollArgs a
     return lim < total ? lim : total;
   };
 
-  // Phase 1: push my copy of chunk p to rank p.
-  for (long long i = pb + threadIdx.x; i < pe; i += blockDim.x) {
+  // Phase 1: push my copy of chunk p to rank p.  Four packs per thread are loaded
+  // before any is stored so that several local reads are in flight per thread.
+  constexpr int U = 4;
+  for (long long i0 = pb + threadIdx.x; i0 < pe; i0 += static_cast<long long>(blockDim.x) * U) {
 #pragma unroll 1
     for (int k = 1; k < N; ++k) {
       const int p = (rank + k) % N;
-      const long long e0 = static_cast<long long>(p) * stride + i * E;
-      const int nv = valid_in_pack(e0, chunk_limit(p), E);
-      if (nv <= 0) continue;
-      Acc v[E];
-      load_pack<T, E, Acc>(in + e0, v, nv, aligned16(in + e0));
-      W* dst = reinterpret_cast<W*>(c.arena[p] + recv_off + static_cast<size_t>(rank) * slot_bytes) + i * E;
-      store_pack<W, E, Acc>(dst, v, E, true);
+      Acc v[U][E];
+      int nv[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long i = i0 + static_cast<long long>(u) * blockDim.x;
+        const long long e0 = static_cast<long long>(p) * stride + i * E;
+        nv[u] = i < pe ? valid_in_pack(e0, chunk_limit(p), E) : 0;
+        if (nv[u] > 0) load_pack<T, E, Acc>(in + e0, v[u], nv[u], aligned16(in + e0));
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (nv[u] <= 0) continue;
+        const long long i = i0 + static_cast<long long>(u) * blockDim.x;
+        W* dst = reinterpret_cast<W*>(c.arena[p] + recv_off + static_cast<size_t>(rank) * slot_bytes) + i * E;
+        store_pack<W, E, Acc>(dst, v[u], E, true);
+      }
     }
   }
   if (barrier_all(c, vr, rank, s, PH_PUSH)) {
@@ -127,14 +139,18 @@ __global__ void __launch_bounds__(kThreads) twoshot_kernel(DevComm c, CollArgs a
     if (nv <= 0) continue;
     Acc acc[E];
     load_pack<T, E, Acc>(in + e0, acc, nv, aligned16(in + e0));
-#pragma unroll 1
-    for (int src = 0; src < N; ++src) {
-      if (src == rank) continue;
-      Acc v[E];
-      const W* sp = reinterpret_cast<const W*>(c.arena[rank] + recv_off + static_cast<size_t>(src) * slot_bytes) + i * E;
-      load_pack<W, E, Acc>(sp, v, E, true);
+    uint4 slots[kMaxRanks];
 #pragma unroll
-      for (int e = 0; e < E; ++e) acc[e] = apply_op<Acc>(a.op, acc[e], v[e]);
+    for (int src = 0; src < kMaxRanks; ++src)
+      if (src < N && src != rank)
+        slots[src] = ld16(c.arena[rank] + recv_off + static_cast<size_t>(src) * slot_bytes + static_cast<size_t>(i) * 16);
+#pragma unroll
+    for (int src = 0; src < kMaxRanks; ++src) {
+      if (src < N && src != rank) {
+        const W* w = reinterpret_cast<const W*>(&slots[src]);
+#pragma unroll
+        for (int e = 0; e < E; ++e) acc[e] = apply_op<Acc>(a.op, acc[e], static_cast<Acc>(Elem<W>::up(w[e])));
+      }
     }
     if (a.op == OP_AVG) {
 #pragma unroll
@@ -157,33 +173,44 @@ __global__ void __launch_bounds__(kThreads) twoshot_kernel(DevComm c, CollArgs a
       cta_end(c, vr, s);
       return;
     }
-    // Phase 3: pull every other rank's reduced chunk.  All loads of one pack
-    // index are issued before the stores so that N-1 remote reads are in flight.
-    for (long long i = pb + threadIdx.x; i < pe; i += blockDim.x) {
-      uint4 raw[kMaxRanks - 1];
+    // Phase 3: pull every other rank's reduced chunk.  All loads of a batch are
+    // issued before its stores; small worlds batch several packs per peer so that
+    // about eight remote reads are in flight per thread whatever N is.
+    auto pull = [&](auto u_tag, auto p_tag) {
+      constexpr int PU = decltype(u_tag)::value, PP = decltype(p_tag)::value;
+      for (long long i0 = pb + threadIdx.x; i0 < pe; i0 += static_cast<long long>(blockDim.x) * PU) {
+        uint4 raw[PU][PP];
 #pragma unroll
-      for (int k = 1; k < kMaxRanks; ++k) {
-        if (k < N) {
-          const int p = (rank + k) % N;
-          raw[k - 1] = *reinterpret_cast<const uint4*>(c.arena[p] + red_off + static_cast<size_t>(i) * 16);
+        for (int u = 0; u < PU; ++u) {
+          const long long i = i0 + static_cast<long long>(u) * blockDim.x;
+#pragma unroll
+          for (int k = 1; k <= PP; ++k)
+            if (k < N && i < pe) raw[u][k - 1] = ld16(c.arena[(rank + k) % N] + red_off + static_cast<size_t>(i) * 16);
         }
-      }
 #pragma unroll
-      for (int k = 1; k < kMaxRanks; ++k) {
-        if (k < N) {
-          const int p = (rank + k) % N;
-          const long long e0 = static_cast<long long>(p) * per + i * E;
-          const int nv = valid_in_pack(e0, chunk_limit(p), E);
-          if (nv > 0) {
-            Acc v[E];
-            const W* w = reinterpret_cast<const W*>(&raw[k - 1]);
+        for (int u = 0; u < PU; ++u) {
+          const long long i = i0 + static_cast<long long>(u) * blockDim.x;
 #pragma unroll
-            for (int e = 0; e < E; ++e) v[e] = static_cast<Acc>(Elem<W>::up(w[e]));
-            store_pack<T, E, Acc>(out + e0, v, nv, aligned16(out + e0));
+          for (int k = 1; k <= PP; ++k) {
+            if (k < N && i < pe) {
+              const int p = (rank + k) % N;
+              const long long e0 = static_cast<long long>(p) * per + i * E;
+              const int nv = valid_in_pack(e0, chunk_limit(p), E);
+              if (nv > 0) {
+                Acc v[E];
+                const W* w = reinterpret_cast<const W*>(&raw[u][k - 1]);
+#pragma unroll
+                for (int e = 0; e < E; ++e) v[e] = static_cast<Acc>(Elem<W>::up(w[e]));
+                store_pack<T, E, Acc>(out + e0, v, nv, aligned16(out + e0));
+              }
+            }
           }
         }
       }
-    }
+    };
+    if (N <= 2) pull(std::integral_constant<int, 8>{}, std::integral_constant<int, 1>{});
+    else if (N <= 4) pull(std::integral_constant<int, 3>{}, std::integral_constant<int, 3>{});
+    else pull(std::integral_constant<int, 1>{}, std::integral_constant<int, kMaxRanks - 1>{});
     cta_end(c, vr, s);
   }
 }
@@ -542,15 +569,25 @@ __global__ void __launch_bounds__(kThreads) nvls_kernel(DevComm c, CollArgs a, c
   // Phase 1: reduce chunk `rank` in the switch and broadcast it back.
   cta_span(per / WE, pb, pe);
   const size_t chunk_byte0 = static_cast<size_t>(rank) * per * sizeof(W);
-  for (long long i = pb + threadIdx.x; i < pe; i += blockDim.x) {
-    const size_t off = chunk_byte0 + static_cast<size_t>(i) * 16;
-    uint4 v = Multimem<W>::ld_reduce(stage_mc + off);
-    if (a.op == OP_AVG) {
-      W* w = reinterpret_cast<W*>(&v);
+  constexpr int NU = 4;  // in-switch reductions in flight per thread
+  for (long long i0 = pb + threadIdx.x; i0 < pe; i0 += static_cast<long long>(blockDim.x) * NU) {
+    uint4 v[NU];
 #pragma unroll
-      for (int e = 0; e < WE; ++e) w[e] = Elem<W>::down(Elem<W>::up(w[e]) * a.inv_world);
+    for (int u = 0; u < NU; ++u) {
+      const long long i = i0 + static_cast<long long>(u) * blockDim.x;
+      if (i < pe) v[u] = Multimem<W>::ld_reduce(stage_mc + chunk_byte0 + static_cast<size_t>(i) * 16);
     }
-    multimem_st16(result_mc + off, v);
+#pragma unroll
+    for (int u = 0; u < NU; ++u) {
+      const long long i = i0 + static_cast<long long>(u) * blockDim.x;
+      if (i >= pe) continue;
+      if (a.op == OP_AVG) {
+        W* w = reinterpret_cast<W*>(&v[u]);
+#pragma unroll
+        for (int e = 0; e < WE; ++e) w[e] = Elem<W>::down(Elem<W>::up(w[e]) * a.inv_world);
+      }
+      multimem_st16(result_mc + chunk_byte0 + static_cast<size_t>(i) * 16, v[u]);
+    }
   }
   if (barrier_all(c, 0, rank, s, PH_NVLS)) {
     cta_end(c, 0, s);
