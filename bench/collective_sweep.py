@@ -58,7 +58,7 @@ def main() -> None:
     ap.add_argument("--max-mb", type=float, default=1024.0)
     ap.add_argument("--min-kb", type=float, default=1.0)
     ap.add_argument("--ops", default="allreduce,allgather,reduce_scatter,alltoall")
-    ap.add_argument("--algos", default="oneshot,twoshot,ring,tree,nvls,auto")
+    ap.add_argument("--algos", default="oneshot,twoshot,ring,tree,nvls,symm,auto")
     ap.add_argument("--dtypes", default="fp32,fp32+bf16wire,bf16")
     ap.add_argument("--out", default="")
     args = ap.parse_args()
@@ -80,6 +80,7 @@ def main() -> None:
         sizes.append(s)
         s *= 2
     rows = []
+    symm_cache = {}
     ops = args.ops.split(",")
     for op in ops:
         for dt_name in args.dtypes.split(","):
@@ -90,6 +91,8 @@ def main() -> None:
             es = 2 if dtype == torch.bfloat16 else 4
             for nbytes in sizes:
                 numel = max(world, nbytes // es // world * world)
+                if op == "allgather":
+                    numel = max(1, numel // world)   # per-rank input; the gathered buffer has `nbytes`
                 pool = max(1, min(16, (256 << 20) // max(nbytes, 1)))
                 g = torch.Generator(device="cpu").manual_seed(rank)
                 base = torch.randn(min(numel, 1 << 20), generator=g).to(dtype)
@@ -104,11 +107,21 @@ def main() -> None:
                 variants = []
                 if op == "allreduce":
                     for algo in args.algos.split(","):
+                        if algo == "symm":
+                            continue
                         if algo == "nvls" and not comm.nvls_available:
                             continue
                         if algo in ("oneshot", "tree") and nbytes > (64 << 20):
                             continue  # latency schedules: not meaningful (and arena-bound) for huge messages
                         variants.append((f"mccl:{algo}", lambda a=algo: (lambda t: comm.allreduce([t], [t], op="sum", algo=a, wire=wire))(nxt())))
+                    if wire == "native" and nbytes >= (64 << 10) and "symm" in args.algos.split(","):
+                        # buffer registered in the symmetric heap: reduced in place, no staging copies
+                        padded = ((numel + world - 1) // world + 15) // 16 * 16 * world
+                        if nbytes not in symm_cache:
+                            symm_cache.clear()
+                            symm_cache[nbytes] = comm.symm_alloc(padded * es)
+                        sb = symm_cache[nbytes]
+                        variants.append(("mccl:symm", lambda: comm.allreduce_symm(sb, 0, numel, dtype, "sum")))
                     if wire == "native":
                         variants.append(("nccl", lambda: dist.all_reduce(nxt(), group=nccl)))
                 elif op == "allgather":
@@ -129,7 +142,8 @@ def main() -> None:
                 for name, fn in variants:
                     us = timed(fn, iters, device)
                     comm.check_status()
-                    msg = numel * es
+                    # message size in the nccl-tests sense: the full gathered buffer for allgather
+                    msg = numel * es * (world if op == "allgather" else 1)
                     busbw = msg / (us * 1e-6) / 1e9 * bus_factor(op, world)
                     row = {"op": op, "dtype": dt_name, "bytes": msg, "impl": name, "us": round(us, 2),
                            "busbw_gbs": round(busbw, 2), "frac_of_900": round(busbw / NVLINK_GBS, 3), "world": world}

@@ -69,6 +69,7 @@ struct DeviceComm::Impl {
   size_t half_bytes = 0;
   unsigned long long timeout_ns = 0;
   int max_ctas = 32;
+  int64_t nvls_above = 0;  // AUTO uses staged NVLS at or above this many wire bytes (0 = never)
 
   dev::DevComm ctx(int world, int rank_base, int nlocal, int channel) const {
     dev::DevComm c{};
@@ -118,6 +119,7 @@ void DeviceComm::init_common() {
   impl_->timeout_ns = static_cast<unsigned long long>(std::max<int64_t>(cfg_.device_timeout_ms, 1)) * 1000000ull;
   int cap = cfg_.max_ctas > 0 ? cfg_.max_ctas : 32;
   impl_->max_ctas = std::min(cap, dev::kMaxCtas);
+  impl_->nvls_above = env::i64("MCCL_NVLS_ABOVE", 0);
   if (nlocal_ > 1) impl_->max_ctas = std::max(1, std::min(impl_->max_ctas, 96 / nlocal_));  // all virtual ranks co-resident
   if (mesh_->mode() != SymmMesh::Mode::LOCAL) mesh_->store_barrier("devcomm-ready");
 }
@@ -185,8 +187,13 @@ Algo DeviceComm::decide_allreduce(Algo requested, size_t numel, DType t, RedOp o
                        (t == DType::F32 || t == DType::F16 || t == DType::BF16);
   Algo a = requested;
   if (a == Algo::AUTO) {
+    // Measured on 8 x B200: one-shot wins up to a few hundred KB, two-shot above.  The
+    // staged NVLS schedule pays two local copies and only wins when asked for by the
+    // tuning table (MCCL_NVLS_ABOVE, wire bytes); buffers that already live in the
+    // symmetric heap take the copy-free NVLS path through allreduce_symm instead.
     if (static_cast<int64_t>(wire_bytes) <= tree_below) a = Algo::ONESHOT;
-    else a = nvls_ok ? Algo::NVLS : Algo::BUTTERFLY;
+    else a = (nvls_ok && impl_->nvls_above > 0 && static_cast<int64_t>(wire_bytes) >= impl_->nvls_above) ? Algo::NVLS
+                                                                                                        : Algo::BUTTERFLY;
   }
   if (a == Algo::NVLS && !nvls_ok) a = Algo::BUTTERFLY;
   if (a == Algo::RING && numel < static_cast<size_t>(world_)) a = Algo::TREE;
@@ -403,9 +410,9 @@ void DeviceComm::alltoallv(const void* const* ins, void* const* outs, const std:
   cfg.nlocal = nlocal_;
   cfg.stream = static_cast<cudaStream_t>(stream);
   cfg.ctas = ctas_for(longest, impl_->max_ctas);
-  // The CTA count must agree across ranks although segment sizes differ: it
-  // is a function of the slot size only when sizes are uneven.
-  cfg.ctas = std::min(impl_->max_ctas, 16);
+  // The CTA count must agree across ranks although segment sizes differ, so it
+  // cannot depend on this rank's sizes.
+  cfg.ctas = impl_->max_ctas;
   dev::DevComm c = impl_->ctx(world_, rank_, nlocal_, 0);
   cudaError_t rc = dev::launch_alltoall(c, a, cfg);
   MCCL_CHECK_T(rc == cudaSuccess, CudaError, "alltoall launch failed: " << cudaGetErrorString(rc));

@@ -41,7 +41,8 @@ def _allreduce_all(rank, world):
                 torch.cuda.synchronize()
                 be.check_device_status()
                 err = ((t.double().cpu() - gold).abs().max() / gold.abs().max().clamp_min(1.0)).item()
-                assert err <= (1e-2 if wire else 1e-5), (algo, wire, n, err)
+                # tree rounds its partial sums to bf16 at every level: allow for log2(world) roundings
+                assert err <= (2.5e-2 if wire else 1e-5), (algo, wire, n, err)
                 gathered = [torch.empty_like(t) for _ in range(world)]
                 dist.all_gather(gathered, t)
                 assert all(torch.equal(g, gathered[0]) for g in gathered), (algo, wire, n, "ranks differ")
