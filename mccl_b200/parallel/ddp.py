@@ -7,8 +7,6 @@ communication hook that sends fp32 gradient buckets as bf16 on the wire with
 fp32 accumulation and the 1/world scale fused into the same kernel, which is
 what ``MCCL_WIRE_DTYPE=bf16`` selects globally.
 """
-from __future__ import annotations
-
 import contextlib
 import os
 
@@ -33,7 +31,7 @@ def wire_dtype(name: str):
             os.environ["MCCL_WIRE_DTYPE"] = old
 
 
-def bf16_wire_hook(group, bucket: dist.GradBucket) -> torch.futures.Future:
+def bf16_wire_hook(group, bucket: dist.GradBucket) -> torch.futures.Future[torch.Tensor]:
     """``model.register_comm_hook(group, bf16_wire_hook)``: averaged gradients, bf16 on the wire."""
     buf = bucket.buffer()
     with wire_dtype("bf16" if buf.dtype == torch.float32 else ""):
