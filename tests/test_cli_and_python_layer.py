@@ -40,9 +40,11 @@ def test_tuning_table_crossover(tmp_path, monkeypatch):
     monkeypatch.setenv("MCCL_TUNING_FILE", path)
     monkeypatch.delenv("MCCL_TREE_BELOW", raising=False)
     applied = tuning.apply_nvlink_production_defaults(training_defaults=True)
-    assert applied["MCCL_TREE_BELOW"] == str(1 << 20) and os.environ["DDP_BUCKET_MB"] == "25"
-    for k in applied:
-        monkeypatch.delenv(k, raising=False)
+    try:
+        assert applied["MCCL_TREE_BELOW"] == str(1 << 20) and os.environ["DDP_BUCKET_MB"] == "25"
+    finally:
+        for k in applied:      # set directly in os.environ by the call above: remove them the same way
+            os.environ.pop(k, None)
 
 
 def test_model_parallel_plan_splits():
