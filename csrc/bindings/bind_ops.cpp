@@ -8,6 +8,9 @@
 
 #include "../core/errors.hpp"
 #include "../ops/ops.hpp"
+#include "../ops/tp_gemm.hpp"
+#include "../pg/device_comm.hpp"
+#include "../symm/symm_mesh.hpp"
 #include "bind.hpp"
 
 namespace py = pybind11;
@@ -216,6 +219,61 @@ void bind_ops(py::module_& m) {
       py::arg("logits"), py::arg("targets"), py::arg("grad_scale") = 1.0,
       "Returns per-row losses; overwrites logits with (softmax - onehot) * grad_scale.");
 
+  // ---- tensor-parallel GEMMs fused with their collective ----
+  py::class_<ops::TpGemm>(m, "TpGemm")
+      .def(py::init<std::shared_ptr<DeviceComm>, size_t>(), py::arg("comm"), py::arg("max_rs_elems"),
+           py::call_guard<py::gil_scoped_release>())
+      .def_property_readonly("world", &ops::TpGemm::world)
+      .def_property_readonly("rank", &ops::TpGemm::rank)
+      .def("status", &ops::TpGemm::status)
+      .def("check_status", &ops::TpGemm::check_status)
+      .def(
+          "ag_gemm",
+          [](ops::TpGemm& t, std::shared_ptr<SymmAlloc> x_sym, int64_t x_off, int64_t rows_local, const at::Tensor& w, bool w_kn,
+             const c10::optional<at::Tensor>& bias, const std::string& epilogue) {
+            need_cuda(w, "ag_gemm(w)");
+            MCCL_CHECK_TENSOR(w.scalar_type() == at::kBFloat16 && w.dim() == 2 && w.stride(1) == 1, "ag_gemm: w must be 2-D bf16");
+            c10::cuda::CUDAGuard guard(w.device());
+            const int64_t K = w_kn ? w.size(0) : w.size(1), N = w_kn ? w.size(1) : w.size(0);
+            const int64_t rows = rows_local * t.world();
+            at::Tensor y = at::empty({rows, N}, w.options());
+            at::Tensor gathered = at::empty({rows, K}, w.options());
+            const float* bp = nullptr;
+            if (bias.has_value() && bias->defined()) {
+              need(*bias, at::kFloat, "ag_gemm(bias)");
+              bp = bias->data_ptr<float>();
+            }
+            const int epi = parse_epilogue(epilogue, bp != nullptr);
+            at::Tensor aux;
+            if (epi == ops::EPI_BIAS_GELU || epi == ops::EPI_GELU) aux = at::empty({rows, N}, w.options());
+            t.ag_gemm(*x_sym, static_cast<size_t>(x_off), static_cast<int>(rows_local), static_cast<int>(K), bf(w),
+                      static_cast<int>(w.stride(0)), w_kn, static_cast<int>(N), bf(y), bf(gathered), bp, epi,
+                      aux.defined() ? bf(aux) : nullptr, stream_of(w));
+            ops::count_launch(1);
+            return std::make_tuple(y, gathered, aux.defined() ? c10::optional<at::Tensor>(aux) : c10::nullopt);
+          },
+          py::arg("x_sym"), py::arg("x_offset"), py::arg("rows_local"), py::arg("w"), py::arg("w_kn") = false,
+          py::arg("bias") = py::none(), py::arg("epilogue") = "none",
+          "Returns (all_gather(x) @ w^T, gathered x, pre-activation or None).")
+      .def(
+          "gemm_rs",
+          [](ops::TpGemm& t, const at::Tensor& x, const at::Tensor& w, bool w_kn) {
+            need_cuda(x, "gemm_rs(x)");
+            need_cuda(w, "gemm_rs(w)");
+            MCCL_CHECK_TENSOR(x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.stride(1) == 1, "gemm_rs: x must be 2-D bf16");
+            MCCL_CHECK_TENSOR(w.scalar_type() == at::kBFloat16 && w.dim() == 2 && w.stride(1) == 1, "gemm_rs: w must be 2-D bf16");
+            c10::cuda::CUDAGuard guard(x.device());
+            const int64_t K = w_kn ? w.size(0) : w.size(1), N = w_kn ? w.size(1) : w.size(0);
+            MCCL_CHECK_TENSOR(x.size(1) == K && x.size(0) % t.world() == 0, "gemm_rs: shapes [world*rows, K] x [N, K] expected");
+            const int64_t rows_local = x.size(0) / t.world();
+            at::Tensor out = at::empty({rows_local, N}, x.options());
+            t.gemm_rs(bf(x), static_cast<int>(x.stride(0)), static_cast<int>(rows_local), static_cast<int>(K), bf(w),
+                      static_cast<int>(w.stride(0)), w_kn, static_cast<int>(N), bf(out), stream_of(x));
+            ops::count_launch(1);
+            return out;
+          },
+          py::arg("x"), py::arg("w"), py::arg("w_kn") = false, "Returns this rank's rows of reduce_scatter(x @ w^T).");
+
   m.def("colsum_bf16", [](const at::Tensor& x, const c10::optional<at::Tensor>& out_opt, bool accumulate) {
     need(x, at::kBFloat16, "colsum(x)");
     MCCL_CHECK_TENSOR(x.dim() == 2, "colsum: 2-D tensor expected");
@@ -266,6 +324,43 @@ void bind_ops(py::module_& m) {
     check_launch(ops::gelu_bwd(bf(dy), bf(z), bf(dz), dy.numel(), stream_of(dy)), "gelu_bwd");
     return dz;
   });
+  m.def("embed_fwd", [](const at::Tensor& ids, const at::Tensor& tok, const c10::optional<at::Tensor>& pos, int64_t seq) {
+    need(ids, at::kLong, "embed_fwd(ids)");
+    need(tok, at::kFloat, "embed_fwd(tok)");
+    MCCL_CHECK_TENSOR(tok.dim() == 2 && tok.size(1) % 8 == 0, "embed_fwd: table [vocab, dim] with dim % 8 == 0 expected");
+    const float* pp = nullptr;
+    if (pos.has_value() && pos->defined()) {
+      need(*pos, at::kFloat, "embed_fwd(pos)");
+      MCCL_CHECK_TENSOR(pos->dim() == 2 && pos->size(1) == tok.size(1) && pos->size(0) >= seq, "embed_fwd: position table too small");
+      pp = pos->data_ptr<float>();
+    }
+    c10::cuda::CUDAGuard guard(ids.device());
+    at::Tensor y = at::empty({ids.numel(), tok.size(1)}, tok.options().dtype(at::kBFloat16));
+    check_launch(ops::embed_fwd(reinterpret_cast<const long long*>(ids.data_ptr<int64_t>()),
+                                tok.data_ptr<float>(), pp, bf(y), static_cast<int>(ids.numel()), static_cast<int>(seq),
+                                static_cast<int>(tok.size(1)), static_cast<int>(tok.size(0)), stream_of(ids)),
+                 "embed_fwd");
+    return y;
+  }, py::arg("ids"), py::arg("tok"), py::arg("pos") = py::none(), py::arg("seq") = 1);
+  m.def("embed_bwd", [](const at::Tensor& ids, const at::Tensor& dy, at::Tensor dtok, const c10::optional<at::Tensor>& dpos,
+                        int64_t seq) {
+    need(ids, at::kLong, "embed_bwd(ids)");
+    need(dy, at::kBFloat16, "embed_bwd(dy)");
+    need(dtok, at::kFloat, "embed_bwd(dtok)");
+    MCCL_CHECK_TENSOR(dtok.dim() == 2 && dtok.size(1) % 8 == 0 && dy.numel() == ids.numel() * dtok.size(1),
+                      "embed_bwd: dy must be [tokens, dim] and dtok [vocab, dim] with dim % 8 == 0");
+    float* pp = nullptr;
+    if (dpos.has_value() && dpos->defined()) {
+      need(*dpos, at::kFloat, "embed_bwd(dpos)");
+      MCCL_CHECK_TENSOR(dpos->dim() == 2 && dpos->size(1) == dtok.size(1) && dpos->size(0) >= seq, "embed_bwd: position table too small");
+      pp = dpos->data_ptr<float>();
+    }
+    c10::cuda::CUDAGuard guard(ids.device());
+    check_launch(ops::embed_bwd(reinterpret_cast<const long long*>(ids.data_ptr<int64_t>()), bf(dy), dtok.data_ptr<float>(), pp,
+                                static_cast<int>(ids.numel()), static_cast<int>(seq), static_cast<int>(dtok.size(1)),
+                                static_cast<int>(dtok.size(0)), stream_of(ids)),
+                 "embed_bwd");
+  }, py::arg("ids"), py::arg("dy"), py::arg("dtok"), py::arg("dpos") = py::none(), py::arg("seq") = 1);
 }
 
 }  // namespace mccl

@@ -495,6 +495,78 @@ cudaError_t gelu_bwd(const __nv_bfloat16* dy, const __nv_bfloat16* z, __nv_bfloa
   return cudaGetLastError();
 }
 
+// ------------------------------------------------------------ embedding ---
+// One thread per 8 output elements; ids outside [0, vocab) read row 0 and add nothing.
+__global__ void __launch_bounds__(256) embed_fwd_kernel(const long long* __restrict__ ids, const float* __restrict__ tok,
+                                                        const float* __restrict__ pos, __nv_bfloat16* __restrict__ y, long long n8,
+                                                        int seq, int dim8, int vocab) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n8;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long t = i / dim8;
+    const int c = static_cast<int>(i % dim8);
+    long long id = ids[t];
+    if (id < 0 || id >= vocab) id = 0;
+    const float4* row = reinterpret_cast<const float4*>(tok + id * dim8 * 8) + 2 * c;
+    float4 a = row[0], b = row[1];
+    if (pos != nullptr) {
+      const float4* prow = reinterpret_cast<const float4*>(pos + (t % seq) * dim8 * 8) + 2 * c;
+      const float4 pa = prow[0], pb = prow[1];
+      a.x += pa.x, a.y += pa.y, a.z += pa.z, a.w += pa.w;
+      b.x += pb.x, b.y += pb.y, b.z += pb.z, b.w += pb.w;
+    }
+    const float o[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    reinterpret_cast<uint4*>(y)[i] = pack8(o);
+  }
+}
+
+__global__ void __launch_bounds__(256) embed_bwd_kernel(const long long* __restrict__ ids, const __nv_bfloat16* __restrict__ dy,
+                                                        float* __restrict__ dtok, float* __restrict__ dpos, long long n8, int seq,
+                                                        int dim8, int vocab) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n8;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long t = i / dim8;
+    const int c = static_cast<int>(i % dim8);
+    float g[8];
+    unpack8(reinterpret_cast<const uint4*>(dy)[i], g);
+    const float4 lo = make_float4(g[0], g[1], g[2], g[3]), hi = make_float4(g[4], g[5], g[6], g[7]);
+    const long long id = ids[t];
+    if (id >= 0 && id < vocab) {
+      float4* row = reinterpret_cast<float4*>(dtok + id * dim8 * 8) + 2 * c;
+      atomicAdd(row, lo);
+      atomicAdd(row + 1, hi);
+    }
+    if (dpos != nullptr) {
+      float4* prow = reinterpret_cast<float4*>(dpos + (t % seq) * dim8 * 8) + 2 * c;
+      atomicAdd(prow, lo);
+      atomicAdd(prow + 1, hi);
+    }
+  }
+}
+
+static int embed_blocks(long long n8) {
+  long long blocks = (n8 + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  return blocks < 1 ? 1 : static_cast<int>(blocks);
+}
+
+cudaError_t embed_fwd(const long long* ids, const float* tok, const float* pos, __nv_bfloat16* y, int tokens, int seq, int dim,
+                      int vocab, cudaStream_t stream) {
+  if (dim % 8 != 0 || tokens <= 0 || seq <= 0) return cudaErrorNotSupported;
+  const long long n8 = static_cast<long long>(tokens) * (dim / 8);
+  embed_fwd_kernel<<<embed_blocks(n8), 256, 0, stream>>>(ids, tok, pos, y, n8, seq, dim / 8, vocab);
+  count_launch();
+  return cudaGetLastError();
+}
+
+cudaError_t embed_bwd(const long long* ids, const __nv_bfloat16* dy, float* dtok, float* dpos, int tokens, int seq, int dim,
+                      int vocab, cudaStream_t stream) {
+  if (dim % 8 != 0 || tokens <= 0 || seq <= 0) return cudaErrorNotSupported;
+  const long long n8 = static_cast<long long>(tokens) * (dim / 8);
+  embed_bwd_kernel<<<embed_blocks(n8), 256, 0, stream>>>(ids, dy, dtok, dpos, n8, seq, dim / 8, vocab);
+  count_launch();
+  return cudaGetLastError();
+}
+
 }  // namespace ops
 }  // namespace mccl
 

@@ -35,27 +35,163 @@ struct PLayout {
   static constexpr int kTotal = kTiles + kBarriers + 1024;
 };
 
-// Bounded wait that also gives up when another role of this CTA has failed.
-__device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-  for (uint32_t i = 0; i < (1u << 22); ++i) {
+__device__ __forceinline__ unsigned long long now_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Bounded wait that also gives up when another role of this CTA has failed.  The limit is a
+// time (the fused roles legitimately wait for other GPUs), read only once the fast path missed.
+__device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag, unsigned long long limit_ns) {
+  for (int i = 0; i < 64; ++i)
     if (tc::mbar_try_wait(bar, parity)) return true;
-    if ((i & 255u) == 255u && *abort_flag) return false;
+  const unsigned long long t0 = now_ns();
+  for (uint32_t i = 0;; ++i) {
+    if (tc::mbar_try_wait(bar, parity)) return true;
+    if ((i & 255u) == 255u) {
+      if (*abort_flag) return false;
+      if (now_ns() - t0 > limit_ns) return false;
+    }
   }
-  return false;
 }
 
 // Spin on a flag word in global memory written by another CTA of this GPU (chunk
 // arrival in the all-gather fusion).  Bounded; false on timeout.
-__device__ __forceinline__ bool wait_flag_geq(const uint32_t* flag, uint32_t value, volatile int* abort_flag) {
-  for (uint32_t i = 0; i < (1u << 24); ++i) {
+__device__ __forceinline__ bool wait_flag_geq(const uint32_t* flag, uint32_t value, volatile int* abort_flag, unsigned long long limit_ns) {
+  const unsigned long long t0 = now_ns();
+  for (uint32_t i = 0;; ++i) {
     uint32_t v;
     asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
     if (static_cast<int32_t>(v - value) >= 0) return true;
-    if ((i & 255u) == 255u && *abort_flag) return false;
+    if ((i & 63u) == 63u) {
+      if (*abort_flag) return false;
+      if (now_ns() - t0 > limit_ns) return false;
+    }
     __nanosleep(64);
   }
-  return false;
 }
+
+
+// ---- cross-GPU signalling for the fused roles (bounded waits, status word on timeout) ----
+__device__ __forceinline__ void sig_store(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ bool sig_wait(const uint32_t* p, uint32_t v, unsigned long long timeout_ns) {
+  unsigned long long t0;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+  for (unsigned spins = 0;; ++spins) {
+    uint32_t cur;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(cur) : "l"(p) : "memory");
+    if (static_cast<int32_t>(cur - v) >= 0) return true;
+    if ((spins & 63u) == 63u) {
+      unsigned long long t;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+      if (t - t0 > timeout_ns) return false;
+    }
+  }
+}
+// Meeting of copy CTA `cta` of every rank.  Returns false when a peer did not arrive in time.
+__device__ __forceinline__ bool copy_cta_meet(const FusedDev& f, int cta, uint32_t value) {
+  __syncthreads();
+  bool bad = false;
+  const int t = threadIdx.x;
+  if (t < f.world) {
+    __threadfence_system();
+    sig_store(f.sig[t] + 8 + 8 * cta + f.rank, value);
+    bad = !sig_wait(f.sig[f.rank] + 8 + 8 * cta + t, value, f.timeout_ns);
+    if (bad) atomicCAS(f.status, 0, 0x100 + t);
+  }
+  return __syncthreads_or(bad ? 1 : 0) == 0;
+}
+// 16-byte copy of [b0, b1) by the whole CTA with four transfers in flight per thread.
+__device__ __forceinline__ void cta_copy16(char* dst, const char* src, unsigned long long b0, unsigned long long b1) {
+  const unsigned long long v0 = b0 / 16, v1 = b1 / 16;
+  unsigned long long i = v0 + threadIdx.x;
+  for (; i + 3ull * blockDim.x < v1; i += 4ull * blockDim.x) {
+    const uint4 a = reinterpret_cast<const uint4*>(src)[i], b = reinterpret_cast<const uint4*>(src)[i + blockDim.x];
+    const uint4 c = reinterpret_cast<const uint4*>(src)[i + 2ull * blockDim.x], d = reinterpret_cast<const uint4*>(src)[i + 3ull * blockDim.x];
+    reinterpret_cast<uint4*>(dst)[i] = a;
+    reinterpret_cast<uint4*>(dst)[i + blockDim.x] = b;
+    reinterpret_cast<uint4*>(dst)[i + 2ull * blockDim.x] = c;
+    reinterpret_cast<uint4*>(dst)[i + 3ull * blockDim.x] = d;
+  }
+  for (; i < v1; i += blockDim.x) reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(src)[i];
+}
+
+// Role of CTAs [0, copy_ctas) in the all-gather fusion: meet the peers (their shards are
+// complete), pull the shards chunk by chunk starting with the own one, raise a chunk's flag
+// when every copy CTA has finished it, meet again (nobody reads my shard any more).
+__device__ void allgather_copy_role(const FusedDev& f, uint32_t epoch) {
+  const int cta = blockIdx.x;
+  if (!copy_cta_meet(f, cta, 2 * epoch - 1)) return;
+  const unsigned long long units = f.chunk_bytes / 16;
+  const unsigned long long per = (units + f.copy_ctas - 1) / f.copy_ctas;
+  unsigned long long b0 = cta * per * 16, b1 = b0 + per * 16;
+  if (b0 > f.chunk_bytes) b0 = f.chunk_bytes;
+  if (b1 > f.chunk_bytes) b1 = f.chunk_bytes;
+  for (int k = 0; k < f.world; ++k) {
+    const int c = (f.rank + k) % f.world;
+    cta_copy16(static_cast<char*>(f.a_gathered) + static_cast<size_t>(c) * f.chunk_bytes, static_cast<const char*>(f.a_peer[c]), b0, b1);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence();
+      const uint32_t arrived = atomicAdd(f.chunk_counters + c, 1u) + 1u;
+      if (arrived == static_cast<uint32_t>(f.copy_ctas) * epoch)
+        asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(f.chunk_flags + c), "r"(epoch) : "memory");
+    }
+  }
+  copy_cta_meet(f, cta, 2 * epoch);
+}
+
+// Tail of the reduce-scatter fusion, run by every GEMM CTA after its tiles: tell the peers when
+// this rank's last CTA has pushed its partial tiles, wait for every peer's tell, then reduce
+// the world slots of my chunk (fp32 accumulation, fixed rank order) into the bf16 result.
+__device__ void reduce_scatter_tail(const FusedDev& f, const GemmDev& g, uint32_t epoch, int gcta, int gctas) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    const uint32_t done = atomicAdd(f.done_counter, 1u) + 1u;
+    if (done == static_cast<uint32_t>(gctas) * epoch)
+      for (int p = 0; p < f.world; ++p) sig_store(f.sig[p] + f.rank, epoch);
+  }
+  bool bad = false;
+  if (threadIdx.x < f.world) {
+    bad = !sig_wait(f.sig[f.rank] + threadIdx.x, epoch, f.timeout_ns);
+    if (bad) atomicCAS(f.status, 0, 0x200 + static_cast<int>(threadIdx.x));
+  }
+  if (__syncthreads_or(bad ? 1 : 0)) return;
+  const size_t slot_elems = static_cast<size_t>(f.chunk_rows) * g.n;
+  const __nv_bfloat16* slots = static_cast<const __nv_bfloat16*>(f.rs_slots[epoch & 1u]);
+  __nv_bfloat16* out = static_cast<__nv_bfloat16*>(f.rs_out);
+  const size_t vecs = slot_elems / 8;
+  for (size_t i = static_cast<size_t>(gcta) * blockDim.x + threadIdx.x; i < vecs; i += static_cast<size_t>(gctas) * blockDim.x) {
+    uint4 raw[kFuseMaxRanks];
+#pragma unroll
+    for (int r = 0; r < kFuseMaxRanks; ++r)
+      if (r < f.world) raw[r] = reinterpret_cast<const uint4*>(slots + static_cast<size_t>(r) * slot_elems)[i];
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+    for (int r = 0; r < kFuseMaxRanks; ++r) {
+      if (r < f.world) {
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[r]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 t = __bfloat1622float2(h[j]);
+          acc[2 * j] += t.x;
+          acc[2 * j + 1] += t.y;
+        }
+      }
+    }
+    uint4 pk;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+    reinterpret_cast<uint4*>(out)[i] = pk;
+  }
+}
+
+__global__ void bump_epoch_kernel(uint32_t* epoch) { *epoch = *epoch + 1; }
 
 template <int BN, int STAGES, bool kAMn, bool kBMn>
 __global__ void __launch_bounds__(192, 1) gemm_persistent_kernel(const __grid_constant__ CUtensorMap tma_a,
@@ -72,6 +208,14 @@ __global__ void __launch_bounds__(192, 1) gemm_persistent_kernel(const __grid_co
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
+  const uint32_t epoch = f.mode != FUSE_NONE ? *f.epoch_ptr : 0u;
+  if (f.mode == FUSE_ALLGATHER_A && static_cast<int>(blockIdx.x) < f.copy_ctas) {
+    allgather_copy_role(f, epoch);   // these CTAs move data; the others compute
+    return;
+  }
+  // in-CTA waits: two seconds alone, the cross-GPU limit plus two seconds when a role waits for peers
+  const unsigned long long wait_ns = 2000000000ull + (f.mode != FUSE_NONE ? f.timeout_ns : 0ull);
+  const int gcta = static_cast<int>(blockIdx.x) - f.copy_ctas, gctas = static_cast<int>(gridDim.x) - f.copy_ctas;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m_tiles = (g.m + BM - 1) / BM, n_tiles = (g.n + BN - 1) / BN;
   // Split-K: a work item is (tile, k-slice); slices of one tile run on different SMs
@@ -114,17 +258,19 @@ __global__ void __launch_bounds__(192, 1) gemm_persistent_kernel(const __grid_co
     if (lane == 0) {
       bool ok = true;
       uint32_t it = 0;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      for (int t = gcta; t < total_tiles && ok; t += gctas) {
         int m_blk, n_blk, kb0;
         tile_coords(t, m_blk, n_blk, kb0);
         if (f.mode == FUSE_ALLGATHER_A) {
           const int chunk = (m_blk * BM) / f.chunk_rows;
-          if (chunk != f.rank) ok = wait_flag_geq(f.chunk_flags + chunk, f.epoch, abort_flag);
+          ok = wait_flag_geq(f.chunk_flags + chunk, epoch, abort_flag, wait_ns);
           if (!ok) break;
+          // the chunk was written with ordinary stores by other CTAs; TMA reads it through the async proxy
+          asm volatile("fence.proxy.async;" ::: "memory");
         }
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % STAGES;
-          if (it >= STAGES) ok = wait_or_abort(&empty[s], ((it / STAGES) - 1) & 1, abort_flag);
+          if (it >= STAGES) ok = wait_or_abort(&empty[s], ((it / STAGES) - 1) & 1, abort_flag, wait_ns);
           if (!ok) break;
           tc::mbar_expect_tx(&full[s], L::kStageBytes);
           uint8_t* a_dst = tiles + s * L::kStageBytes;
@@ -160,17 +306,17 @@ __global__ void __launch_bounds__(192, 1) gemm_persistent_kernel(const __grid_co
       bool ok = true;
       uint32_t it = 0;
       int i = 0;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++i) {
+      for (int t = gcta; t < total_tiles && ok; t += gctas, ++i) {
         const int buf = i & 1;
         if (i >= 2) {
-          ok = wait_or_abort(&acc_empty[buf], ((i >> 1) - 1) & 1, abort_flag);
+          ok = wait_or_abort(&acc_empty[buf], ((i >> 1) - 1) & 1, abort_flag, wait_ns);
           if (!ok) break;
           tc::fence_after_sync();
         }
         const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(buf * BN);
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % STAGES;
-          ok = wait_or_abort(&full[s], (it / STAGES) & 1, abort_flag);
+          ok = wait_or_abort(&full[s], (it / STAGES) & 1, abort_flag, wait_ns);
           if (!ok) break;
           tc::fence_after_sync();
           const uint8_t* a_tile = tiles + s * L::kStageBytes;
@@ -194,11 +340,11 @@ __global__ void __launch_bounds__(192, 1) gemm_persistent_kernel(const __grid_co
     const int quarter = warp & 3;
     bool ok = true;
     int i = 0;
-    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++i) {
+    for (int t = gcta; t < total_tiles; t += gctas, ++i) {
       int m_blk, n_blk, kb0;
       tile_coords(t, m_blk, n_blk, kb0);
       const int buf = i & 1;
-      ok = wait_or_abort(&acc_full[buf], (i >> 1) & 1, abort_flag);
+      ok = wait_or_abort(&acc_full[buf], (i >> 1) & 1, abort_flag, wait_ns);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc::fence_after_sync();
@@ -207,7 +353,7 @@ __global__ void __launch_bounds__(192, 1) gemm_persistent_kernel(const __grid_co
       if (f.mode == FUSE_REDUCE_SCATTER_D) {
         // the tile's rows belong to rank `owner`: store into that rank's staging slot for this rank
         const int owner = (m_blk * BM) / f.chunk_rows;
-        gt.d = static_cast<char*>(f.d_owner[owner]) -
+        gt.d = static_cast<char*>(f.d_owner[epoch & 1u][owner]) -
                static_cast<size_t>(owner) * f.chunk_rows * g.ldd * (g.d_fp32 ? 4 : 2);
       }
       const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(buf * BN) + (static_cast<uint32_t>(quarter * 32) << 16);
@@ -236,6 +382,7 @@ __global__ void __launch_bounds__(192, 1) gemm_persistent_kernel(const __grid_co
     tc::fence_after_sync();
     tc::tmem_dealloc(tmem_base, 2 * BN);
   }
+  if (f.mode == FUSE_REDUCE_SCATTER_D && *abort_flag == 0) reduce_scatter_tail(f, g, epoch, gcta, gctas);
 }
 
 int sm_count() {
@@ -324,13 +471,22 @@ cudaError_t launch_persistent_cfg(const GemmArgs& a, const FusedDev& f_in, int m
 no_split:
   int ctas = sm_count();
   if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
-  if (tiles < ctas) ctas = tiles;
-  gemm_persistent_kernel<BN, STAGES, kAMn, kBMn><<<ctas, 192, L::kTotal, stream>>>(ma, mb, g, f);
+  // fused roles wait on one another inside the kernel: every CTA must be resident (one per SM)
+  int gemm_ctas = ctas - f.copy_ctas;
+  if (gemm_ctas < 1) return cudaErrorInvalidValue;
+  if (tiles < gemm_ctas && f.mode != FUSE_REDUCE_SCATTER_D) gemm_ctas = tiles;
+  if (f.mode == FUSE_REDUCE_SCATTER_D && f.rs_gemm_ctas > 0) gemm_ctas = f.rs_gemm_ctas;  // fixed: the done counter depends on it
+  gemm_persistent_kernel<BN, STAGES, kAMn, kBMn><<<gemm_ctas + f.copy_ctas, 192, L::kTotal, stream>>>(ma, mb, g, f);
   count_launch();
   return cudaGetLastError();
 }
 
 }  // namespace
+
+cudaError_t launch_bump_epoch(uint32_t* epoch, cudaStream_t stream) {
+  bump_epoch_kernel<<<1, 1, 0, stream>>>(epoch);
+  return cudaGetLastError();
+}
 
 cudaError_t launch_gemm_persistent(const GemmArgs& a, const FusedDev& f, int max_ctas, cudaStream_t stream) {
   // Wide tiles when they still give every SM work; otherwise 128 x 128.

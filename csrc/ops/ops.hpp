@@ -53,6 +53,14 @@ cudaError_t cast_f32_bf16(const float* in, __nv_bfloat16* out, long long n, cuda
 // GELU backward on a pre-activation: dz = dy * gelu'(z).
 cudaError_t gelu_bwd(const __nv_bfloat16* dy, const __nv_bfloat16* z, __nv_bfloat16* dz, long long n, cudaStream_t stream);
 
+// ---- token (+ learned position) embedding.  y[t, :] = bf16(tok[ids[t], :] + pos[t % seq, :]);
+// tok / pos are fp32 [vocab, dim] / [>= seq, dim] (pos may be null); dim % 8 == 0.
+cudaError_t embed_fwd(const long long* ids, const float* tok, const float* pos, __nv_bfloat16* y, int tokens, int seq, int dim,
+                      int vocab, cudaStream_t stream);
+// Adds dy[t, :] into dtok[ids[t], :] and dpos[t % seq, :] (fp32, atomically; dpos may be null).
+cudaError_t embed_bwd(const long long* ids, const __nv_bfloat16* dy, float* dtok, float* dpos, int tokens, int seq, int dim,
+                      int vocab, cudaStream_t stream);
+
 // ---- tcgen05 GEMM: D[M,N] = A[M,K] · B[N,K]^T (+ bias[N]) (GELU) ; A, B bf16 with K contiguous.
 enum GemmEpilogue : int {
   EPI_NONE = 0,       // D = acc

@@ -172,10 +172,14 @@ class Decoder(nn.Module):
     def hidden(self, tokens: torch.Tensor) -> torch.Tensor:
         B, S = tokens.shape
         native = self._native(tokens)
-        x = self.tok(tokens)
-        if self.pos is not None:
-            x = x + self.pos.weight[:S]
-        x = x.to(torch.bfloat16)
+        if native:
+            from .. import ops
+            x = ops.embedding(tokens, self.tok.weight, None if self.pos is None else self.pos.weight)
+        else:
+            x = self.tok(tokens)
+            if self.pos is not None:
+                x = x + self.pos.weight[:S]
+            x = x.to(torch.bfloat16)
         rope = _rope_tables(S, self.cfg.head_dim, tokens.device) if self.cfg.pos == "rope" else None
         for blk in self.blocks:
             x = blk(x, rope, native)

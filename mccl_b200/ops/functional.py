@@ -7,7 +7,7 @@ import torch.nn.functional as F
 
 from .. import _C
 
-_HAS = {name: hasattr(_C, name) for name in ("gemm_bf16", "norm_fwd", "norm_bwd", "adamw_flat", "ce_fwd_bwd")}
+_HAS = {name: hasattr(_C, name) for name in ("gemm_bf16", "norm_fwd", "norm_bwd", "adamw_flat", "ce_fwd_bwd", "embed_fwd")}
 _launches = 0
 
 
@@ -39,6 +39,18 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias=None, act: str = "none", 
     y = F.linear(x, weight.to(x.dtype), None if bias is None else bias.to(x.dtype))
     y = F.gelu(y) if act == "gelu" else y
     return y if residual is None else y + residual
+
+
+def embedding(ids: torch.Tensor, tok: torch.Tensor, pos=None) -> torch.Tensor:
+    """bf16(tok[ids] + pos[:seq]) for ids [..., seq]; tok / pos are fp32 tables."""
+    seq = ids.shape[-1]
+    if ids.is_cuda and _HAS.get("embed_fwd") and tok.dtype == torch.float32 and tok.shape[1] % 8 == 0:
+        from .native import EmbeddingFn
+        return EmbeddingFn.apply(ids, tok, pos, seq)
+    x = F.embedding(ids, tok)
+    if pos is not None:
+        x = x + pos[:seq]
+    return x.to(torch.bfloat16)
 
 
 def linear_cross_entropy(h: torch.Tensor, weight: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:

@@ -181,3 +181,40 @@ class LinearCrossEntropyFn(torch.autograd.Function):
             else:
                 dw = (dlogits.t() @ h).float()
         return dh, dw, None
+
+
+class EmbeddingFn(torch.autograd.Function):
+    """bf16(tok[ids] + pos[position]) in one kernel; the backward adds the output gradient into the
+    fp32 gradient buffers of both tables (the trainer's sinks when there are any) with vector atomics,
+    so no sort, no dense zero-filled intermediate and no autograd accumulation step is needed."""
+
+    @staticmethod
+    def forward(ctx, ids, tok, pos, seq):
+        flat = ids.reshape(-1).contiguous()
+        y = _C.embed_fwd(flat, tok.detach(), None if pos is None else pos.detach(), seq)
+        ctx.save_for_backward(flat)
+        ctx.tok, ctx.pos, ctx.seq = tok, pos, seq
+        return y.view(*ids.shape, tok.shape[1])
+
+    @staticmethod
+    def backward(ctx, dy):
+        (flat,) = ctx.saved_tensors
+        tok, pos, seq = ctx.tok, ctx.pos, ctx.seq
+        dyc = dy.reshape(-1, tok.shape[1])
+        if not dyc.is_contiguous():
+            dyc = dyc.contiguous()
+        tsink = _sink(tok)
+        psink = _sink(pos) if pos is not None else None
+        dtok = tsink if tsink is not None else torch.zeros_like(tok, dtype=torch.float32)
+        dpos = None
+        if pos is not None:
+            dpos = psink if psink is not None else torch.zeros_like(pos, dtype=torch.float32)
+        _C.embed_bwd(flat, dyc, dtok, dpos, seq)
+        # this is the last contribution to a tied table's gradient, so it is the one that reports it
+        for p, sink in ((tok, tsink), (pos, psink)):
+            if p is not None and sink is not None:
+                cb = getattr(p, "_grad_ready", None)
+                if cb is not None:
+                    cb()
+        return None, (None if tsink is not None else dtok), (None if pos is None or psink is not None else dpos), None
+

@@ -30,10 +30,14 @@ from .. import _C, ops
 
 
 class _Bucket:
-    __slots__ = ("start", "numel", "pending", "total")
+    __slots__ = ("start", "numel", "pending", "total", "late")
 
     def __init__(self, start: int):
         self.start, self.numel, self.pending, self.total = start, 0, 0, 0
+        # True once a gradient of this bucket has arrived through autograd's own accumulation: such a
+        # bucket is reduced after backward() has returned (the engine has then joined the stream that
+        # accumulated it with the caller's stream), not from inside the hook.
+        self.late = False
 
 
 class DDPTrainer:
@@ -46,6 +50,7 @@ class DDPTrainer:
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.comm = None
+        self._late: List[_Bucket] = []
         if self.world > 1:
             import mccl_b200
             be = mccl_b200.get_backend(group)
@@ -112,7 +117,7 @@ class DDPTrainer:
             if self.world > 1:
                 # ... and say so; gradients that come back through autograd fire its hook instead
                 p._grad_ready = (lambda q=p: self._on_grad_ready(q))
-                p.register_post_accumulate_grad_hook(self._on_grad_ready)
+                p.register_post_accumulate_grad_hook(self._on_autograd_grad)
         # bf16 working copies of the parameters, refreshed by the optimizer kernel (the GEMMs
         # read them in either orientation, so no transposed copies are kept).
         self.flat_p16 = None
@@ -133,7 +138,14 @@ class DDPTrainer:
         b.pending += 1
         if b.pending == b.total:
             b.pending = 0
-            self._reduce_bucket(b)
+            if b.late:
+                self._late.append(b)
+            else:
+                self._reduce_bucket(b)
+
+    def _on_autograd_grad(self, p: torch.Tensor) -> None:
+        self.buckets[self._param_bucket[p]].late = True
+        self._on_grad_ready(p)
 
     def _reduce_bucket(self, b: _Bucket) -> None:
         main = torch.cuda.current_stream(self.device)
@@ -153,6 +165,9 @@ class DDPTrainer:
         self.flat_g.zero_()
         loss = self.model(tokens, targets)
         loss.backward()
+        for b in self._late:
+            self._reduce_bucket(b)
+        self._late.clear()
         if self.comm_stream is not None and self.overlap:
             torch.cuda.current_stream(self.device).wait_stream(self.comm_stream)
         self.step_t.add_(1.0)

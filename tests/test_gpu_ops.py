@@ -194,3 +194,26 @@ def test_direct_gradient_sinks_match_autograd():
     for (n, pa), (_, pb) in zip(a.named_parameters(), b.named_parameters()):
         denom = pb.grad.abs().max().clamp_min(1e-6)
         assert ((pa.grad - pb.grad).abs().max() / denom).item() < 1e-3, n
+
+
+@pytest.mark.parametrize("with_pos", [True, False])
+def test_embedding_forward_backward(with_pos):
+    from mccl_b200 import ops
+    torch.manual_seed(5)
+    V, D, B, S = 300, 64, 3, 17
+    tok = torch.randn(V, D, device="cuda", requires_grad=True)
+    pos = torch.randn(S + 4, D, device="cuda", requires_grad=True) if with_pos else None
+    ids = torch.randint(0, V, (B, S), device="cuda")
+    ids[0, :4] = 7   # repeated ids: their gradients must add up
+    y = ops.embedding(ids, tok, pos)
+    ref = F.embedding(ids, tok.detach()) + (pos.detach()[:S] if with_pos else 0)
+    assert y.dtype == torch.bfloat16 and y.shape == (B, S, D)
+    assert _rel(y, ref) < 1e-2
+    dy = torch.randn(B, S, D, device="cuda").bfloat16()
+    y.backward(dy)
+    tref = torch.zeros(V, D, device="cuda").index_add_(0, ids.reshape(-1), dy.float().reshape(-1, D))
+    assert _rel(tok.grad, tref) < 1e-5
+    if with_pos:
+        pref = torch.zeros(S + 4, D, device="cuda")
+        pref[:S] = dy.float().sum(0)
+        assert _rel(pos.grad, pref) < 1e-5
