@@ -53,6 +53,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--model", default="70m")
     ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--shape", type=int, nargs=3, metavar=("M", "N", "K"), help="time one forward GEMM of this shape only")
     args = ap.parse_args()
     peak = None
     p = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
@@ -60,7 +61,8 @@ def main():
         peak = json.load(open(p)).get("bf16_tflops")
     flush = torch.zeros(64 << 20, device="cuda")
     print(f"{'kind':6} {'M':>6} {'N':>6} {'K':>6} {'ours us':>9} {'TF/s':>7} {'cublas us':>10} {'TF/s':>7} {'ours/cublas':>11} {'of peak':>8}")
-    for kind, m, n, k, a_t, b_t in shapes(args.model):
+    todo = [("fwd", *args.shape, False, False)] if args.shape else shapes(args.model)
+    for kind, m, n, k, a_t, b_t in todo:
         a = torch.randn(m, k, device="cuda").bfloat16()
         b = torch.randn(n, k, device="cuda").bfloat16()
         aa = a.t().contiguous() if a_t else a

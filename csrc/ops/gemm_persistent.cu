@@ -104,41 +104,104 @@ __device__ __forceinline__ bool copy_cta_meet(const FusedDev& f, int cta, uint32
   }
   return __syncthreads_or(bad ? 1 : 0) == 0;
 }
-// 16-byte copy of [b0, b1) by the whole CTA with four transfers in flight per thread.
-__device__ __forceinline__ void cta_copy16(char* dst, const char* src, unsigned long long b0, unsigned long long b1) {
-  const unsigned long long v0 = b0 / 16, v1 = b1 / 16;
-  unsigned long long i = v0 + threadIdx.x;
-  for (; i + 3ull * blockDim.x < v1; i += 4ull * blockDim.x) {
-    const uint4 a = reinterpret_cast<const uint4*>(src)[i], b = reinterpret_cast<const uint4*>(src)[i + blockDim.x];
-    const uint4 c = reinterpret_cast<const uint4*>(src)[i + 2ull * blockDim.x], d = reinterpret_cast<const uint4*>(src)[i + 3ull * blockDim.x];
-    reinterpret_cast<uint4*>(dst)[i] = a;
-    reinterpret_cast<uint4*>(dst)[i + blockDim.x] = b;
-    reinterpret_cast<uint4*>(dst)[i + 2ull * blockDim.x] = c;
-    reinterpret_cast<uint4*>(dst)[i + 3ull * blockDim.x] = d;
+// Bulk (TMA, untiled, no multicast) copy engine of a copy CTA: one thread streams [b0, b1) of
+// `src` (possibly a peer's memory) to `dst` (local) through `stages` shared-memory buffers of
+// `piece` bytes, so that (stages - 1) * piece bytes are in flight per CTA with a single thread
+// issuing.  Addresses and sizes are multiples of 16 bytes.  Returns false when a load never landed.
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(tc::smem_u32(smem_dst)),
+               "l"(gsrc), "r"(bytes), "r"(tc::smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void bulk_store(void* gdst, const void* smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(tc::smem_u32(smem_src)), "r"(bytes)
+               : "memory");
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+constexpr int kCopyStages = 4;
+constexpr uint32_t kCopyPiece = 48 * 1024;
+
+struct CopyEngine {
+  uint8_t* buf;       // kCopyStages * kCopyPiece bytes of shared memory, 128-byte aligned
+  uint64_t* full;     // kCopyStages barriers
+  uint32_t issued;    // loads issued so far (all chunks)
+  uint32_t drained;   // pieces stored so far
+};
+
+// Streams one byte range and returns when its last piece has been handed to a store.
+__device__ bool copy_range(CopyEngine& e, char* dst, const char* src, unsigned long long b0, unsigned long long b1,
+                           unsigned long long limit_ns) {
+  const unsigned long long total = b1 - b0;
+  const uint32_t pieces = static_cast<uint32_t>((total + kCopyPiece - 1) / kCopyPiece);
+  uint32_t loaded = 0;
+  auto issue = [&](uint32_t j) {
+    const unsigned long long off = static_cast<unsigned long long>(j) * kCopyPiece;
+    const uint32_t n = static_cast<uint32_t>(total - off < kCopyPiece ? total - off : kCopyPiece);
+    const uint32_t s = e.issued % kCopyStages;
+    tc::mbar_expect_tx(&e.full[s], n);
+    bulk_load(e.buf + static_cast<size_t>(s) * kCopyPiece, src + b0 + off, n, &e.full[s]);
+    ++e.issued;
+  };
+  // a stage may be refilled once the store that read it has finished reading: keep one stage for that
+  while (loaded < pieces && e.issued - e.drained < kCopyStages - 1) issue(loaded++);
+  for (uint32_t j = 0; j < pieces; ++j) {
+    const uint32_t s = e.drained % kCopyStages;
+    const unsigned long long t0 = now_ns();
+    while (!tc::mbar_try_wait(&e.full[s], (e.drained / kCopyStages) & 1u))
+      if (now_ns() - t0 > limit_ns) return false;
+    const unsigned long long off = static_cast<unsigned long long>(j) * kCopyPiece;
+    const uint32_t n = static_cast<uint32_t>(total - off < kCopyPiece ? total - off : kCopyPiece);
+    bulk_store(dst + b0 + off, e.buf + static_cast<size_t>(s) * kCopyPiece, n);
+    ++e.drained;
+    if (loaded < pieces) {
+      // the stage to refill is the one stored in the previous iteration: wait until at most the newest
+      // store is still reading shared memory
+      asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+      issue(loaded++);
+    }
   }
-  for (; i < v1; i += blockDim.x) reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(src)[i];
+  return true;
 }
 
 // Role of CTAs [0, copy_ctas) in the all-gather fusion: meet the peers (their shards are
 // complete), pull the shards chunk by chunk starting with the own one, raise a chunk's flag
 // when every copy CTA has finished it, meet again (nobody reads my shard any more).
-__device__ void allgather_copy_role(const FusedDev& f, uint32_t epoch) {
+__device__ void allgather_copy_role(const FusedDev& f, uint32_t epoch, uint8_t* smem) {
   const int cta = blockIdx.x;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + kCopyStages * kCopyPiece);
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kCopyStages; ++s) tc::mbar_init(&full[s], 1);
+    tc::mbar_init_fence();
+  }
   if (!copy_cta_meet(f, cta, 2 * epoch - 1)) return;
   const unsigned long long units = f.chunk_bytes / 16;
   const unsigned long long per = (units + f.copy_ctas - 1) / f.copy_ctas;
   unsigned long long b0 = cta * per * 16, b1 = b0 + per * 16;
   if (b0 > f.chunk_bytes) b0 = f.chunk_bytes;
   if (b1 > f.chunk_bytes) b1 = f.chunk_bytes;
-  for (int k = 0; k < f.world; ++k) {
-    const int c = (f.rank + k) % f.world;
-    cta_copy16(static_cast<char*>(f.a_gathered) + static_cast<size_t>(c) * f.chunk_bytes, static_cast<const char*>(f.a_peer[c]), b0, b1);
-    __syncthreads();
-    if (threadIdx.x == 0) {
+  if (threadIdx.x == 0) {
+    asm volatile("fence.proxy.async;" ::: "memory");   // the shards were written with ordinary stores
+    CopyEngine e{smem, full, 0u, 0u};
+    bool ok = true;
+    for (int k = 0; k < f.world && ok; ++k) {
+      const int c = (f.rank + k) % f.world;
+      if (b1 > b0)
+        ok = copy_range(e, static_cast<char*>(f.a_gathered) + static_cast<size_t>(c) * f.chunk_bytes,
+                        static_cast<const char*>(f.a_peer[c]), b0, b1, f.timeout_ns);
+      if (!ok) break;
+      // the chunk's bytes must be in global memory before its flag can rise
+      asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+      asm volatile("fence.proxy.async;" ::: "memory");
       __threadfence();
       const uint32_t arrived = atomicAdd(f.chunk_counters + c, 1u) + 1u;
       if (arrived == static_cast<uint32_t>(f.copy_ctas) * epoch)
         asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(f.chunk_flags + c), "r"(epoch) : "memory");
+    }
+    if (!ok) {
+      atomicCAS(f.status, 0, 0x100 + f.rank);
+      // queued stores must have read shared memory, and loads in flight must land, before the CTA retires
+      asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+      for (uint32_t j = e.drained; j < e.issued; ++j) tc::mbar_wait(&full[j % kCopyStages], (j / kCopyStages) & 1u, 1u << 22);
     }
   }
   copy_cta_meet(f, cta, 2 * epoch);
@@ -198,6 +261,7 @@ __global__ void __launch_bounds__(192, 1) gemm_persistent_kernel(const __grid_co
                                                                  const __grid_constant__ CUtensorMap tma_b, GemmDev g,
                                                                  FusedDev f) {
   using L = PLayout<BN, STAGES>;
+  static_assert(L::kTiles >= kCopyStages * static_cast<int>(kCopyPiece), "copy CTAs stage through the tile ring");
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint8_t* tiles = smem;
@@ -210,7 +274,7 @@ __global__ void __launch_bounds__(192, 1) gemm_persistent_kernel(const __grid_co
 
   const uint32_t epoch = f.mode != FUSE_NONE ? *f.epoch_ptr : 0u;
   if (f.mode == FUSE_ALLGATHER_A && static_cast<int>(blockIdx.x) < f.copy_ctas) {
-    allgather_copy_role(f, epoch);   // these CTAs move data; the others compute
+    allgather_copy_role(f, epoch, smem);   // these CTAs move data; the others compute
     return;
   }
   // in-CTA waits: two seconds alone, the cross-GPU limit plus two seconds when a role waits for peers
