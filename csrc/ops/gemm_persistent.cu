@@ -31,7 +31,8 @@ struct PLayout {
   static constexpr int kBBytes = BN * BK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kTiles = STAGES * kStageBytes;
-  static constexpr int kBarriers = (2 * STAGES + 4) * 8 + 16;
+  static constexpr int kGemmBarriers = (2 * STAGES + 4) * 8 + 16;
+  static constexpr int kBarriers = kGemmBarriers + 64;   // + the reduce-scatter reducers' barriers and ring
   static constexpr int kTotal = kTiles + kBarriers + 1024;
 };
 
@@ -98,8 +99,8 @@ __device__ __forceinline__ bool copy_cta_meet(const FusedDev& f, int cta, uint32
   const int t = threadIdx.x;
   if (t < f.world) {
     __threadfence_system();
-    sig_store(f.sig[t] + 8 + 8 * cta + f.rank, value);
-    bad = !sig_wait(f.sig[f.rank] + 8 + 8 * cta + t, value, f.timeout_ns);
+    sig_store(f.sig[t] + kFuseSigAg + 8 * cta + f.rank, value);
+    bad = !sig_wait(f.sig[f.rank] + kFuseSigAg + 8 * cta + t, value, f.timeout_ns);
     if (bad) atomicCAS(f.status, 0, 0x100 + t);
   }
   return __syncthreads_or(bad ? 1 : 0) == 0;
@@ -207,54 +208,153 @@ __device__ void allgather_copy_role(const FusedDev& f, uint32_t epoch, uint8_t* 
   copy_cta_meet(f, cta, 2 * epoch);
 }
 
-// Tail of the reduce-scatter fusion, run by every GEMM CTA after its tiles: tell the peers when
-// this rank's last CTA has pushed its partial tiles, wait for every peer's tell, then reduce
-// the world slots of my chunk (fp32 accumulation, fixed rank order) into the bf16 result.
-__device__ void reduce_scatter_tail(const FusedDev& f, const GemmDev& g, uint32_t epoch, int gcta, int gctas) {
+// Reduction side of the reduce-scatter fusion.  The chunk this rank owns is cut into `rs_phases`
+// row groups and every group into pieces; a piece is pulled from all partial products (bulk loads
+// into shared memory, `world` buffers per stage), added in fp32 in rank order and written as bf16.
+// Pieces are handed out through a device-wide counter: the dedicated CTAs [0, copy_ctas) take
+// pieces of a group as soon as every rank has flagged it, while the GEMM CTAs still work on the
+// next group, and the GEMM CTAs join in when they have run out of tiles.
+constexpr int kReduceStages = 3;
+constexpr uint32_t kReduceStageBytes = 64 * 1024;
+constexpr uint32_t kNoPiece = 0xffffffffu;
+
+struct ReduceShared {           // lives behind the GEMM roles' barriers in shared memory
+  uint64_t full[kReduceStages];
+  uint32_t piece[kReduceStages];
+  int bad;
+};
+
+__device__ void reduce_scatter_role(const FusedDev& f, const GemmDev& g, uint32_t epoch, uint8_t* smem, ReduceShared* sh) {
+  const int tid = threadIdx.x;
+  if (tid == 0) {
+    for (int s = 0; s < kReduceStages; ++s) tc::mbar_init(&sh->full[s], 1);
+    sh->bad = 0;
+    tc::mbar_init_fence();
+  }
   __syncthreads();
-  if (threadIdx.x == 0) {
-    __threadfence_system();
-    const uint32_t done = atomicAdd(f.done_counter, 1u) + 1u;
-    if (done == static_cast<uint32_t>(gctas) * epoch)
-      for (int p = 0; p < f.world; ++p) sig_store(f.sig[p] + f.rank, epoch);
-  }
-  bool bad = false;
-  if (threadIdx.x < f.world) {
-    bad = !sig_wait(f.sig[f.rank] + threadIdx.x, epoch, f.timeout_ns);
-    if (bad) atomicCAS(f.status, 0, 0x200 + static_cast<int>(threadIdx.x));
-  }
-  if (__syncthreads_or(bad ? 1 : 0)) return;
-  const size_t slot_elems = static_cast<size_t>(f.chunk_rows) * g.n;
-  const __nv_bfloat16* slots = static_cast<const __nv_bfloat16*>(f.rs_slots[epoch & 1u]);
-  __nv_bfloat16* out = static_cast<__nv_bfloat16*>(f.rs_out);
-  const size_t vecs = slot_elems / 8;
-  for (size_t i = static_cast<size_t>(gcta) * blockDim.x + threadIdx.x; i < vecs; i += static_cast<size_t>(gctas) * blockDim.x) {
-    uint4 raw[kFuseMaxRanks];
-#pragma unroll
-    for (int r = 0; r < kFuseMaxRanks; ++r)
-      if (r < f.world) raw[r] = reinterpret_cast<const uint4*>(slots + static_cast<size_t>(r) * slot_elems)[i];
-    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-#pragma unroll
-    for (int r = 0; r < kFuseMaxRanks; ++r) {
-      if (r < f.world) {
-        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[r]);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float2 t = __bfloat1622float2(h[j]);
-          acc[2 * j] += t.x;
-          acc[2 * j + 1] += t.y;
+  const uint32_t piece = (kReduceStageBytes / static_cast<uint32_t>(f.world)) & ~127u;   // bytes per rank per stage
+  const unsigned long long chunk_bytes = static_cast<unsigned long long>(f.chunk_rows) * g.n * 2ull;
+  const unsigned long long phase_bytes = chunk_bytes / f.rs_phases;
+  const uint32_t pieces_per_phase = static_cast<uint32_t>((phase_bytes + piece - 1) / piece);
+  const uint32_t total = pieces_per_phase * static_cast<uint32_t>(f.rs_phases);
+  const unsigned long long my_base = static_cast<unsigned long long>(f.rank) * chunk_bytes;   // my rows inside a partial product
+  volatile int* bad_flag = &sh->bad;
+
+  auto piece_range = [&](uint32_t p, unsigned long long& off, uint32_t& n) {
+    const uint32_t ph = p / pieces_per_phase, q = p % pieces_per_phase;
+    const unsigned long long o = static_cast<unsigned long long>(q) * piece;
+    n = static_cast<uint32_t>(phase_bytes - o < piece ? phase_bytes - o : piece);
+    off = static_cast<unsigned long long>(ph) * phase_bytes + o;   // byte offset inside my chunk
+  };
+  uint32_t issued = 0;
+  int ready_phase = -1;
+  bool exhausted = false;
+  // thread 0 only: takes the next piece, waits for its group's flags when needed, queues the loads
+  auto issue = [&]() -> bool {
+    const uint32_t s = issued % kReduceStages;
+    const uint32_t p = exhausted ? total : atomicAdd(f.work_counter, 1u);
+    ++issued;
+    if (p >= total) {
+      exhausted = true;
+      sh->piece[s] = kNoPiece;
+      return true;
+    }
+    const int ph = static_cast<int>(p / pieces_per_phase);
+    while (ready_phase < ph) {
+      for (int r = 0; r < f.world; ++r) {
+        if (!sig_wait(f.sig[f.rank] + kFuseSigRs + 4 * r + (ready_phase + 1), epoch, f.timeout_ns)) {
+          atomicCAS(f.status, 0, 0x200 + r);
+          sh->piece[s] = kNoPiece;
+          return false;
         }
       }
+      ++ready_phase;
+      asm volatile("fence.proxy.async;" ::: "memory");   // the partial products were written with ordinary stores
     }
-    uint4 pk;
-    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
+    unsigned long long off;
+    uint32_t n;
+    piece_range(p, off, n);
+    sh->piece[s] = p;
+    tc::mbar_expect_tx(&sh->full[s], n * static_cast<uint32_t>(f.world));
+    for (int r = 0; r < f.world; ++r)
+      bulk_load(smem + static_cast<size_t>(s) * kReduceStageBytes + static_cast<size_t>(r) * piece,
+                static_cast<const char*>(f.rs_partial[epoch & 1u][r]) + my_base + off, n, &sh->full[s]);
+    return true;
+  };
+  uint32_t consumed_loaded = 0;   // thread 0: loaded pieces consumed so far
+  uint32_t j = 0;
+  for (;; ++j) {
+    const uint32_t s = j % kReduceStages;
+    // thread 0 keeps the ring full: the stage refilled here was released at the end of iteration j - 1
+    if (tid == 0) {
+      while (!*bad_flag && issued < j + kReduceStages) {
+        if (!issue()) *bad_flag = 1;
+      }
+    }
+    __syncthreads();
+    const uint32_t p = sh->piece[s];
+    if (p == kNoPiece || *bad_flag) break;   // uniform: both were written before the barrier above
+    bool landed = false;
+    {
+      const unsigned long long t0 = now_ns();
+      for (uint32_t i = 0;; ++i) {
+        if (tc::mbar_try_wait(&sh->full[s], (j / kReduceStages) & 1u)) {
+          landed = true;
+          break;
+        }
+        if ((i & 255u) == 255u && now_ns() - t0 > f.timeout_ns + 2000000000ull) break;
+      }
+    }
+    if (__syncthreads_or(landed ? 0 : 1)) {
+      if (tid == 0) {
+        *bad_flag = 1;
+        atomicCAS(f.status, 0, 0x200 + f.rank);
+      }
+      break;
+    }
+    if (tid == 0) ++consumed_loaded;
+    unsigned long long off;
+    uint32_t n;
+    piece_range(p, off, n);
+    const uint8_t* st = smem + static_cast<size_t>(s) * kReduceStageBytes;
+    uint4* out = reinterpret_cast<uint4*>(static_cast<char*>(f.rs_out) + off);
+    for (uint32_t v = tid; v < n / 16; v += blockDim.x) {
+      float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
 #pragma unroll
-    for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
-    reinterpret_cast<uint4*>(out)[i] = pk;
+      for (int r = 0; r < kFuseMaxRanks; ++r) {
+        if (r < f.world) {
+          const uint4 raw = reinterpret_cast<const uint4*>(st + static_cast<size_t>(r) * piece)[v];
+          const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const float2 t = __bfloat1622float2(h[q]);
+            acc[2 * q] += t.x;
+            acc[2 * q + 1] += t.y;
+          }
+        }
+      }
+      uint4 pk;
+      __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) h[q] = __floats2bfloat162_rn(acc[2 * q], acc[2 * q + 1]);
+      out[v] = pk;
+    }
+    __syncthreads();   // stage s may be refilled
   }
+  __syncthreads();
+  if (tid == 0 && *bad_flag) {
+    // loads already queued must land before the CTA retires (stages whose entry is a real piece)
+    for (uint32_t q = j; q < issued; ++q)
+      if (sh->piece[q % kReduceStages] != kNoPiece) tc::mbar_wait(&sh->full[q % kReduceStages], (q / kReduceStages) & 1u, 1u << 22);
+  }
+  (void)consumed_loaded;
 }
 
-__global__ void bump_epoch_kernel(uint32_t* epoch) { *epoch = *epoch + 1; }
+// ++*epoch and, when given, *zeroed = 0 (the reduce-scatter fusion's piece counter).
+__global__ void bump_epoch_kernel(uint32_t* epoch, uint32_t* zeroed) {
+  *epoch = *epoch + 1;
+  if (zeroed) *zeroed = 0;
+}
 
 template <int BN, int STAGES, bool kAMn, bool kBMn>
 __global__ void __launch_bounds__(192, 1) gemm_persistent_kernel(const __grid_constant__ CUtensorMap tma_a,
@@ -262,6 +362,7 @@ __global__ void __launch_bounds__(192, 1) gemm_persistent_kernel(const __grid_co
                                                                  FusedDev f) {
   using L = PLayout<BN, STAGES>;
   static_assert(L::kTiles >= kCopyStages * static_cast<int>(kCopyPiece), "copy CTAs stage through the tile ring");
+  static_assert(L::kTiles >= kReduceStages * static_cast<int>(kReduceStageBytes), "reducer CTAs stage through the tile ring");
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint8_t* tiles = smem;
@@ -273,8 +374,10 @@ __global__ void __launch_bounds__(192, 1) gemm_persistent_kernel(const __grid_co
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const uint32_t epoch = f.mode != FUSE_NONE ? *f.epoch_ptr : 0u;
-  if (f.mode == FUSE_ALLGATHER_A && static_cast<int>(blockIdx.x) < f.copy_ctas) {
-    allgather_copy_role(f, epoch, smem);   // these CTAs move data; the others compute
+  if (f.mode != FUSE_NONE && static_cast<int>(blockIdx.x) < f.copy_ctas) {
+    // these CTAs move data; the others compute
+    if (f.mode == FUSE_ALLGATHER_A) allgather_copy_role(f, epoch, smem);
+    else reduce_scatter_role(f, g, epoch, smem, reinterpret_cast<ReduceShared*>(smem + L::kTiles + L::kGemmBarriers));
     return;
   }
   // in-CTA waits: two seconds alone, the cross-GPU limit plus two seconds when a role waits for peers
@@ -310,11 +413,25 @@ __global__ void __launch_bounds__(192, 1) gemm_persistent_kernel(const __grid_co
   tc::fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
-  auto tile_coords = [&](int w, int& m_blk, int& n_blk, int& kb0) {
+  // Reduce-scatter fusion: phase-major order; inside a phase the chunks of the other ranks come first
+  // (rank + 1, rank + 2, ...) and this rank's own chunk last, so what peers wait for is ready earliest.
+  const int chunk_mt = f.mode == FUSE_REDUCE_SCATTER_D ? f.chunk_rows / BM : 1;
+  const int phase_mt = f.mode == FUSE_REDUCE_SCATTER_D ? chunk_mt / f.rs_phases : 1;
+  const int per_chunk_phase = phase_mt * n_tiles, per_phase = per_chunk_phase * f.world;
+  auto tile_coords = [&](int w, int& m_blk, int& n_blk, int& kb0) -> int {
+    if (f.mode == FUSE_REDUCE_SCATTER_D) {
+      const int ph = w / per_phase, rem = w % per_phase;
+      const int c = (f.rank + 1 + rem / per_chunk_phase) % f.world, rem2 = rem % per_chunk_phase;
+      kb0 = 0;
+      n_blk = rem2 % n_tiles;
+      m_blk = c * chunk_mt + ph * phase_mt + rem2 / n_tiles;
+      return ph;
+    }
     const int t = w / splits;
     kb0 = (w % splits) * num_kb;
     n_blk = t % n_tiles;
     m_blk = (t / n_tiles + m_rot) % m_tiles;
+    return 0;
   };
 
   if (warp == 0) {
@@ -406,7 +523,7 @@ __global__ void __launch_bounds__(192, 1) gemm_persistent_kernel(const __grid_co
     int i = 0;
     for (int t = gcta; t < total_tiles; t += gctas, ++i) {
       int m_blk, n_blk, kb0;
-      tile_coords(t, m_blk, n_blk, kb0);
+      const int phase = tile_coords(t, m_blk, n_blk, kb0);
       const int buf = i & 1;
       ok = wait_or_abort(&acc_full[buf], (i >> 1) & 1, abort_flag, wait_ns);
       ok = __all_sync(0xffffffffu, ok);
@@ -414,12 +531,7 @@ __global__ void __launch_bounds__(192, 1) gemm_persistent_kernel(const __grid_co
       tc::fence_after_sync();
       const int row = m_blk * BM + quarter * 32 + lane;
       GemmDev gt = g;
-      if (f.mode == FUSE_REDUCE_SCATTER_D) {
-        // the tile's rows belong to rank `owner`: store into that rank's staging slot for this rank
-        const int owner = (m_blk * BM) / f.chunk_rows;
-        gt.d = static_cast<char*>(f.d_owner[epoch & 1u][owner]) -
-               static_cast<size_t>(owner) * f.chunk_rows * g.ldd * (g.d_fp32 ? 4 : 2);
-      }
+      if (f.mode == FUSE_REDUCE_SCATTER_D) gt.d = f.rs_partial[epoch & 1u][f.rank];   // my partial product; the owners pull from it
       const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(buf * BN) + (static_cast<uint32_t>(quarter * 32) << 16);
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
@@ -434,6 +546,19 @@ __global__ void __launch_bounds__(192, 1) gemm_persistent_kernel(const __grid_co
         const int col0 = n_blk * BN + c0;
         if (row < g.m && col0 < g.n) epilogue_store(gt, row, col0, r);
       }
+      if (f.mode == FUSE_REDUCE_SCATTER_D) {
+        // count this warp's quarter of the tile; the warp that completes a phase tells every rank
+        __syncwarp();
+        if (lane == 0) {
+          __threadfence();
+          const uint32_t target = static_cast<uint32_t>(per_phase) * 4u;
+          if (atomicAdd(f.phase_counters + phase, 1u) + 1u == target) {
+            atomicExch(f.phase_counters + phase, 0u);
+            __threadfence_system();
+            for (int p = 0; p < f.world; ++p) sig_store(f.sig[p] + kFuseSigRs + 4 * f.rank + phase, epoch);
+          }
+        }
+      }
     }
     if (!ok && lane == 0) {
       *abort_flag = 1;
@@ -446,7 +571,9 @@ __global__ void __launch_bounds__(192, 1) gemm_persistent_kernel(const __grid_co
     tc::fence_after_sync();
     tc::tmem_dealloc(tmem_base, 2 * BN);
   }
-  if (f.mode == FUSE_REDUCE_SCATTER_D && *abort_flag == 0) reduce_scatter_tail(f, g, epoch, gcta, gctas);
+  // out of tiles: help with the reduction (the tile ring is idle now)
+  if (f.mode == FUSE_REDUCE_SCATTER_D && *abort_flag == 0)
+    reduce_scatter_role(f, g, epoch, smem, reinterpret_cast<ReduceShared*>(smem + L::kTiles + L::kGemmBarriers));
 }
 
 int sm_count() {
@@ -538,8 +665,7 @@ no_split:
   // fused roles wait on one another inside the kernel: every CTA must be resident (one per SM)
   int gemm_ctas = ctas - f.copy_ctas;
   if (gemm_ctas < 1) return cudaErrorInvalidValue;
-  if (tiles < gemm_ctas && f.mode != FUSE_REDUCE_SCATTER_D) gemm_ctas = tiles;
-  if (f.mode == FUSE_REDUCE_SCATTER_D && f.rs_gemm_ctas > 0) gemm_ctas = f.rs_gemm_ctas;  // fixed: the done counter depends on it
+  if (tiles < gemm_ctas) gemm_ctas = tiles;
   gemm_persistent_kernel<BN, STAGES, kAMn, kBMn><<<gemm_ctas + f.copy_ctas, 192, L::kTotal, stream>>>(ma, mb, g, f);
   count_launch();
   return cudaGetLastError();
@@ -547,8 +673,8 @@ no_split:
 
 }  // namespace
 
-cudaError_t launch_bump_epoch(uint32_t* epoch, cudaStream_t stream) {
-  bump_epoch_kernel<<<1, 1, 0, stream>>>(epoch);
+cudaError_t launch_bump_epoch(uint32_t* epoch, uint32_t* zeroed, cudaStream_t stream) {
+  bump_epoch_kernel<<<1, 1, 0, stream>>>(epoch, zeroed);
   return cudaGetLastError();
 }
 

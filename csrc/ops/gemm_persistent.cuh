@@ -14,21 +14,23 @@ namespace ops {
 enum FuseMode : int {
   FUSE_NONE = 0,
   FUSE_ALLGATHER_A = 1,        // rows of A arrive chunk by chunk (one chunk per rank) while tiles are computed
-  FUSE_REDUCE_SCATTER_D = 2,   // rows of D belong to different ranks; partial tiles go to the owner, who reduces
+  FUSE_REDUCE_SCATTER_D = 2,   // rows of D belong to different ranks; the owner pulls and adds the partial rows
 };
 
 constexpr int kFuseMaxRanks = 8;
-constexpr int kFuseCopyCtas = 16;   // CTAs of the all-gather fusion that move data (fixed: counters depend on it)
+constexpr int kFuseCopyCtas = 16;     // all-gather fusion: CTAs that move data (fixed: counters depend on it)
+constexpr int kFuseReduceCtas = 16;   // reduce-scatter fusion: CTAs that only pull and add partial rows (default)
+constexpr int kFuseMaxPhases = 4;     // reduce-scatter fusion: row groups of a chunk that complete one after another
 
 // Everything the fused roles need.  Pointers into other GPUs' memory are peer
-// mappings (plain loads / stores over NVLink); no TMA descriptor ever covers them.
+// mappings read with plain or bulk (never multicast) loads over NVLink.
 struct FusedDev {
   int mode = FUSE_NONE;
   int world = 1;
   int rank = 0;
   int chunk_rows = 0;                         // rows per rank chunk, a multiple of 128
   int k_splits = 1;                           // split-K factor (set by the launcher)
-  int copy_ctas = 0;                          // all-gather: CTAs [0, copy_ctas) pull the peers' shards
+  int copy_ctas = 0;                          // CTAs [0, copy_ctas) move data instead of computing tiles
   const uint32_t* epoch_ptr = nullptr;        // device word: number of this fused call (bumped before the launch)
   unsigned long long timeout_ns = 0;          // bound of every cross-GPU wait
   int* status = nullptr;                      // written (non-zero) when such a wait runs out
@@ -39,23 +41,26 @@ struct FusedDev {
   unsigned long long chunk_bytes = 0;
   uint32_t* chunk_flags = nullptr;            // local [world]: chunk c has landed when chunk_flags[c] >= epoch
   uint32_t* chunk_counters = nullptr;         // local [world]: copy CTAs that finished chunk c (cumulative)
-  // GEMM → reduce-scatter
-  void* d_owner[2][kFuseMaxRanks] = {};       // [epoch parity][owner]: where this rank's partial rows of that chunk go
-  const void* rs_slots[2] = {};               // [epoch parity]: my staging, world slots of chunk_rows x N bf16
+  // GEMM → reduce-scatter.  Every rank writes its partial product [world * chunk_rows, N] (bf16, dense)
+  // into its own buffer; rank o then reads rows [o * chunk_rows, (o + 1) * chunk_rows) of every buffer.
+  void* rs_partial[2][kFuseMaxRanks] = {};    // [epoch parity][r]: rank r's partial product (mine is written, all are read)
   void* rs_out = nullptr;                     // [chunk_rows, N] bf16 result of the reduction
-  uint32_t* done_counter = nullptr;           // local: GEMM CTAs that finished their tiles (cumulative)
-  int rs_gemm_ctas = 0;                       // fixed number of GEMM CTAs of the reduce-scatter fusion
+  int rs_phases = 1;                          // row groups per chunk (1, 2 or 4)
+  uint32_t* phase_counters = nullptr;         // local [kFuseMaxPhases]: epilogue warps done with a phase (self-resetting)
+  uint32_t* work_counter = nullptr;           // local: next piece of the reduction (zeroed before the launch)
 };
 
 // Signal-word layout (uint32 per entry) inside sig[r]:
-//   [0, 8)                 reduce-scatter "pushes done" flags, indexed by source rank
-//   [8 + 8*c, 8 + 8*c + 8) all-gather meeting flags of copy CTA c, indexed by source rank
-constexpr int kFuseSigWords = 8 + 8 * kFuseCopyCtas;
+//   [4*s, 4*s + 4)           reduce-scatter: rank s has written phase 0..3 of its partial product
+//   [32 + 8*c, 32 + 8*c + 8) all-gather meeting flags of copy CTA c, indexed by source rank
+constexpr int kFuseSigRs = 0;
+constexpr int kFuseSigAg = 4 * kFuseMaxRanks;
+constexpr int kFuseSigWords = kFuseSigAg + 8 * kFuseCopyCtas;
 
 // max_ctas <= 0: one CTA per SM.
 cudaError_t launch_gemm_persistent(const GemmArgs& a, const FusedDev& f, int max_ctas, cudaStream_t stream);
-// ++*epoch (one thread); enqueue before a fused launch.
-cudaError_t launch_bump_epoch(uint32_t* epoch, cudaStream_t stream);
+// ++*epoch and *zeroed = 0 (zeroed may be null), one thread; enqueue before a fused launch.
+cudaError_t launch_bump_epoch(uint32_t* epoch, uint32_t* zeroed, cudaStream_t stream);
 
 }  // namespace ops
 }  // namespace mccl

@@ -1,5 +1,6 @@
 #include "tp_gemm.hpp"
 
+#include <cstdlib>
 #include <cstring>
 
 #include "../core/errors.hpp"
@@ -40,6 +41,12 @@ void TpGemm::check_status() const {
 }
 
 namespace {
+int env_int(const char* name, int def, int lo, int hi) {
+  const char* v = std::getenv(name);
+  if (!v || !*v) return def;
+  const int x = std::atoi(v);
+  return x < lo ? lo : (x > hi ? hi : x);
+}
 void fill_common(FusedDev& f, DeviceComm& comm, const SymmAlloc& sig, int* status_dev) {
   f.world = comm.world();
   f.rank = comm.rank();
@@ -81,7 +88,7 @@ void TpGemm::ag_gemm(const SymmAlloc& x_sym, size_t x_off, int rows_local, int k
   a.ldd = n;
   a.b_mn_major = w_kn;
   a.epilogue = epilogue;
-  MCCL_CUDA_CHECK(launch_bump_epoch(words_ + 0, stream));
+  MCCL_CUDA_CHECK(launch_bump_epoch(words_ + 0, nullptr, stream));
   cudaError_t rc = launch_gemm_persistent(a, f, sms_, stream);
   MCCL_CHECK_T(rc == cudaSuccess, CudaError, "ag_gemm launch failed: " << cudaGetErrorString(rc));
 }
@@ -97,21 +104,23 @@ void TpGemm::gemm_rs(const __nv_bfloat16* x, int ldx, int rows_local, int k, con
   fill_common(f, *comm_, *sig_, status_dev_);
   f.mode = FUSE_REDUCE_SCATTER_D;
   f.chunk_rows = rows_local;
+  static const int reduce_ctas = env_int("MCCL_TP_REDUCE_CTAS", kFuseReduceCtas, 1, 64);
+  static const int max_phases = env_int("MCCL_TP_PHASES", kFuseMaxPhases, 1, kFuseMaxPhases);
+  f.copy_ctas = reduce_ctas;
   f.epoch_ptr = words_ + 1;
-  f.done_counter = words_ + 2;
-  f.rs_gemm_ctas = sms_;
+  f.phase_counters = words_ + 24;
+  f.work_counter = words_ + 28;
   f.rs_out = out;
+  const int chunk_mt = rows_local / 128;
+  f.rs_phases = (max_phases >= 4 && chunk_mt % 4 == 0) ? 4 : ((max_phases >= 2 && chunk_mt % 2 == 0) ? 2 : 1);
+  // every rank's partial product [world * rows_local, N] lives in its half (by call parity) of the symmetric staging
   const size_t parity_elems = static_cast<size_t>(f.world) * max_rs_elems_;
-  for (int par = 0; par < 2; ++par) {
-    f.rs_slots[par] = static_cast<const __nv_bfloat16*>(stage_->ptrs[f.rank]) + par * parity_elems;
-    for (int owner = 0; owner < f.world; ++owner)   // my slot (index = my rank) inside the owner's staging
-      f.d_owner[par][owner] = static_cast<__nv_bfloat16*>(stage_->ptrs[owner]) + par * parity_elems + static_cast<size_t>(f.rank) * slot_elems;
-  }
-  // the reduction reads world slots that are slot_elems apart: lay the slots out densely for this call
+  for (int par = 0; par < 2; ++par)
+    for (int r = 0; r < f.world; ++r) f.rs_partial[par][r] = static_cast<__nv_bfloat16*>(stage_->ptrs[r]) + par * parity_elems;
   GemmArgs a;
   a.a = x;
   a.b = w;
-  a.d = out;   // replaced per tile by the owner's slot
+  a.d = out;   // replaced inside the kernel by this rank's partial-product buffer
   a.m = rows_local * f.world;
   a.n = n;
   a.k = k;
@@ -119,7 +128,7 @@ void TpGemm::gemm_rs(const __nv_bfloat16* x, int ldx, int rows_local, int k, con
   a.ldb = ldw;
   a.ldd = n;
   a.b_mn_major = w_kn;
-  MCCL_CUDA_CHECK(launch_bump_epoch(words_ + 1, stream));
+  MCCL_CUDA_CHECK(launch_bump_epoch(words_ + 1, words_ + 28, stream));
   cudaError_t rc = launch_gemm_persistent(a, f, sms_, stream);
   MCCL_CHECK_T(rc == cudaSuccess, CudaError, "gemm_rs launch failed: " << cudaGetErrorString(rc));
 }

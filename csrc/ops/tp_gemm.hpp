@@ -4,8 +4,10 @@
 //             CTAs of the same kernel pull the peers' shards of X over NVLink while the tensor
 //             cores already multiply the chunks that have landed (own chunk first).
 //   gemm_rs   Y_r = reduce_scatter(X · W^T)   row-parallel forward, column-parallel input gradient
-//             each output tile is stored straight into the staging slot of the rank that owns its
-//             rows; after a cross-GPU hand-shake the same kernel adds the world partial slots.
+//             every rank writes its partial product into a symmetric buffer, row group by row group;
+//             reducer CTAs of the same kernel pull the groups of the rows they own from all ranks
+//             (bulk loads over NVLink into shared memory), add them in fp32 and write the result
+//             while the tensor cores work on the next group.
 //
 // The reference only offers `tensor_parallel_split` (a torch.chunk, mccl/distributed/sharding.py:54-69)
 // and states that hand-wired column/row parallelism works over its collectives (README.md:76);
@@ -52,7 +54,7 @@ class TpGemm {
   std::shared_ptr<DeviceComm> comm_;
   std::shared_ptr<SymmAlloc> sig_, stage_;
   size_t max_rs_elems_;
-  uint32_t* words_ = nullptr;   // device: [0] ag epoch, [1] rs epoch, [2] done counter, [8..16) flags, [16..24) counters
+  uint32_t* words_ = nullptr;   // device: [0] ag epoch, [1] rs epoch, [8..16) chunk flags, [16..24) chunk counters, [24..28) phase counters, [28] piece counter
   int* status_host_ = nullptr;
   int* status_dev_ = nullptr;
   int sms_ = 148;
