@@ -50,6 +50,8 @@ def main() -> None:
     ap.add_argument("--tokens", type=int, default=16384)
     ap.add_argument("--d-model", type=int, default=2048)
     ap.add_argument("--d-ff", type=int, default=8192)
+    ap.add_argument("--pull-only", action="store_true",
+                    help="time ag_gemm with a 64-column weight (the tiles are negligible): the all-gather pull rate")
     args = ap.parse_args()
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     local = int(os.environ.get("LOCAL_RANK", 0))
@@ -71,6 +73,19 @@ def main() -> None:
     link = 770e9
     results = []
     torch.manual_seed(rank)
+    if args.pull_only:
+        x = torch.randn(rows, D, device=dev).bfloat16()
+        sym.tensor(rank, 0, [rows, D], torch.bfloat16, local).copy_(x)
+        w = torch.randn(64, D, device=dev).bfloat16()
+        t = timed(lambda: tp.ag_gemm(sym, 0, rows, w, False), args.iters, dev)
+        nv = (world - 1) * rows * D * 2
+        tp.check_status()
+        if rank == 0:
+            print(f"pull-only world {world} copy_ctas {os.environ.get('MCCL_TP_COPY_CTAS', 'auto')}: {t:.1f} us, "
+                  f"{nv / t / 1e3:.1f} GB/s per GPU over NVLink ({nv / 1e6:.1f} MB)")
+        dist.barrier()
+        dist.destroy_process_group()
+        return
     # all-gather -> GEMM: (name, N_out, weight stored [K, N]?)
     for name, n_out, w_kn in [("qkv fwd", 3 * D // world, False), ("gate_up fwd", 2 * FF // world, False),
                               ("proj dgrad", D // world, True), ("down dgrad", FF // world, True)]:

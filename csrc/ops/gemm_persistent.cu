@@ -92,19 +92,6 @@ __device__ __forceinline__ bool sig_wait(const uint32_t* p, uint32_t v, unsigned
     }
   }
 }
-// Meeting of copy CTA `cta` of every rank.  Returns false when a peer did not arrive in time.
-__device__ __forceinline__ bool copy_cta_meet(const FusedDev& f, int cta, uint32_t value) {
-  __syncthreads();
-  bool bad = false;
-  const int t = threadIdx.x;
-  if (t < f.world) {
-    __threadfence_system();
-    sig_store(f.sig[t] + kFuseSigAg + 8 * cta + f.rank, value);
-    bad = !sig_wait(f.sig[f.rank] + kFuseSigAg + 8 * cta + t, value, f.timeout_ns);
-    if (bad) atomicCAS(f.status, 0, 0x100 + t);
-  }
-  return __syncthreads_or(bad ? 1 : 0) == 0;
-}
 // Bulk (TMA, untiled, no multicast) copy engine of a copy CTA: one thread streams [b0, b1) of
 // `src` (possibly a peer's memory) to `dst` (local) through `stages` shared-memory buffers of
 // `piece` bytes, so that (stages - 1) * piece bytes are in flight per CTA with a single thread
@@ -164,48 +151,62 @@ __device__ bool copy_range(CopyEngine& e, char* dst, const char* src, unsigned l
   return true;
 }
 
-// Role of CTAs [0, copy_ctas) in the all-gather fusion: meet the peers (their shards are
-// complete), pull the shards chunk by chunk starting with the own one, raise a chunk's flag
-// when every copy CTA has finished it, meet again (nobody reads my shard any more).
+// Role of CTAs [0, copy_ctas) in the all-gather fusion: pull the shards chunk by chunk, the own one
+// first and a peer's as soon as that peer has announced it (its launch has been reached in stream
+// order), and raise a chunk's flag when every copy CTA has finished its share of it.  The copy CTA
+// that finishes last tells the peers that this rank reads their shards no more and stays until every
+// peer has said the same, so that a shard is never overwritten while somebody still pulls from it.
 __device__ void allgather_copy_role(const FusedDev& f, uint32_t epoch, uint8_t* smem) {
   const int cta = blockIdx.x;
+  if (threadIdx.x != 0) return;   // one thread drives the copy engine
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + kCopyStages * kCopyPiece);
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < kCopyStages; ++s) tc::mbar_init(&full[s], 1);
-    tc::mbar_init_fence();
-  }
-  if (!copy_cta_meet(f, cta, 2 * epoch - 1)) return;
+  for (int s = 0; s < kCopyStages; ++s) tc::mbar_init(&full[s], 1);
+  tc::mbar_init_fence();
   const unsigned long long units = f.chunk_bytes / 16;
   const unsigned long long per = (units + f.copy_ctas - 1) / f.copy_ctas;
   unsigned long long b0 = cta * per * 16, b1 = b0 + per * 16;
   if (b0 > f.chunk_bytes) b0 = f.chunk_bytes;
   if (b1 > f.chunk_bytes) b1 = f.chunk_bytes;
-  if (threadIdx.x == 0) {
-    asm volatile("fence.proxy.async;" ::: "memory");   // the shards were written with ordinary stores
-    CopyEngine e{smem, full, 0u, 0u};
-    bool ok = true;
-    for (int k = 0; k < f.world && ok; ++k) {
-      const int c = (f.rank + k) % f.world;
-      if (b1 > b0)
-        ok = copy_range(e, static_cast<char*>(f.a_gathered) + static_cast<size_t>(c) * f.chunk_bytes,
-                        static_cast<const char*>(f.a_peer[c]), b0, b1, f.timeout_ns);
-      if (!ok) break;
-      // the chunk's bytes must be in global memory before its flag can rise
-      asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
-      asm volatile("fence.proxy.async;" ::: "memory");
-      __threadfence();
-      const uint32_t arrived = atomicAdd(f.chunk_counters + c, 1u) + 1u;
-      if (arrived == static_cast<uint32_t>(f.copy_ctas) * epoch)
-        asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(f.chunk_flags + c), "r"(epoch) : "memory");
+  CopyEngine e{smem, full, 0u, 0u};
+  bool ok = true;
+  for (int k = 0; k < f.world && ok; ++k) {
+    const int c = (f.rank + k) % f.world;
+    if (c != f.rank && !sig_wait(f.sig[f.rank] + kFuseSigAgReady + c, epoch, f.timeout_ns)) {
+      atomicCAS(f.status, 0, 0x100 + c);
+      ok = false;
+      break;
     }
+    asm volatile("fence.proxy.async;" ::: "memory");   // the shards were written with ordinary stores
+    if (b1 > b0)
+      ok = copy_range(e, static_cast<char*>(f.a_gathered) + static_cast<size_t>(c) * f.chunk_bytes,
+                      static_cast<const char*>(f.a_peer[c]), b0, b1, f.timeout_ns);
     if (!ok) {
-      atomicCAS(f.status, 0, 0x100 + f.rank);
-      // queued stores must have read shared memory, and loads in flight must land, before the CTA retires
-      asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
-      for (uint32_t j = e.drained; j < e.issued; ++j) tc::mbar_wait(&full[j % kCopyStages], (j / kCopyStages) & 1u, 1u << 22);
+      atomicCAS(f.status, 0, 0x100 + c);
+      break;
+    }
+    // the chunk's bytes must be in global memory before its flag can rise
+    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    asm volatile("fence.proxy.async;" ::: "memory");
+    __threadfence();
+    if (atomicAdd(f.chunk_counters + c, 1u) + 1u == static_cast<uint32_t>(f.copy_ctas)) {
+      atomicExch(f.chunk_counters + c, 0u);
+      asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(f.chunk_flags + c), "r"(epoch) : "memory");
     }
   }
-  copy_cta_meet(f, cta, 2 * epoch);
+  if (!ok) {
+    // queued stores must have read shared memory, and loads in flight must land, before the CTA retires
+    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    for (uint32_t j = e.drained; j < e.issued; ++j) tc::mbar_wait(&full[j % kCopyStages], (j / kCopyStages) & 1u, 1u << 22);
+    return;
+  }
+  if (atomicAdd(f.copy_done_counter, 1u) + 1u == static_cast<uint32_t>(f.copy_ctas)) {
+    atomicExch(f.copy_done_counter, 0u);
+    __threadfence_system();
+    for (int p = 0; p < f.world; ++p)
+      if (p != f.rank) sig_store(f.sig[p] + kFuseSigAgDone + f.rank, epoch);
+    for (int p = 0; p < f.world; ++p)
+      if (p != f.rank && !sig_wait(f.sig[f.rank] + kFuseSigAgDone + p, epoch, f.timeout_ns)) atomicCAS(f.status, 0, 0x100 + p);
+  }
 }
 
 // Reduction side of the reduce-scatter fusion.  The chunk this rank owns is cut into `rs_phases`
@@ -350,10 +351,18 @@ __device__ void reduce_scatter_role(const FusedDev& f, const GemmDev& g, uint32_
   (void)consumed_loaded;
 }
 
-// ++*epoch and, when given, *zeroed = 0 (the reduce-scatter fusion's piece counter).
-__global__ void bump_epoch_kernel(uint32_t* epoch, uint32_t* zeroed) {
-  *epoch = *epoch + 1;
-  if (zeroed) *zeroed = 0;
+// ++*epoch; *zeroed = 0 when given (the reduce-scatter fusion's piece counter); and the new epoch
+// is stored to every `announce` word (the all-gather fusion's "my shard is complete": everything
+// enqueued before this launch has finished).
+__global__ void bump_epoch_kernel(BumpArgs b) {
+  const uint32_t e = *b.epoch + 1;
+  *b.epoch = e;
+  if (b.zeroed) *b.zeroed = 0;
+  if (b.n_announce > 0) {
+    __threadfence_system();
+    for (int p = 0; p < b.n_announce; ++p)
+      if (b.announce[p]) sig_store(b.announce[p], e);
+  }
 }
 
 template <int BN, int STAGES, bool kAMn, bool kBMn>
@@ -673,8 +682,8 @@ no_split:
 
 }  // namespace
 
-cudaError_t launch_bump_epoch(uint32_t* epoch, uint32_t* zeroed, cudaStream_t stream) {
-  bump_epoch_kernel<<<1, 1, 0, stream>>>(epoch, zeroed);
+cudaError_t launch_bump_epoch(const BumpArgs& b, cudaStream_t stream) {
+  bump_epoch_kernel<<<1, 1, 0, stream>>>(b);
   return cudaGetLastError();
 }
 

@@ -18,7 +18,8 @@ enum FuseMode : int {
 };
 
 constexpr int kFuseMaxRanks = 8;
-constexpr int kFuseCopyCtas = 16;     // all-gather fusion: CTAs that move data (fixed: counters depend on it)
+constexpr int kFuseCopyCtas = 16;     // all-gather fusion: CTAs that move data (default; at most kFuseMaxCopyCtas)
+constexpr int kFuseMaxCopyCtas = 96;
 constexpr int kFuseReduceCtas = 16;   // reduce-scatter fusion: CTAs that only pull and add partial rows (default)
 constexpr int kFuseMaxPhases = 4;     // reduce-scatter fusion: row groups of a chunk that complete one after another
 
@@ -40,7 +41,8 @@ struct FusedDev {
   void* a_gathered = nullptr;                 // local [world * chunk_rows, K] buffer the tiles are loaded from
   unsigned long long chunk_bytes = 0;
   uint32_t* chunk_flags = nullptr;            // local [world]: chunk c has landed when chunk_flags[c] >= epoch
-  uint32_t* chunk_counters = nullptr;         // local [world]: copy CTAs that finished chunk c (cumulative)
+  uint32_t* chunk_counters = nullptr;         // local [world]: copy CTAs that finished chunk c (self-resetting)
+  uint32_t* copy_done_counter = nullptr;      // local: copy CTAs that finished all chunks (self-resetting)
   // GEMM → reduce-scatter.  Every rank writes its partial product [world * chunk_rows, N] (bf16, dense)
   // into its own buffer; rank o then reads rows [o * chunk_rows, (o + 1) * chunk_rows) of every buffer.
   void* rs_partial[2][kFuseMaxRanks] = {};    // [epoch parity][r]: rank r's partial product (mine is written, all are read)
@@ -51,16 +53,25 @@ struct FusedDev {
 };
 
 // Signal-word layout (uint32 per entry) inside sig[r]:
-//   [4*s, 4*s + 4)           reduce-scatter: rank s has written phase 0..3 of its partial product
-//   [32 + 8*c, 32 + 8*c + 8) all-gather meeting flags of copy CTA c, indexed by source rank
+//   [4*s, 4*s + 4)  reduce-scatter: rank s has written phase 0..3 of its partial product
+//   [32 + s]        all-gather: rank s's shard is complete (written by s before its launch)
+//   [40 + s]        all-gather: rank s has finished reading every shard
 constexpr int kFuseSigRs = 0;
-constexpr int kFuseSigAg = 4 * kFuseMaxRanks;
-constexpr int kFuseSigWords = kFuseSigAg + 8 * kFuseCopyCtas;
+constexpr int kFuseSigAgReady = 4 * kFuseMaxRanks;
+constexpr int kFuseSigAgDone = kFuseSigAgReady + kFuseMaxRanks;
+constexpr int kFuseSigWords = 64;
+
+struct BumpArgs {
+  uint32_t* epoch = nullptr;                   // device word to increment
+  uint32_t* zeroed = nullptr;                  // device word to clear (may be null)
+  uint32_t* announce[kFuseMaxRanks] = {};      // peer words that receive the new epoch (null entries skipped)
+  int n_announce = 0;
+};
 
 // max_ctas <= 0: one CTA per SM.
 cudaError_t launch_gemm_persistent(const GemmArgs& a, const FusedDev& f, int max_ctas, cudaStream_t stream);
-// ++*epoch and *zeroed = 0 (zeroed may be null), one thread; enqueue before a fused launch.
-cudaError_t launch_bump_epoch(uint32_t* epoch, uint32_t* zeroed, cudaStream_t stream);
+// One thread: ++*epoch, clear, announce; enqueue before a fused launch.
+cudaError_t launch_bump_epoch(const BumpArgs& b, cudaStream_t stream);
 
 }  // namespace ops
 }  // namespace mccl

@@ -47,6 +47,24 @@ int env_int(const char* name, int def, int lo, int hi) {
   const int x = std::atoi(v);
   return x < lo ? lo : (x > hi ? hi : x);
 }
+// Copy CTAs of the all-gather fusion: enough that pulling the remote bytes takes no longer than the tiles
+// on the remaining SMs.  One SM sustains about `kPullPerSm` bytes/s of bulk loads from a peer.
+constexpr double kPullPerSm = 22e9, kTilePeak = 1.38e15;
+int choose_copy_ctas(double remote_bytes, double flops, int sms) {
+  static const int forced = env_int("MCCL_TP_COPY_CTAS", 0, 0, kFuseMaxCopyCtas);
+  if (forced > 0) return forced;
+  int best = 8;
+  double best_t = 1e30;
+  for (int c = 8; c <= kFuseMaxCopyCtas && c < sms - 8; c += 8) {
+    const double t_comm = remote_bytes / (kPullPerSm * c), t_gemm = flops / (kTilePeak * (sms - c) / sms);
+    const double t = t_comm > t_gemm ? t_comm : t_gemm;
+    if (t < best_t * 0.97) {   // prefer fewer copy CTAs unless more of them help noticeably
+      best_t = t;
+      best = c;
+    }
+  }
+  return best;
+}
 void fill_common(FusedDev& f, DeviceComm& comm, const SymmAlloc& sig, int* status_dev) {
   f.world = comm.world();
   f.rank = comm.rank();
@@ -67,7 +85,8 @@ void TpGemm::ag_gemm(const SymmAlloc& x_sym, size_t x_off, int rows_local, int k
   fill_common(f, *comm_, *sig_, status_dev_);
   f.mode = FUSE_ALLGATHER_A;
   f.chunk_rows = rows_local;
-  f.copy_ctas = kFuseCopyCtas;
+  f.copy_ctas = choose_copy_ctas(static_cast<double>(f.world - 1) * chunk_bytes, 2.0 * rows_local * f.world * n * k, sms_);
+  f.copy_done_counter = words_ + 29;
   f.epoch_ptr = words_ + 0;
   for (int r = 0; r < f.world; ++r) f.a_peer[r] = static_cast<const char*>(x_sym.ptrs[r]) + x_off;
   f.a_gathered = gathered;
@@ -88,7 +107,11 @@ void TpGemm::ag_gemm(const SymmAlloc& x_sym, size_t x_off, int rows_local, int k
   a.ldd = n;
   a.b_mn_major = w_kn;
   a.epilogue = epilogue;
-  MCCL_CUDA_CHECK(launch_bump_epoch(words_ + 0, nullptr, stream));
+  BumpArgs b;
+  b.epoch = words_ + 0;
+  b.n_announce = f.world;
+  for (int p = 0; p < f.world; ++p) b.announce[p] = p == f.rank ? nullptr : f.sig[p] + kFuseSigAgReady + f.rank;
+  MCCL_CUDA_CHECK(launch_bump_epoch(b, stream));
   cudaError_t rc = launch_gemm_persistent(a, f, sms_, stream);
   MCCL_CHECK_T(rc == cudaSuccess, CudaError, "ag_gemm launch failed: " << cudaGetErrorString(rc));
 }
@@ -128,7 +151,10 @@ void TpGemm::gemm_rs(const __nv_bfloat16* x, int ldx, int rows_local, int k, con
   a.ldb = ldw;
   a.ldd = n;
   a.b_mn_major = w_kn;
-  MCCL_CUDA_CHECK(launch_bump_epoch(words_ + 1, words_ + 28, stream));
+  BumpArgs b;
+  b.epoch = words_ + 1;
+  b.zeroed = words_ + 28;
+  MCCL_CUDA_CHECK(launch_bump_epoch(b, stream));
   cudaError_t rc = launch_gemm_persistent(a, f, sms_, stream);
   MCCL_CHECK_T(rc == cudaSuccess, CudaError, "gemm_rs launch failed: " << cudaGetErrorString(rc));
 }

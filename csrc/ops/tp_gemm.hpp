@@ -54,7 +54,7 @@ class TpGemm {
   std::shared_ptr<DeviceComm> comm_;
   std::shared_ptr<SymmAlloc> sig_, stage_;
   size_t max_rs_elems_;
-  uint32_t* words_ = nullptr;   // device: [0] ag epoch, [1] rs epoch, [8..16) chunk flags, [16..24) chunk counters, [24..28) phase counters, [28] piece counter
+  uint32_t* words_ = nullptr;   // device: [0] ag epoch, [1] rs epoch, [8..16) chunk flags, [16..24) chunk counters, [24..28) phase counters, [28] piece counter, [29] finished copy CTAs
   int* status_host_ = nullptr;
   int* status_dev_ = nullptr;
   int sms_ = 148;
