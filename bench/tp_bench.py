@@ -47,7 +47,7 @@ def main() -> None:
     cfg = MODELS[args.model]
     rows_local = cfg["batch"] * cfg["seq"] // world
     ctx = TensorParallelContext(device=dev, max_rows_local=rows_local, max_features=cfg["d_model"],
-                                fused=args.impl == "mccl")
+                                fused=args.impl == "mccl", ag_slots=4 * cfg["n_layers"] + 8)
     torch.manual_seed(1234 + rank)
     model = TPDecoder(ctx, **cfg).to(dev)
     for p in model.replicated_parameters():
