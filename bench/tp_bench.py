@@ -35,6 +35,8 @@ def main() -> None:
     ap.add_argument("--model", default="1.3b", choices=sorted(MODELS))
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--pp", type=int, default=1, help="pipeline stages; tensor parallelism runs over world / pp ranks per stage")
+    ap.add_argument("--microbatches", type=int, default=4, help="micro-batches per step when --pp > 1")
     args = ap.parse_args()
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     local = int(os.environ.get("LOCAL_RANK", 0))
@@ -44,26 +46,58 @@ def main() -> None:
     from mccl_b200.parallel.tp import TensorParallelContext, TPDecoder
     from mccl_b200.utils.clocks import ClockSampler
     dist.init_process_group(backend=args.impl, device_id=dev if args.impl == "nccl" else None)
-    cfg = MODELS[args.model]
-    rows_local = cfg["batch"] * cfg["seq"] // world
-    ctx = TensorParallelContext(device=dev, max_rows_local=rows_local, max_features=cfg["d_model"],
-                                fused=args.impl == "mccl", ag_slots=4 * cfg["n_layers"] + 8)
+    cfg = dict(MODELS[args.model])
+    pp = args.pp
+    tp_size = world // pp
+    stage, tp_rank = rank // tp_size, rank % tp_size
+    tp_group = None
+    if pp > 1:
+        for s in range(pp):   # every rank creates every group
+            g_ = dist.new_group(list(range(s * tp_size, (s + 1) * tp_size)), backend=args.impl)
+            if s == stage:
+                tp_group = g_
+    n_mb = args.microbatches if pp > 1 else 1
+    mb_batch = cfg["batch"] // n_mb
+    rows_local = mb_batch * cfg["seq"] // tp_size
+    from mccl_b200.parallel.pp import PipelineStage, split_layers
+    layers = split_layers(cfg["n_layers"], pp)[stage]
+    ctx = TensorParallelContext(group=tp_group, device=dev, max_rows_local=rows_local, max_features=cfg["d_model"],
+                                fused=args.impl == "mccl", ag_slots=4 * len(layers) * min(n_mb, pp) + 8)
     torch.manual_seed(1234 + rank)
-    model = TPDecoder(ctx, **cfg).to(dev)
+    mcfg = dict(cfg, batch=mb_batch)
+    model = TPDecoder(ctx, layers_range=(layers.start, layers.stop), **mcfg).to(dev)
     for p in model.replicated_parameters():
-        dist.broadcast(p.data, 0)
+        dist.broadcast(p.data, stage * tp_size, group=tp_group)
     opt = torch.optim.AdamW(model.parameters(), lr=1e-4, fused=True)
     g = torch.Generator().manual_seed(99)
     tokens = torch.randint(0, cfg["vocab"], (cfg["batch"], cfg["seq"] + 1), generator=g).to(dev)
     inp, tgt = tokens[:, :-1].contiguous(), tokens[:, 1:].contiguous()
 
-    def step():
-        opt.zero_grad(set_to_none=True)
-        loss = model(inp, tgt)
-        loss.backward()
-        model.sync_replicated_grads()
-        opt.step()
-        return loss
+    if pp == 1:
+        def step():
+            opt.zero_grad(set_to_none=True)
+            loss = model(inp, tgt)
+            loss.backward()
+            model.sync_replicated_grads()
+            opt.step()
+            return loss
+    else:
+        def fn(x, mb):
+            sl = slice(mb * mb_batch, (mb + 1) * mb_batch)
+            if stage == 0:
+                return model(inp[sl], None)
+            out = model(inp[sl] if stage == 0 else None, tgt[sl] if stage == pp - 1 else None, hidden=x)
+            return out / n_mb if stage == pp - 1 else out
+
+        pipe = PipelineStage(fn, stage, pp, rank - tp_size if stage > 0 else None, rank + tp_size if stage < pp - 1 else None,
+                             (rows_local, cfg["d_model"]), torch.bfloat16, dev)
+
+        def step():
+            opt.zero_grad(set_to_none=True)
+            loss = pipe.run(n_mb)
+            model.sync_replicated_grads()
+            opt.step()
+            return loss if loss is not None else torch.zeros((), device=dev)
 
     for _ in range(max(args.warmup, 3)):
         loss = step()
@@ -82,7 +116,7 @@ def main() -> None:
     clocks = sampler.stop() if sampler else None
     ms = torch.tensor([e0.elapsed_time(e1) / args.steps], device=dev)
     dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-    total = loss.detach().clone()
+    total = loss.detach().clone().float()
     dist.all_reduce(total)
     ctx.check()
     if rank == 0:
@@ -91,7 +125,8 @@ def main() -> None:
             "metric": "tp_decoder_train_tokens_per_sec", "impl": args.impl, "value": tokens_per_step / (ms.item() / 1e3),
             "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms.item(),
             "loss": total.item(), "dtype": "bf16", "data": "synthetic",
-            "config": {"model": args.model, **cfg, "parallelism": f"tp{world}", "inputs": "activations larger than L2"},
+            "config": {"model": args.model, **cfg, "parallelism": f"tp{tp_size}" + (f" x pp{pp} ({n_mb} micro-batches, 1F1B)" if pp > 1 else ""),
+                       "inputs": "activations larger than L2"},
             "clocks": clocks,
         }), flush=True)
     dist.barrier()

@@ -14,6 +14,10 @@
 
 #include "../core/log.hpp"
 #include "../core/version.hpp"
+#include <nvtx3/nvToolsExt.h>
+
+#include <cstdlib>
+
 #include "../engine/metrics.hpp"
 #include "../pg/device_comm.hpp"
 #include "../pg/process_group.hpp"
@@ -92,6 +96,19 @@ void bind_pg(py::module_& m) {
       .def_readonly("ops_by_name", &MetricsSummary::ops_by_name)
       .def_readonly("bytes_by_algo", &MetricsSummary::bytes_by_algo);
   m.def("get_metrics", [] { return Metrics::global().summarize(); });
+  m.def("set_trace", [](const std::string& path) { Metrics::global().set_trace(path); }, py::arg("path"),
+        "Append every finished op to <path>.<pid> as one Chrome-trace event per line; an empty path stops tracing.");
+  m.def("enable_nvtx", [](bool on) {
+    if (on)
+      Metrics::global().set_nvtx([](const char* name) -> uint64_t { return static_cast<uint64_t>(nvtxRangeStartA(name)); },
+                                 [](uint64_t id) { nvtxRangeEnd(static_cast<nvtxRangeId_t>(id)); });
+    else
+      Metrics::global().set_nvtx(nullptr, nullptr);
+  }, py::arg("on") = true, "Bracket every collective with an NVTX range (also switched on by MCCL_NVTX=1 at import).");
+  if (const char* nv = std::getenv("MCCL_NVTX"))
+    if (nv[0] == '1')
+      Metrics::global().set_nvtx([](const char* name) -> uint64_t { return static_cast<uint64_t>(nvtxRangeStartA(name)); },
+                                 [](uint64_t id) { nvtxRangeEnd(static_cast<nvtxRangeId_t>(id)); });
   m.def("reset_metrics", [] { Metrics::global().reset(); });
   m.def("metrics_history", [] {
     py::list out;

@@ -9,11 +9,23 @@
 // pair around the kernels) and host time; CPU collectives keep the
 // sync / network / reduce split.  Python reads the summary through
 // mccl.get_metrics().
+//
+// Tracing: with MCCL_TRACE=<path> every finished op is appended to <path>.<pid>
+// as one Chrome-trace event per line ({"name","ph":"X","ts","dur","pid","tid",
+// "args":{bytes,algo,queue_wait_ms,device_ms,...}}), which chrome://tracing and
+// Perfetto load after wrapping the lines in [ ].  With MCCL_NVTX=1 the same ops
+// are bracketed by NVTX ranges (begin at submit, end at completion) so that they
+// line up with the kernels in a timeline profiler.  The reference has only
+// os_signpost calls for Instruments (csrc/metal/MPSInterop.mm:338-349).
 #pragma once
+
+#include <unistd.h>
 
 #include <algorithm>
 #include <chrono>
 #include <cstdint>
+#include <cstdio>
+#include <cstdlib>
 #include <deque>
 #include <map>
 #include <mutex>
@@ -30,6 +42,7 @@ struct OpMetric {
   double start_us = 0, execute_start_us = 0, end_us = 0;
   double sync_ms = 0, network_ms = 0, reduce_ms = 0, device_ms = 0;
   bool failed = false;
+  uint64_t nvtx_id = 0;
   double latency_ms() const { return (end_us - start_us) / 1e3; }
   double queue_wait_ms() const { return (execute_start_us - start_us) / 1e3; }
   double execution_ms() const { return (end_us - execute_start_us) / 1e3; }
@@ -69,7 +82,24 @@ class Metrics {
     m.bytes = bytes;
     m.start_us = m.execute_start_us = now_us();
     inflight_[m.seq] = m;
+    if (nvtx_begin_) m.nvtx_id = nvtx_begin_(name.c_str());
+    inflight_[m.seq].nvtx_id = m.nvtx_id;
     return m.seq;
+  }
+  // Installed by the CUDA side (the host-only build has no NVTX): begin returns a range id, end closes it.
+  void set_nvtx(uint64_t (*begin)(const char*), void (*end)(uint64_t)) {
+    std::lock_guard<std::mutex> g(mu_);
+    nvtx_begin_ = begin;
+    nvtx_end_ = end;
+  }
+  // Appends finished ops to `path`.<pid>; an empty path turns tracing off.
+  void set_trace(const std::string& path) {
+    std::lock_guard<std::mutex> g(mu_);
+    if (trace_) {
+      std::fclose(trace_);
+      trace_ = nullptr;
+    }
+    if (!path.empty()) trace_ = std::fopen((path + "." + std::to_string(static_cast<long>(getpid()))).c_str(), "a");
   }
   void op_execute_start(uint64_t seq) {
     std::lock_guard<std::mutex> g(mu_);
@@ -95,6 +125,23 @@ class Metrics {
     it->second.end_us = now_us();
     it->second.failed = failed;
     if (failed) ++errors_;
+    if (nvtx_end_ && it->second.nvtx_id) nvtx_end_(it->second.nvtx_id);
+    if (!trace_checked_) {
+      trace_checked_ = true;
+      const char* tp = std::getenv("MCCL_TRACE");
+      if (tp && *tp && !trace_) trace_ = std::fopen((std::string(tp) + "." + std::to_string(static_cast<long>(getpid()))).c_str(), "a");
+    }
+    if (trace_) {
+      const OpMetric& m = it->second;
+      std::fprintf(trace_,
+                   "{\"name\":\"%s\",\"ph\":\"X\",\"ts\":%.3f,\"dur\":%.3f,\"pid\":%ld,\"tid\":0,\"args\":{\"seq\":%llu,\"bytes\":%llu,"
+                   "\"algo\":\"%s\",\"queue_wait_ms\":%.4f,\"device_ms\":%.4f,\"sync_ms\":%.4f,\"network_ms\":%.4f,\"reduce_ms\":%.4f,"
+                   "\"failed\":%s}},\n",
+                   m.name.c_str(), m.start_us, m.end_us - m.start_us, static_cast<long>(getpid()),
+                   static_cast<unsigned long long>(m.seq), static_cast<unsigned long long>(m.bytes), m.algo.c_str(), m.queue_wait_ms(),
+                   m.device_ms, m.sync_ms, m.network_ms, m.reduce_ms, m.failed ? "true" : "false");
+      std::fflush(trace_);
+    }
     history_.push_back(it->second);
     if (history_.size() > kHistoryCap) history_.pop_front();
     ++total_ops_;
@@ -167,6 +214,10 @@ class Metrics {
   std::map<uint64_t, OpMetric> inflight_;
   std::deque<OpMetric> history_;
   uint64_t total_ops_ = 0, total_bytes_ = 0, errors_ = 0, tx_ = 0, rx_ = 0;
+  std::FILE* trace_ = nullptr;
+  bool trace_checked_ = false;
+  uint64_t (*nvtx_begin_)(const char*) = nullptr;
+  void (*nvtx_end_)(uint64_t) = nullptr;
 };
 
 }  // namespace mccl

@@ -25,6 +25,19 @@ def metrics_history():
     return _C.metrics_history()
 
 
+def set_trace(path: str) -> None:
+    """Appends every finished collective to ``<path>.<pid>`` as a Chrome-trace event (one JSON object per
+    line); ``""`` stops.  ``MCCL_TRACE=<path>`` in the environment does the same from the first op on."""
+    from . import _C
+    _C.set_trace(path)
+
+
+def enable_nvtx(on: bool = True) -> None:
+    """Brackets every collective with an NVTX range (``MCCL_NVTX=1`` switches it on at import)."""
+    from . import _C
+    _C.enable_nvtx(on)
+
+
 def log_metrics(file=None) -> None:
     m = get_metrics()
     out = file or sys.stderr
