@@ -62,7 +62,7 @@ def main() -> None:
     from mccl_b200.parallel.pp import PipelineStage, split_layers
     layers = split_layers(cfg["n_layers"], pp)[stage]
     ctx = TensorParallelContext(group=tp_group, device=dev, max_rows_local=rows_local, max_features=cfg["d_model"],
-                                fused=args.impl == "mccl", ag_slots=4 * len(layers) * min(n_mb, pp) + 8)
+                                fused=args.impl == "mccl")
     torch.manual_seed(1234 + rank)
     mcfg = dict(cfg, batch=mb_batch)
     model = TPDecoder(ctx, layers_range=(layers.start, layers.stop), **mcfg).to(dev)

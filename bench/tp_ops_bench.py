@@ -6,9 +6,9 @@
 For every GEMM of one 1.3B decoder layer under N-way tensor parallelism (tokens 16384, d_model
 2048, FFN 8192) it times
 
-* ``ag_gemm``   (one kernel: the activation shards are pushed to the peers while the tcgen05 tiles run)
+* ``ag_gemm``   (one kernel: all-gather of the activation shard overlapped with the tcgen05 tiles)
   against ``all_gather_into_tensor`` + ``torch.matmul`` on the same `mccl` group's NCCL twin, and
-* ``gemm_rs``   (one kernel: partial rows pushed into the owner's staging, in-kernel reduction)
+* ``gemm_rs``   (one kernel: tiles stored into the owner's staging slot, in-kernel reduction)
   against ``torch.matmul`` + ``reduce_scatter_tensor``.
 
 Device time from CUDA events around `iters` back-to-back calls, max over ranks.  The roofline
@@ -50,8 +50,6 @@ def main() -> None:
     ap.add_argument("--tokens", type=int, default=16384)
     ap.add_argument("--d-model", type=int, default=2048)
     ap.add_argument("--d-ff", type=int, default=8192)
-    ap.add_argument("--comm-only", action="store_true",
-                    help="time ag_gemm with a 64-column weight (the tiles are negligible): the all-gather transfer rate")
     args = ap.parse_args()
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     local = int(os.environ.get("LOCAL_RANK", 0))
@@ -65,6 +63,7 @@ def main() -> None:
     T, D, FF = args.tokens, args.d_model, args.d_ff
     rows = T // world
     tp = _C.TpGemm(comm, rows * D)
+    sym = comm.symm_alloc(rows * D * 2)
     peak = 1.38e15
     p = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
     if os.path.exists(p):
@@ -72,22 +71,11 @@ def main() -> None:
     link = 770e9
     results = []
     torch.manual_seed(rank)
-    if args.comm_only:
-        x = torch.randn(rows, D, device=dev).bfloat16()
-        w = torch.randn(64, D, device=dev).bfloat16()
-        t = timed(lambda: tp.ag_gemm(x, w, False), args.iters, dev)
-        nv = (world - 1) * rows * D * 2
-        tp.check_status()
-        if rank == 0:
-            print(f"comm-only world {world} copy_ctas {os.environ.get('MCCL_TP_COPY_CTAS', 'auto')}: {t:.1f} us, "
-                  f"{nv / t / 1e3:.1f} GB/s per GPU over NVLink ({nv / 1e6:.1f} MB)")
-        dist.barrier()
-        dist.destroy_process_group()
-        return
     # all-gather -> GEMM: (name, N_out, weight stored [K, N]?)
     for name, n_out, w_kn in [("qkv fwd", 3 * D // world, False), ("gate_up fwd", 2 * FF // world, False),
                               ("proj dgrad", D // world, True), ("down dgrad", FF // world, True)]:
         x = torch.randn(rows, D, device=dev).bfloat16()
+        sym.tensor(rank, 0, [rows, D], torch.bfloat16, local).copy_(x)
         w = (torch.randn(D, n_out, device=dev) if w_kn else torch.randn(n_out, D, device=dev)).bfloat16()
         full = torch.empty(T, D, dtype=torch.bfloat16, device=dev)
 
@@ -95,7 +83,7 @@ def main() -> None:
             dist.all_gather_into_tensor(full, x, group=nccl)
             return torch.matmul(full, w if w_kn else w.t())
 
-        t_f = timed(lambda: tp.ag_gemm(x, w, w_kn), args.iters, dev)
+        t_f = timed(lambda: tp.ag_gemm(sym, 0, rows, w, w_kn), args.iters, dev)
         t_b = timed(base, args.iters, dev)
         flops = 2.0 * T * n_out * D
         nv = (world - 1) * rows * D * 2

@@ -221,7 +221,7 @@ void bind_ops(py::module_& m) {
 
   // ---- tensor-parallel GEMMs fused with their collective ----
   py::class_<ops::TpGemm>(m, "TpGemm")
-      .def(py::init<std::shared_ptr<DeviceComm>, size_t, int>(), py::arg("comm"), py::arg("max_chunk_elems"), py::arg("ag_slots") = 4,
+      .def(py::init<std::shared_ptr<DeviceComm>, size_t>(), py::arg("comm"), py::arg("max_rs_elems"),
            py::call_guard<py::gil_scoped_release>())
       .def_property_readonly("world", &ops::TpGemm::world)
       .def_property_readonly("rank", &ops::TpGemm::rank)
@@ -229,17 +229,15 @@ void bind_ops(py::module_& m) {
       .def("check_status", &ops::TpGemm::check_status)
       .def(
           "ag_gemm",
-          [](ops::TpGemm& t, const at::Tensor& x, const at::Tensor& w, bool w_kn, const c10::optional<at::Tensor>& bias,
-             const std::string& epilogue) {
-            need(x, at::kBFloat16, "ag_gemm(x)");
+          [](ops::TpGemm& t, std::shared_ptr<SymmAlloc> x_sym, int64_t x_off, int64_t rows_local, const at::Tensor& w, bool w_kn,
+             const c10::optional<at::Tensor>& bias, const std::string& epilogue) {
             need_cuda(w, "ag_gemm(w)");
-            MCCL_CHECK_TENSOR(x.dim() == 2, "ag_gemm: x must be [rows_local, K]");
             MCCL_CHECK_TENSOR(w.scalar_type() == at::kBFloat16 && w.dim() == 2 && w.stride(1) == 1, "ag_gemm: w must be 2-D bf16");
             c10::cuda::CUDAGuard guard(w.device());
             const int64_t K = w_kn ? w.size(0) : w.size(1), N = w_kn ? w.size(1) : w.size(0);
-            MCCL_CHECK_TENSOR(x.size(1) == K, "ag_gemm: x has " << x.size(1) << " columns, the weight contracts over " << K);
-            const int64_t rows_local = x.size(0), rows = rows_local * t.world();
+            const int64_t rows = rows_local * t.world();
             at::Tensor y = at::empty({rows, N}, w.options());
+            at::Tensor gathered = at::empty({rows, K}, w.options());
             const float* bp = nullptr;
             if (bias.has_value() && bias->defined()) {
               need(*bias, at::kFloat, "ag_gemm(bias)");
@@ -248,20 +246,15 @@ void bind_ops(py::module_& m) {
             const int epi = parse_epilogue(epilogue, bp != nullptr);
             at::Tensor aux;
             if (epi == ops::EPI_BIAS_GELU || epi == ops::EPI_GELU) aux = at::empty({rows, N}, w.options());
-            uint64_t generation = 0;
-            __nv_bfloat16* slot = t.ag_gemm(bf(x), static_cast<int>(rows_local), static_cast<int>(K), bf(w), static_cast<int>(w.stride(0)),
-                                            w_kn, static_cast<int>(N), bf(y), bp, epi, aux.defined() ? bf(aux) : nullptr, stream_of(w),
-                                            &generation);
-            // a view of the ring slot: valid until the ring wraps (TpGemm.ag_valid(generation))
-            at::Tensor gathered = at::from_blob(slot, {rows, K}, w.options());
+            t.ag_gemm(*x_sym, static_cast<size_t>(x_off), static_cast<int>(rows_local), static_cast<int>(K), bf(w),
+                      static_cast<int>(w.stride(0)), w_kn, static_cast<int>(N), bf(y), bf(gathered), bp, epi,
+                      aux.defined() ? bf(aux) : nullptr, stream_of(w));
             ops::count_launch(1);
-            return std::make_tuple(y, gathered, aux.defined() ? c10::optional<at::Tensor>(aux) : c10::nullopt, generation);
+            return std::make_tuple(y, gathered, aux.defined() ? c10::optional<at::Tensor>(aux) : c10::nullopt);
           },
-          py::arg("x"), py::arg("w"), py::arg("w_kn") = false, py::arg("bias") = py::none(), py::arg("epilogue") = "none",
-          "x: this rank's [rows_local, K] shard.  Returns (all_gather(x) @ w^T, gathered x, pre-activation or None, generation); "
-          "`gathered` is a view of a ring slot that stays valid while ag_valid(generation).")
-      .def("ag_valid", &ops::TpGemm::ag_valid, py::arg("generation"))
-      .def_property_readonly("ag_slots", &ops::TpGemm::ag_slots)
+          py::arg("x_sym"), py::arg("x_offset"), py::arg("rows_local"), py::arg("w"), py::arg("w_kn") = false,
+          py::arg("bias") = py::none(), py::arg("epilogue") = "none",
+          "Returns (all_gather(x) @ w^T, gathered x, pre-activation or None).")
       .def(
           "gemm_rs",
           [](ops::TpGemm& t, const at::Tensor& x, const at::Tensor& w, bool w_kn) {

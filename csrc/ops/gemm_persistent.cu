@@ -57,6 +57,23 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, vo
   }
 }
 
+// Spin on a flag word in global memory written by another CTA of this GPU (chunk
+// arrival in the all-gather fusion).  Bounded; false on timeout.
+__device__ __forceinline__ bool wait_flag_geq(const uint32_t* flag, uint32_t value, volatile int* abort_flag, unsigned long long limit_ns) {
+  const unsigned long long t0 = now_ns();
+  for (uint32_t i = 0;; ++i) {
+    uint32_t v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+    if (static_cast<int32_t>(v - value) >= 0) return true;
+    if ((i & 63u) == 63u) {
+      if (*abort_flag) return false;
+      if (now_ns() - t0 > limit_ns) return false;
+    }
+    __nanosleep(64);
+  }
+}
+
+
 // ---- cross-GPU signalling for the fused roles (bounded waits, status word on timeout) ----
 __device__ __forceinline__ void sig_store(uint32_t* p, uint32_t v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
@@ -75,21 +92,23 @@ __device__ __forceinline__ bool sig_wait(const uint32_t* p, uint32_t v, unsigned
     }
   }
 }
-// sig_wait that also gives up when another role of this CTA has failed.
-__device__ __forceinline__ bool sig_wait_abortable(const uint32_t* p, uint32_t v, volatile int* abort_flag, unsigned long long timeout_ns) {
-  const unsigned long long t0 = now_ns();
-  for (unsigned spins = 0;; ++spins) {
-    uint32_t cur;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(cur) : "l"(p) : "memory");
-    if (static_cast<int32_t>(cur - v) >= 0) return true;
-    if ((spins & 63u) == 63u && (*abort_flag || now_ns() - t0 > timeout_ns)) return false;
-    __nanosleep(32);
+// Meeting of copy CTA `cta` of every rank.  Returns false when a peer did not arrive in time.
+__device__ __forceinline__ bool copy_cta_meet(const FusedDev& f, int cta, uint32_t value) {
+  __syncthreads();
+  bool bad = false;
+  const int t = threadIdx.x;
+  if (t < f.world) {
+    __threadfence_system();
+    sig_store(f.sig[t] + kFuseSigAg + 8 * cta + f.rank, value);
+    bad = !sig_wait(f.sig[f.rank] + kFuseSigAg + 8 * cta + t, value, f.timeout_ns);
+    if (bad) atomicCAS(f.status, 0, 0x100 + t);
   }
+  return __syncthreads_or(bad ? 1 : 0) == 0;
 }
-// Bulk (TMA, untiled, no multicast) copy engine of a data-moving CTA: one thread streams a byte range
-// of local memory through `kCopyStages` shared-memory buffers to up to kFuseMaxRanks destinations
-// (peers' staging over NVLink as posted writes, and / or local memory), so that several pieces are in
-// flight with a single thread issuing.  Addresses and sizes are multiples of 16 bytes.
+// Bulk (TMA, untiled, no multicast) copy engine of a copy CTA: one thread streams [b0, b1) of
+// `src` (possibly a peer's memory) to `dst` (local) through `stages` shared-memory buffers of
+// `piece` bytes, so that (stages - 1) * piece bytes are in flight per CTA with a single thread
+// issuing.  Addresses and sizes are multiples of 16 bytes.  Returns false when a load never landed.
 __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(tc::smem_u32(smem_dst)),
                "l"(gsrc), "r"(bytes), "r"(tc::smem_u32(bar))
@@ -98,28 +117,24 @@ __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint
 __device__ __forceinline__ void bulk_store(void* gdst, const void* smem_src, uint32_t bytes) {
   asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(tc::smem_u32(smem_src)), "r"(bytes)
                : "memory");
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
-__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 constexpr int kCopyStages = 4;
 constexpr uint32_t kCopyPiece = 48 * 1024;
 
 struct CopyEngine {
   uint8_t* buf;       // kCopyStages * kCopyPiece bytes of shared memory, 128-byte aligned
   uint64_t* full;     // kCopyStages barriers
-  uint32_t issued;    // loads issued so far
-  uint32_t drained;   // pieces handed to stores so far
+  uint32_t issued;    // loads issued so far (all chunks)
+  uint32_t drained;   // pieces stored so far
 };
 
-// Streams src[b0, b1) to dst[d][b0, b1) for d < ndst; returns when the last piece has been handed to its
-// stores (they may still be in flight: cp.async.bulk.wait_group 0 completes them).  False when a load
-// never landed.
-__device__ bool copy_range(CopyEngine& e, char* const* dst, int ndst, const char* src, unsigned long long b0, unsigned long long b1,
+// Streams one byte range and returns when its last piece has been handed to a store.
+__device__ bool copy_range(CopyEngine& e, char* dst, const char* src, unsigned long long b0, unsigned long long b1,
                            unsigned long long limit_ns) {
   const unsigned long long total = b1 - b0;
   const uint32_t pieces = static_cast<uint32_t>((total + kCopyPiece - 1) / kCopyPiece);
   uint32_t loaded = 0;
-  // stores of an earlier range may still be reading the stages this range is about to refill
-  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
   auto issue = [&](uint32_t j) {
     const unsigned long long off = static_cast<unsigned long long>(j) * kCopyPiece;
     const uint32_t n = static_cast<uint32_t>(total - off < kCopyPiece ? total - off : kCopyPiece);
@@ -128,7 +143,7 @@ __device__ bool copy_range(CopyEngine& e, char* const* dst, int ndst, const char
     bulk_load(e.buf + static_cast<size_t>(s) * kCopyPiece, src + b0 + off, n, &e.full[s]);
     ++e.issued;
   };
-  // a stage may be refilled once the stores that read it have finished reading: keep one stage for that
+  // a stage may be refilled once the store that read it has finished reading: keep one stage for that
   while (loaded < pieces && e.issued - e.drained < kCopyStages - 1) issue(loaded++);
   for (uint32_t j = 0; j < pieces; ++j) {
     const uint32_t s = e.drained % kCopyStages;
@@ -137,119 +152,68 @@ __device__ bool copy_range(CopyEngine& e, char* const* dst, int ndst, const char
       if (now_ns() - t0 > limit_ns) return false;
     const unsigned long long off = static_cast<unsigned long long>(j) * kCopyPiece;
     const uint32_t n = static_cast<uint32_t>(total - off < kCopyPiece ? total - off : kCopyPiece);
-    for (int d = 0; d < ndst; ++d) bulk_store(dst[d] + b0 + off, e.buf + static_cast<size_t>(s) * kCopyPiece, n);
-    bulk_commit();   // one group per piece
+    bulk_store(dst + b0 + off, e.buf + static_cast<size_t>(s) * kCopyPiece, n);
     ++e.drained;
     if (loaded < pieces) {
       // the stage to refill is the one stored in the previous iteration: wait until at most the newest
-      // group is still reading shared memory
+      // store is still reading shared memory
       asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
       issue(loaded++);
     }
   }
   return true;
 }
-// Loads still in flight must land, and queued stores must have read shared memory, before a CTA retires.
-__device__ void copy_engine_quiesce(CopyEngine& e) {
-  asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
-  for (uint32_t j = e.drained; j < e.issued; ++j) tc::mbar_wait(&e.full[j % kCopyStages], (j / kCopyStages) & 1u, 1u << 22);
-}
-// Stores of this thread's bulk groups are complete and ordered before what follows, for every GPU.
-__device__ __forceinline__ void bulk_stores_done_fence() {
-  asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
-  asm volatile("fence.proxy.async;" ::: "memory");
-  __threadfence_system();
-}
-// This CTA's byte share [b0, b1) of a block of `bytes` bytes split over `parts` CTAs in 16-byte units.
-__device__ __forceinline__ void cta_share(unsigned long long bytes, int part, int parts, unsigned long long& b0, unsigned long long& b1) {
-  const unsigned long long units = bytes / 16, per = (units + parts - 1) / parts;
-  b0 = part * per * 16;
-  b1 = b0 + per * 16;
-  if (b0 > bytes) b0 = bytes;
-  if (b1 > bytes) b1 = bytes;
-}
 
-// Role of CTAs [0, copy_ctas) in the all-gather fusion (one thread per CTA drives the engine).
-//   step 0        own shard → chunk `rank` of the local slot (the slot is what the backward pass keeps)
-//   step k >= 1   own shard → chunk `rank` of the slot of rank (rank + k) % world; the copy CTA that
-//                 finishes a step last raises that rank's flag for this chunk
+// Role of CTAs [0, copy_ctas) in the all-gather fusion: meet the peers (their shards are
+// complete), pull the shards chunk by chunk starting with the own one, raise a chunk's flag
+// when every copy CTA has finished it, meet again (nobody reads my shard any more).
 __device__ void allgather_copy_role(const FusedDev& f, uint32_t epoch, uint8_t* smem) {
-  if (threadIdx.x != 0) return;
+  const int cta = blockIdx.x;
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + kCopyStages * kCopyPiece);
-  for (int s = 0; s < kCopyStages; ++s) tc::mbar_init(&full[s], 1);
-  tc::mbar_init_fence();
-  unsigned long long b0, b1;
-  cta_share(f.chunk_bytes, blockIdx.x, f.copy_ctas, b0, b1);
-  CopyEngine e{smem, full, 0u, 0u};
-  const size_t my_off = static_cast<size_t>(f.rank) * f.chunk_bytes;
-  asm volatile("fence.proxy.async;" ::: "memory");   // the shard was written with ordinary stores
-  bool ok = true;
-  for (int k = 1; k < f.world && ok; ++k) {
-    const int p = (f.rank + k) % f.world;
-    char* dst[1] = {static_cast<char*>(f.a_stage[p]) + my_off};
-    if (b1 > b0) ok = copy_range(e, dst, 1, static_cast<const char*>(f.a_own), b0, b1, f.timeout_ns);
-    if (!ok) break;
-    bulk_stores_done_fence();
-    if (atomicAdd(f.step_counters + k, 1u) + 1u == static_cast<uint32_t>(f.copy_ctas)) {
-      atomicExch(f.step_counters + k, 0u);
-      __threadfence_system();
-      sig_store(f.sig[p] + kFuseSigAg + f.rank, epoch);
-    }
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kCopyStages; ++s) tc::mbar_init(&full[s], 1);
+    tc::mbar_init_fence();
   }
-  if (ok && b1 > b0) {
-    char* dst[1] = {static_cast<char*>(f.a_stage[f.rank]) + my_off};
-    ok = copy_range(e, dst, 1, static_cast<const char*>(f.a_own), b0, b1, f.timeout_ns);
-  }
-  if (!ok) atomicCAS(f.status, 0, 0x100 + f.rank);
-  copy_engine_quiesce(e);
-}
-
-// Push side of the reduce-scatter fusion, CTAs [0, copy_ctas), one thread per CTA: as soon as this
-// rank's partial product has reached a phase, the rows of that phase that other ranks own are sent into
-// slot `rank` of the owner's staging, one owner after the other; the pusher that finishes an
-// (owner, phase) block last raises the owner's flag for it.
-__device__ void reduce_scatter_push_role(const FusedDev& f, uint32_t epoch, uint8_t* smem) {
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + kCopyStages * kCopyPiece);
-  for (int s = 0; s < kCopyStages; ++s) tc::mbar_init(&full[s], 1);
-  tc::mbar_init_fence();
-  const unsigned long long phase_bytes = f.chunk_bytes / f.rs_phases;
-  unsigned long long b0, b1;
-  cta_share(phase_bytes, blockIdx.x, f.copy_ctas, b0, b1);
-  CopyEngine e{smem, full, 0u, 0u};
-  const uint32_t par = epoch & 1u;
-  bool ok = true;
-  for (int ph = 0; ph < f.rs_phases && ok; ++ph) {
-    if (!sig_wait(f.sig[f.rank] + kFuseSigRs + 4 * f.rank + ph, epoch, f.timeout_ns + 2000000000ull)) {
-      ok = false;
-      break;
-    }
-    asm volatile("fence.proxy.async;" ::: "memory");   // the partial product was written with ordinary stores
-    for (int k = 1; k < f.world && ok; ++k) {
-      const int p = (f.rank + k) % f.world;
-      const size_t blk = static_cast<size_t>(ph) * phase_bytes;
-      char* dst[1] = {static_cast<char*>(f.rs_stage[par][p]) + static_cast<size_t>(f.rank) * f.chunk_bytes + blk};
+  if (!copy_cta_meet(f, cta, 2 * epoch - 1)) return;
+  const unsigned long long units = f.chunk_bytes / 16;
+  const unsigned long long per = (units + f.copy_ctas - 1) / f.copy_ctas;
+  unsigned long long b0 = cta * per * 16, b1 = b0 + per * 16;
+  if (b0 > f.chunk_bytes) b0 = f.chunk_bytes;
+  if (b1 > f.chunk_bytes) b1 = f.chunk_bytes;
+  if (threadIdx.x == 0) {
+    asm volatile("fence.proxy.async;" ::: "memory");   // the shards were written with ordinary stores
+    CopyEngine e{smem, full, 0u, 0u};
+    bool ok = true;
+    for (int k = 0; k < f.world && ok; ++k) {
+      const int c = (f.rank + k) % f.world;
       if (b1 > b0)
-        ok = copy_range(e, dst, 1, static_cast<const char*>(f.rs_partial) + static_cast<size_t>(p) * f.chunk_bytes + blk, b0, b1,
-                        f.timeout_ns);
+        ok = copy_range(e, static_cast<char*>(f.a_gathered) + static_cast<size_t>(c) * f.chunk_bytes,
+                        static_cast<const char*>(f.a_peer[c]), b0, b1, f.timeout_ns);
       if (!ok) break;
-      bulk_stores_done_fence();
-      if (atomicAdd(f.push_counters + p * kFuseMaxPhases + ph, 1u) + 1u == static_cast<uint32_t>(f.copy_ctas)) {
-        atomicExch(f.push_counters + p * kFuseMaxPhases + ph, 0u);
-        __threadfence_system();
-        sig_store(f.sig[p] + kFuseSigRs + 4 * f.rank + ph, epoch);
-      }
+      // the chunk's bytes must be in global memory before its flag can rise
+      asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+      asm volatile("fence.proxy.async;" ::: "memory");
+      __threadfence();
+      const uint32_t arrived = atomicAdd(f.chunk_counters + c, 1u) + 1u;
+      if (arrived == static_cast<uint32_t>(f.copy_ctas) * epoch)
+        asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(f.chunk_flags + c), "r"(epoch) : "memory");
+    }
+    if (!ok) {
+      atomicCAS(f.status, 0, 0x100 + f.rank);
+      // queued stores must have read shared memory, and loads in flight must land, before the CTA retires
+      asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+      for (uint32_t j = e.drained; j < e.issued; ++j) tc::mbar_wait(&full[j % kCopyStages], (j / kCopyStages) & 1u, 1u << 22);
     }
   }
-  if (!ok) atomicCAS(f.status, 0, 0x200 + f.rank);
-  copy_engine_quiesce(e);
+  copy_cta_meet(f, cta, 2 * epoch);
 }
 
 // Reduction side of the reduce-scatter fusion.  The chunk this rank owns is cut into `rs_phases`
-// row groups and every group into pieces; a piece is read from the world slots of the local staging
-// (this rank's own rows straight from its partial product) with bulk loads into shared memory, added
-// in fp32 in rank order and written as bf16.  Pieces are handed out through a device-wide counter to
-// whichever CTA is free: the pushers when they are done and the GEMM CTAs when they have run out of
-// tiles; a piece of a group waits until every rank has flagged that group.
+// row groups and every group into pieces; a piece is pulled from all partial products (bulk loads
+// into shared memory, `world` buffers per stage), added in fp32 in rank order and written as bf16.
+// Pieces are handed out through a device-wide counter: the dedicated CTAs [0, copy_ctas) take
+// pieces of a group as soon as every rank has flagged it, while the GEMM CTAs still work on the
+// next group, and the GEMM CTAs join in when they have run out of tiles.
 constexpr int kReduceStages = 3;
 constexpr uint32_t kReduceStageBytes = 64 * 1024;
 constexpr uint32_t kNoPiece = 0xffffffffu;
@@ -269,7 +233,7 @@ __device__ void reduce_scatter_role(const FusedDev& f, const GemmDev& g, uint32_
   }
   __syncthreads();
   const uint32_t piece = (kReduceStageBytes / static_cast<uint32_t>(f.world)) & ~127u;   // bytes per rank per stage
-  const unsigned long long chunk_bytes = f.chunk_bytes;
+  const unsigned long long chunk_bytes = static_cast<unsigned long long>(f.chunk_rows) * g.n * 2ull;
   const unsigned long long phase_bytes = chunk_bytes / f.rs_phases;
   const uint32_t pieces_per_phase = static_cast<uint32_t>((phase_bytes + piece - 1) / piece);
   const uint32_t total = pieces_per_phase * static_cast<uint32_t>(f.rs_phases);
@@ -312,11 +276,9 @@ __device__ void reduce_scatter_role(const FusedDev& f, const GemmDev& g, uint32_
     piece_range(p, off, n);
     sh->piece[s] = p;
     tc::mbar_expect_tx(&sh->full[s], n * static_cast<uint32_t>(f.world));
-    for (int r = 0; r < f.world; ++r) {
-      const char* src = r == f.rank ? static_cast<const char*>(f.rs_partial) + my_base + off
-                                    : static_cast<const char*>(f.rs_stage[epoch & 1u][f.rank]) + static_cast<size_t>(r) * chunk_bytes + off;
-      bulk_load(smem + static_cast<size_t>(s) * kReduceStageBytes + static_cast<size_t>(r) * piece, src, n, &sh->full[s]);
-    }
+    for (int r = 0; r < f.world; ++r)
+      bulk_load(smem + static_cast<size_t>(s) * kReduceStageBytes + static_cast<size_t>(r) * piece,
+                static_cast<const char*>(f.rs_partial[epoch & 1u][r]) + my_base + off, n, &sh->full[s]);
     return true;
   };
   uint32_t consumed_loaded = 0;   // thread 0: loaded pieces consumed so far
@@ -388,20 +350,16 @@ __device__ void reduce_scatter_role(const FusedDev& f, const GemmDev& g, uint32_
   (void)consumed_loaded;
 }
 
-// ++*epoch; *zeroed = 0 when given (the reduce-scatter fusion's piece counter).
-__global__ void bump_epoch_kernel(BumpArgs b) {
-  *b.epoch = *b.epoch + 1;
-  if (b.zeroed) *b.zeroed = 0;
+// ++*epoch and, when given, *zeroed = 0 (the reduce-scatter fusion's piece counter).
+__global__ void bump_epoch_kernel(uint32_t* epoch, uint32_t* zeroed) {
+  *epoch = *epoch + 1;
+  if (zeroed) *zeroed = 0;
 }
 
 template <int BN, int STAGES, bool kAMn, bool kBMn>
 __global__ void __launch_bounds__(192, 1) gemm_persistent_kernel(const __grid_constant__ CUtensorMap tma_a,
-                                                                 const __grid_constant__ CUtensorMap tma_b,
-                                                                 const __grid_constant__ CUtensorMap tma_s0,
-                                                                 const __grid_constant__ CUtensorMap tma_s1, GemmDev g,
+                                                                 const __grid_constant__ CUtensorMap tma_b, GemmDev g,
                                                                  FusedDev f) {
-  // tma_a: the A operand (all-gather fusion: this rank's own shard); tma_s0: all-gather fusion only, this
-  // rank's gathered slot [world * chunk_rows, K]; tma_s1: spare.
   using L = PLayout<BN, STAGES>;
   static_assert(L::kTiles >= kCopyStages * static_cast<int>(kCopyPiece), "copy CTAs stage through the tile ring");
   static_assert(L::kTiles >= kReduceStages * static_cast<int>(kReduceStageBytes), "reducer CTAs stage through the tile ring");
@@ -418,13 +376,8 @@ __global__ void __launch_bounds__(192, 1) gemm_persistent_kernel(const __grid_co
   const uint32_t epoch = f.mode != FUSE_NONE ? *f.epoch_ptr : 0u;
   if (f.mode != FUSE_NONE && static_cast<int>(blockIdx.x) < f.copy_ctas) {
     // these CTAs move data; the others compute
-    if (f.mode == FUSE_ALLGATHER_A) {
-      allgather_copy_role(f, epoch, smem);
-    } else {
-      if (threadIdx.x == 0) reduce_scatter_push_role(f, epoch, smem);
-      __syncthreads();
-      reduce_scatter_role(f, g, epoch, smem, reinterpret_cast<ReduceShared*>(smem + L::kTiles + L::kGemmBarriers));
-    }
+    if (f.mode == FUSE_ALLGATHER_A) allgather_copy_role(f, epoch, smem);
+    else reduce_scatter_role(f, g, epoch, smem, reinterpret_cast<ReduceShared*>(smem + L::kTiles + L::kGemmBarriers));
     return;
   }
   // in-CTA waits: two seconds alone, the cross-GPU limit plus two seconds when a role waits for peers
@@ -437,6 +390,8 @@ __global__ void __launch_bounds__(192, 1) gemm_persistent_kernel(const __grid_co
   const int splits = f.k_splits > 1 ? f.k_splits : 1;
   const int total_tiles = m_tiles * n_tiles * splits;
   const int num_kb = (g.k / BK) / splits;
+  // Row-chunk rotation: tile order starts at this rank's own chunk (fusions only).
+  const int m_rot = f.mode != FUSE_NONE ? (f.rank * (f.chunk_rows / BM)) % m_tiles : 0;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -451,7 +406,6 @@ __global__ void __launch_bounds__(192, 1) gemm_persistent_kernel(const __grid_co
     tc::mbar_init_fence();
     tc::tma_prefetch_desc(&tma_a);
     tc::tma_prefetch_desc(&tma_b);
-    if (f.mode == FUSE_ALLGATHER_A) tc::tma_prefetch_desc(&tma_s0);
   }
   if (warp == 1) tc::tmem_alloc(tmem_slot, 2 * BN);
   tc::fence_before_sync();
@@ -461,9 +415,7 @@ __global__ void __launch_bounds__(192, 1) gemm_persistent_kernel(const __grid_co
 
   // Reduce-scatter fusion: phase-major order; inside a phase the chunks of the other ranks come first
   // (rank + 1, rank + 2, ...) and this rank's own chunk last, so what peers wait for is ready earliest.
-  // All-gather fusion: chunk-major order, the own chunk first and the others as they arrive
-  // (rank - 1, rank - 2, ...).
-  const int chunk_mt = f.mode != FUSE_NONE ? f.chunk_rows / BM : 1;
+  const int chunk_mt = f.mode == FUSE_REDUCE_SCATTER_D ? f.chunk_rows / BM : 1;
   const int phase_mt = f.mode == FUSE_REDUCE_SCATTER_D ? chunk_mt / f.rs_phases : 1;
   const int per_chunk_phase = phase_mt * n_tiles, per_phase = per_chunk_phase * f.world;
   auto tile_coords = [&](int w, int& m_blk, int& n_blk, int& kb0) -> int {
@@ -475,17 +427,10 @@ __global__ void __launch_bounds__(192, 1) gemm_persistent_kernel(const __grid_co
       m_blk = c * chunk_mt + ph * phase_mt + rem2 / n_tiles;
       return ph;
     }
-    if (f.mode == FUSE_ALLGATHER_A) {
-      const int per_chunk = chunk_mt * n_tiles, k = w / per_chunk, rem = w % per_chunk;
-      kb0 = 0;
-      n_blk = rem % n_tiles;
-      m_blk = ((f.rank - k + f.world) % f.world) * chunk_mt + rem / n_tiles;
-      return 0;
-    }
     const int t = w / splits;
     kb0 = (w % splits) * num_kb;
     n_blk = t % n_tiles;
-    m_blk = t / n_tiles;
+    m_blk = (t / n_tiles + m_rot) % m_tiles;
     return 0;
   };
 
@@ -497,22 +442,12 @@ __global__ void __launch_bounds__(192, 1) gemm_persistent_kernel(const __grid_co
       for (int t = gcta; t < total_tiles && ok; t += gctas) {
         int m_blk, n_blk, kb0;
         tile_coords(t, m_blk, n_blk, kb0);
-        const CUtensorMap* map_a = &tma_a;
-        int a_row = m_blk * BM;
         if (f.mode == FUSE_ALLGATHER_A) {
-          const int chunk = a_row / f.chunk_rows;
-          if (chunk == f.rank) {
-            a_row -= chunk * f.chunk_rows;   // the own shard is read in place
-          } else {
-            if (!sig_wait_abortable(f.sig[f.rank] + kFuseSigAg + chunk, epoch, abort_flag, wait_ns)) {
-              atomicCAS(f.status, 0, 0x100 + chunk);
-              ok = false;
-              break;
-            }
-            // the chunk was written by a peer's bulk stores; TMA reads it through the async proxy
-            asm volatile("fence.proxy.async;" ::: "memory");
-            map_a = &tma_s0;
-          }
+          const int chunk = (m_blk * BM) / f.chunk_rows;
+          ok = wait_flag_geq(f.chunk_flags + chunk, epoch, abort_flag, wait_ns);
+          if (!ok) break;
+          // the chunk was written with ordinary stores by other CTAs; TMA reads it through the async proxy
+          asm volatile("fence.proxy.async;" ::: "memory");
         }
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % STAGES;
@@ -525,7 +460,7 @@ __global__ void __launch_bounds__(192, 1) gemm_persistent_kernel(const __grid_co
             for (int gq = 0; gq < BM / 64; ++gq)
               tc::tma_load_2d(a_dst + gq * (BK * 128), &tma_a, &full[s], m_blk * BM + gq * 64, (kb0 + kb) * BK);
           } else {
-            tc::tma_load_2d(a_dst, map_a, &full[s], (kb0 + kb) * BK, a_row);
+            tc::tma_load_2d(a_dst, &tma_a, &full[s], (kb0 + kb) * BK, m_blk * BM);
           }
           if (kBMn) {
 #pragma unroll
@@ -596,7 +531,7 @@ __global__ void __launch_bounds__(192, 1) gemm_persistent_kernel(const __grid_co
       tc::fence_after_sync();
       const int row = m_blk * BM + quarter * 32 + lane;
       GemmDev gt = g;
-      if (f.mode == FUSE_REDUCE_SCATTER_D) gt.d = f.rs_partial;   // my partial product; the pushers send it on
+      if (f.mode == FUSE_REDUCE_SCATTER_D) gt.d = f.rs_partial[epoch & 1u][f.rank];   // my partial product; the owners pull from it
       const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(buf * BN) + (static_cast<uint32_t>(quarter * 32) << 16);
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
@@ -620,7 +555,7 @@ __global__ void __launch_bounds__(192, 1) gemm_persistent_kernel(const __grid_co
           if (atomicAdd(f.phase_counters + phase, 1u) + 1u == target) {
             atomicExch(f.phase_counters + phase, 0u);
             __threadfence_system();
-            sig_store(f.sig[f.rank] + kFuseSigRs + 4 * f.rank + phase, epoch);   // pushers and reducers of this GPU wait for it
+            for (int p = 0; p < f.world; ++p) sig_store(f.sig[p] + kFuseSigRs + 4 * f.rank + phase, epoch);
           }
         }
       }
@@ -685,20 +620,10 @@ cudaError_t launch_persistent_cfg(const GemmArgs& a, const FusedDev& f_in, int m
     if (rc != cudaSuccess) return rc;
     configured = true;
   }
-  CUtensorMap ma, mb, ms0, ms1;
-  const bool ag = f.mode == FUSE_ALLGATHER_A;
-  if (ag && kAMn) return cudaErrorNotSupported;
-  // all-gather fusion: a.a is this rank's shard (chunk_rows rows); the other chunks are read from the staging
-  const bool oka = kAMn ? encode_map(&ma, a.a, a.k, a.m, a.lda, BK) : encode_map(&ma, a.a, ag ? f.chunk_rows : a.m, a.k, a.lda, BM);
+  CUtensorMap ma, mb;
+  const bool oka = kAMn ? encode_map(&ma, a.a, a.k, a.m, a.lda, BK) : encode_map(&ma, a.a, a.m, a.k, a.lda, BM);
   const bool okb = kBMn ? encode_map(&mb, a.b, a.k, a.n, a.ldb, BK) : encode_map(&mb, a.b, a.n, a.k, a.ldb, BN);
   if (!oka || !okb) return cudaErrorNotSupported;
-  if (ag) {
-    if (!encode_map(&ms0, static_cast<const __nv_bfloat16*>(f.a_stage[f.rank]), a.m, a.k, a.k, BM)) return cudaErrorNotSupported;
-    ms1 = ms0;
-  } else {
-    ms0 = ma;
-    ms1 = ma;
-  }
   (void)cudaGetLastError();
   GemmDev g;
   g.d = a.d;
@@ -741,15 +666,15 @@ no_split:
   int gemm_ctas = ctas - f.copy_ctas;
   if (gemm_ctas < 1) return cudaErrorInvalidValue;
   if (tiles < gemm_ctas) gemm_ctas = tiles;
-  gemm_persistent_kernel<BN, STAGES, kAMn, kBMn><<<gemm_ctas + f.copy_ctas, 192, L::kTotal, stream>>>(ma, mb, ms0, ms1, g, f);
+  gemm_persistent_kernel<BN, STAGES, kAMn, kBMn><<<gemm_ctas + f.copy_ctas, 192, L::kTotal, stream>>>(ma, mb, g, f);
   count_launch();
   return cudaGetLastError();
 }
 
 }  // namespace
 
-cudaError_t launch_bump_epoch(const BumpArgs& b, cudaStream_t stream) {
-  bump_epoch_kernel<<<1, 1, 0, stream>>>(b);
+cudaError_t launch_bump_epoch(uint32_t* epoch, uint32_t* zeroed, cudaStream_t stream) {
+  bump_epoch_kernel<<<1, 1, 0, stream>>>(epoch, zeroed);
   return cudaGetLastError();
 }
 

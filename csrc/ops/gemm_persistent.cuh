@@ -18,14 +18,12 @@ enum FuseMode : int {
 };
 
 constexpr int kFuseMaxRanks = 8;
-constexpr int kFuseCopyCtas = 16;     // all-gather fusion: CTAs that move data (default; at most kFuseMaxCopyCtas)
-constexpr int kFuseMaxCopyCtas = 96;
+constexpr int kFuseCopyCtas = 16;     // all-gather fusion: CTAs that move data (fixed: counters depend on it)
 constexpr int kFuseReduceCtas = 16;   // reduce-scatter fusion: CTAs that only pull and add partial rows (default)
 constexpr int kFuseMaxPhases = 4;     // reduce-scatter fusion: row groups of a chunk that complete one after another
 
-// Everything the fused roles need.  Data crosses NVLink as posted writes: a rank pushes what it
-// produced into the consumer's symmetric staging (bulk stores from shared memory, never a multicast
-// load), then raises a flag there.  Pointers into other GPUs' memory are peer mappings.
+// Everything the fused roles need.  Pointers into other GPUs' memory are peer
+// mappings read with plain or bulk (never multicast) loads over NVLink.
 struct FusedDev {
   int mode = FUSE_NONE;
   int world = 1;
@@ -37,45 +35,32 @@ struct FusedDev {
   unsigned long long timeout_ns = 0;          // bound of every cross-GPU wait
   int* status = nullptr;                      // written (non-zero) when such a wait runs out
   uint32_t* sig[kFuseMaxRanks] = {};          // every rank's signal words for these fusions (peer-mapped)
-  unsigned long long chunk_bytes = 0;         // bytes of one rank's chunk (A shard, or D rows of one owner)
-  // all-gather → GEMM.  Rank r pushes its shard into chunk r of every peer's gathered buffer (a slot of the
-  // symmetric ring), one peer after the other ((r+1), (r+2), ...), so every rank receives one chunk per
-  // step; the tiles read the own shard in place and the other chunks from the slot, in arrival order.
-  const void* a_own = nullptr;                // this rank's [chunk_rows, K] shard (local)
-  void* a_stage[kFuseMaxRanks] = {};          // [p]: rank p's slot for this call, [world * chunk_rows, K]
-  uint32_t* step_counters = nullptr;          // local [world]: copy CTAs done with push step k (self-resetting)
-  // GEMM → reduce-scatter.  Every rank writes its partial product [world * chunk_rows, N] (bf16, dense) to
-  // local memory, row group by row group; pusher CTAs send the rows other ranks own into slot `rank` of the
-  // owner's staging; the owner adds the world slots (its own rows straight from its partial product).
-  void* rs_partial = nullptr;                 // local partial product
-  void* rs_stage[2][kFuseMaxRanks] = {};      // [epoch parity][p]: rank p's staging, world slots of chunk_rows x N
+  // all-gather → GEMM
+  const void* a_peer[kFuseMaxRanks] = {};     // rank r's shard of A
+  void* a_gathered = nullptr;                 // local [world * chunk_rows, K] buffer the tiles are loaded from
+  unsigned long long chunk_bytes = 0;
+  uint32_t* chunk_flags = nullptr;            // local [world]: chunk c has landed when chunk_flags[c] >= epoch
+  uint32_t* chunk_counters = nullptr;         // local [world]: copy CTAs that finished chunk c (cumulative)
+  // GEMM → reduce-scatter.  Every rank writes its partial product [world * chunk_rows, N] (bf16, dense)
+  // into its own buffer; rank o then reads rows [o * chunk_rows, (o + 1) * chunk_rows) of every buffer.
+  void* rs_partial[2][kFuseMaxRanks] = {};    // [epoch parity][r]: rank r's partial product (mine is written, all are read)
   void* rs_out = nullptr;                     // [chunk_rows, N] bf16 result of the reduction
   int rs_phases = 1;                          // row groups per chunk (1, 2 or 4)
   uint32_t* phase_counters = nullptr;         // local [kFuseMaxPhases]: epilogue warps done with a phase (self-resetting)
-  uint32_t* push_counters = nullptr;          // local [world * kFuseMaxPhases]: pushers done with (owner, phase) (self-resetting)
   uint32_t* work_counter = nullptr;           // local: next piece of the reduction (zeroed before the launch)
 };
 
 // Signal-word layout (uint32 per entry) inside sig[r]:
-//   [4*s + ph]  reduce-scatter: rank s's rows of phase ph for rank r are in r's staging (s == r: r's own
-//               partial product has reached phase ph)
-//   [32 + s]    all-gather: rank s's shard is in r's staging
+//   [4*s, 4*s + 4)           reduce-scatter: rank s has written phase 0..3 of its partial product
+//   [32 + 8*c, 32 + 8*c + 8) all-gather meeting flags of copy CTA c, indexed by source rank
 constexpr int kFuseSigRs = 0;
 constexpr int kFuseSigAg = 4 * kFuseMaxRanks;
-constexpr int kFuseSigWords = 64;
-// Local counter words of one TpGemm object.
-constexpr int kFuseWordAgEpoch = 0, kFuseWordRsEpoch = 1, kFuseWordStep = 8, kFuseWordPhase = 24, kFuseWordWork = 28,
-              kFuseWordPush = 32, kFuseWords = 64;
-
-struct BumpArgs {
-  uint32_t* epoch = nullptr;                   // device word to increment
-  uint32_t* zeroed = nullptr;                  // device word to clear (may be null)
-};
+constexpr int kFuseSigWords = kFuseSigAg + 8 * kFuseCopyCtas;
 
 // max_ctas <= 0: one CTA per SM.
 cudaError_t launch_gemm_persistent(const GemmArgs& a, const FusedDev& f, int max_ctas, cudaStream_t stream);
-// One thread: ++*epoch, clear, announce; enqueue before a fused launch.
-cudaError_t launch_bump_epoch(const BumpArgs& b, cudaStream_t stream);
+// ++*epoch and *zeroed = 0 (zeroed may be null), one thread; enqueue before a fused launch.
+cudaError_t launch_bump_epoch(uint32_t* epoch, uint32_t* zeroed, cudaStream_t stream);
 
 }  // namespace ops
 }  // namespace mccl

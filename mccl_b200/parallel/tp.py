@@ -31,9 +31,7 @@ class TensorParallelContext:
     """Per-group state of the fused tensor-parallel kernels."""
 
     def __init__(self, group=None, device: Optional[torch.device] = None, max_rows_local: int = 2048, max_features: int = 8192,
-                 fused: bool = True, ag_slots: int = 8):
-        """ag_slots: ring of gathered-activation buffers kept in symmetric memory; it has to span the fused
-        all-gather calls between a layer's forward and its backward (2 per layer each way, plus slack)."""
+                 fused: bool = True):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -42,14 +40,26 @@ class TensorParallelContext:
         self.native = self.fused   # fused arm: this package's kernels everywhere; otherwise stock PyTorch operators
         self.tp = None
         self.comm = None
+        self._act = None
         if self.fused:
             import mccl_b200
             be = mccl_b200.get_backend(group)
             if be is None:
                 raise RuntimeError("fused tensor parallelism needs a process group created with backend='mccl'")
             self.comm = be.device_comm(device.index)
-            # symmetric staging the peers push activation shards and partial products into
-            self.tp = _C.TpGemm(self.comm, max_rows_local * max_features, ag_slots)
+            self.tp = _C.TpGemm(self.comm, max_rows_local * max_features)
+            # symmetric staging for the shard a fused all-gather reads from the peers
+            self._act_bytes = max_rows_local * max_features * 2
+            self._act = self.comm.symm_alloc(self._act_bytes)
+
+    def stage(self, x: torch.Tensor):
+        """Copies a [rows, features] bf16 shard into the symmetric staging buffer (peers read it from there)."""
+        n = x.numel() * 2
+        if n > self._act_bytes:
+            raise ValueError(f"shard of {n} bytes exceeds the symmetric staging buffer ({self._act_bytes})")
+        view = self._act.tensor(self.rank, 0, list(x.shape), torch.bfloat16, self.device.index)
+        view.copy_(x)
+        return self._act
 
     def check(self) -> None:
         if self.tp is not None:
@@ -89,7 +99,8 @@ class _ColumnParallelFn(torch.autograd.Function):
         w16 = _w16(weight)
         rows_local = x.shape[0]
         if ctxp.fused and rows_local % 128 == 0 and x.shape[1] % 64 == 0 and w16.shape[0] % 8 == 0:
-            y, gathered, _, ctx.generation = ctxp.tp.ag_gemm(x.contiguous(), w16, False)
+            sym = ctxp.stage(x)
+            y, gathered, _ = ctxp.tp.ag_gemm(sym, 0, rows_local, w16, False)
             ctx.fused_path = True
         else:
             gathered = _all_gather_rows(x, ctxp) if ctxp.world > 1 else x
@@ -104,9 +115,6 @@ class _ColumnParallelFn(torch.autograd.Function):
         gathered, w16 = ctx.saved_tensors
         ctxp = ctx.ctxp
         dy = dy.contiguous()
-        if ctx.fused_path and not ctxp.tp.ag_valid(ctx.generation):
-            raise RuntimeError(f"the gathered activation of this layer was overwritten: the ring of {ctxp.tp.ag_slots} buffers is "
-                               "shorter than the distance between forward and backward; build the context with more ag_slots")
         # dx_shard = reduce_scatter(dy @ W): W is stored [contraction = N_local, K]
         if ctx.fused_path and dy.shape[1] % 64 == 0 and w16.shape[1] % 8 == 0:
             dx = ctxp.tp.gemm_rs(dy, w16, True)
@@ -141,7 +149,8 @@ class _RowParallelFn(torch.autograd.Function):
         rows_local = dy.shape[0]
         # dx = all_gather(dy) @ W: W is stored [contraction = N, K_local]
         if ctx.fused_path and dy.shape[1] % 64 == 0 and w16.shape[1] % 8 == 0:
-            dx, dy_full, _, _ = ctxp.tp.ag_gemm(dy, w16, True)
+            sym = ctxp.stage(dy)
+            dx, dy_full, _ = ctxp.tp.ag_gemm(sym, 0, rows_local, w16, True)
         else:
             dy_full = _all_gather_rows(dy, ctxp) if ctxp.world > 1 else dy
             dx = dy_full @ w16

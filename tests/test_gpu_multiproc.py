@@ -246,6 +246,8 @@ def _tp_gemms(rank, world):
     comm = mccl_b200.get_backend().device_comm(dev.index)
     rows, K, N = 256, 512, 384
     tp = _C.TpGemm(comm, rows * max(N, K))
+    sym = comm.symm_alloc(rows * K * 2)
+    mine = sym.tensor(rank, 0, [rows, K], torch.bfloat16, dev.index)
     worst = 0.0
     for it in range(3):   # several epochs: both staging parities and flag reuse
         g = torch.Generator(device="cpu").manual_seed(100 * it + rank)
@@ -253,14 +255,14 @@ def _tp_gemms(rank, world):
         gw = torch.Generator(device="cpu").manual_seed(1000 + it)
         w = (torch.randn(N, K, generator=gw) * 0.05).to(dev).bfloat16()
         # all-gather -> GEMM, both weight layouts
+        mine.copy_(x)
         full = torch.empty(world * rows, K, dtype=torch.bfloat16, device=dev)
         dist.all_gather_into_tensor(full, x)
         gold = full.float() @ w.float().t()
-        y, gathered, _, gen = tp.ag_gemm(x, w, False)
-        assert tp.ag_valid(gen)
+        y, gathered, _ = tp.ag_gemm(sym, 0, rows, w, False)
         assert torch.equal(gathered, full)
         worst = max(worst, ((y.float() - gold).abs().max() / gold.abs().max()).item())
-        y2, _, _, _ = tp.ag_gemm(x, w.t().contiguous(), True)
+        y2, _, _ = tp.ag_gemm(sym, 0, rows, w.t().contiguous(), True)
         worst = max(worst, ((y2.float() - gold).abs().max() / gold.abs().max()).item())
         # GEMM -> reduce-scatter
         xr = torch.randn(world * rows, K, generator=g).to(dev).bfloat16()
@@ -290,8 +292,7 @@ def _tp_model(rank, world):
     grads = {}
     for fused in (True, False):
         torch.manual_seed(7)   # same replicated weights; shards differ by rank below
-        ctx = TensorParallelContext(device=dev, max_rows_local=B * S // world, max_features=max(3 * D, FF), fused=fused,
-                                    ag_slots=4 * L + 4)
+        ctx = TensorParallelContext(device=dev, max_rows_local=B * S // world, max_features=max(3 * D, FF), fused=fused)
         torch.manual_seed(7 + rank)
         model = TPDecoder(ctx, vocab=V, d_model=D, n_layers=L, n_heads=H, d_ff=FF, batch=B, seq=S).to(dev)
         for p in model.replicated_parameters():   # replicated parameters must agree
