@@ -17,6 +17,8 @@
 // index arithmetic and the flag protocol can be tested on one device.
 #include "collectives.hpp"
 
+#include <cstdlib>
+
 #include <cstdio>
 #include <type_traits>
 
@@ -790,6 +792,14 @@ namespace {
 
 template <typename... KArgs, typename... Args>
 cudaError_t launch(void (*kernel)(KArgs...), const LaunchCfg& cfg, int threads, Args... args) {
+  // MCCL_COMM_THREADS (128..512): threads per CTA.  With 256 a collective CTA needs half a register file,
+  // so it can share an SM with a persistent GEMM CTA instead of waiting for one to retire.
+  static const int env_threads = [] {
+    const char* v = std::getenv("MCCL_COMM_THREADS");
+    const int t = v && *v ? std::atoi(v) : 0;
+    return t >= 128 && t <= kThreads ? (t / 32) * 32 : 0;
+  }();
+  if (env_threads > 0 && threads == kThreads) threads = env_threads;
   dim3 grid(cfg.ctas, cfg.nlocal > 1 ? cfg.nlocal : 1);
   if (cfg.nlocal > 1) {
     void* params[] = {static_cast<void*>(&args)...};

@@ -2,6 +2,8 @@
 fallbacks below only serve CPU tensors (tests without a GPU)."""
 from __future__ import annotations
 
+import os
+
 import torch
 import torch.nn.functional as F
 
@@ -44,7 +46,8 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias=None, act: str = "none", 
 def embedding(ids: torch.Tensor, tok: torch.Tensor, pos=None) -> torch.Tensor:
     """bf16(tok[ids] + pos[:seq]) for ids [..., seq]; tok / pos are fp32 tables."""
     seq = ids.shape[-1]
-    if ids.is_cuda and _HAS.get("embed_fwd") and tok.dtype == torch.float32 and tok.shape[1] % 8 == 0:
+    if (ids.is_cuda and _HAS.get("embed_fwd") and tok.dtype == torch.float32 and tok.shape[1] % 8 == 0
+            and os.environ.get("MCCL_NATIVE_EMBED", "1") != "0"):
         from .native import EmbeddingFn
         return EmbeddingFn.apply(ids, tok, pos, seq)
     x = F.embedding(ids, tok)

@@ -95,10 +95,14 @@ class DDPTrainer:
         self.buckets[-1].numel = total - self.buckets[-1].start
         self.total = total
         self.flat_p = torch.zeros(total, device=self.device, dtype=torch.float32)
-        if self.comm is not None:
+        if self.comm is not None and self.wire != "bf16":
+            # the in-place symmetric allreduce reads the peers' gradient buffers directly
             self.symm = self.comm.symm_alloc(total * 4)
             self.flat_g = self.symm.tensor(self.rank, 0, [total], torch.float32, self.device.index)
         else:
+            # the staged (bf16-wire) allreduce copies through the arena, so the gradients stay in ordinary
+            # device memory: every weight-gradient GEMM and the optimizer touch this buffer, and plain
+            # memory is faster for them than a peer-mapped, multicast-bound allocation
             self.symm = None
             self.flat_g = torch.zeros(total, device=self.device, dtype=torch.float32)
         self.flat_g.zero_()
