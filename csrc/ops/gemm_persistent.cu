@@ -18,6 +18,7 @@
 #include "gemm_common.cuh"
 #include "gemm_persistent.cuh"
 
+#include <atomic>
 #include <cstdlib>
 
 namespace mccl {
@@ -32,7 +33,9 @@ struct PLayout {
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kTiles = STAGES * kStageBytes;
   static constexpr int kGemmBarriers = (2 * STAGES + 4) * 8 + 16;
-  static constexpr int kBarriers = kGemmBarriers + 64;   // + the reduce-scatter reducers' barriers and ring
+  static constexpr int kReduceBarriers = 64;             // the reduce-scatter reducers' barriers and ring
+  static constexpr int kSchedBytes = 4 * 8 * 2 + 4 * 4;  // tile scheduler: full / empty barriers and tile ring
+  static constexpr int kBarriers = kGemmBarriers + kReduceBarriers + kSchedBytes;
   static constexpr int kTotal = kTiles + kBarriers + 1024;
 };
 
@@ -372,6 +375,12 @@ __global__ void __launch_bounds__(192, 1) gemm_persistent_kernel(const __grid_co
   uint64_t* acc_empty = acc_full + 2;    // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  // Tile scheduler (plain GEMMs): the producer draws the next tile from a device-wide counter and
+  // publishes it to the MMA and epilogue warps through a ring of four entries, so a CTA that starts
+  // late or shares its SM with a collective kernel simply takes fewer tiles.
+  uint64_t* sched_full = reinterpret_cast<uint64_t*>(smem + L::kTiles + L::kGemmBarriers + L::kReduceBarriers);
+  uint64_t* sched_empty = sched_full + 4;
+  volatile int* sched_tile = reinterpret_cast<volatile int*>(sched_empty + 4);
 
   const uint32_t epoch = f.mode != FUSE_NONE ? *f.epoch_ptr : 0u;
   if (f.mode != FUSE_NONE && static_cast<int>(blockIdx.x) < f.copy_ctas) {
@@ -401,6 +410,10 @@ __global__ void __launch_bounds__(192, 1) gemm_persistent_kernel(const __grid_co
     for (int b = 0; b < 2; ++b) {
       tc::mbar_init(&acc_full[b], 1);
       tc::mbar_init(&acc_empty[b], 4);
+    }
+    for (int b = 0; b < 4; ++b) {
+      tc::mbar_init(&sched_full[b], 1);
+      tc::mbar_init(&sched_empty[b], 5);   // the MMA thread and the four epilogue warps
     }
     *abort_flag = 0;
     tc::mbar_init_fence();
@@ -439,7 +452,19 @@ __global__ void __launch_bounds__(192, 1) gemm_persistent_kernel(const __grid_co
     if (lane == 0) {
       bool ok = true;
       uint32_t it = 0;
-      for (int t = gcta; t < total_tiles && ok; t += gctas) {
+      for (int i = 0; ok; ++i) {
+        // draw and publish tile i of this CTA (-1: no more)
+        const int slot = i & 3;
+        if (i >= 4) {
+          ok = wait_or_abort(&sched_empty[slot], ((i >> 2) - 1) & 1, abort_flag, wait_ns);
+          if (!ok) break;
+        }
+        int t = (f.sched_counter == nullptr || i == 0) ? gcta + i * gctas
+                                                       : gctas + static_cast<int>(atomicAdd(f.sched_counter, 1u));
+        if (t >= total_tiles) t = -1;
+        sched_tile[slot] = t;
+        tc::mbar_arrive(&sched_full[slot]);
+        if (t < 0) break;
         int m_blk, n_blk, kb0;
         tile_coords(t, m_blk, n_blk, kb0);
         if (f.mode == FUSE_ALLGATHER_A) {
@@ -487,7 +512,13 @@ __global__ void __launch_bounds__(192, 1) gemm_persistent_kernel(const __grid_co
       bool ok = true;
       uint32_t it = 0;
       int i = 0;
-      for (int t = gcta; t < total_tiles && ok; t += gctas, ++i) {
+      for (;; ++i) {
+        const int slot = i & 3;
+        ok = wait_or_abort(&sched_full[slot], (i >> 2) & 1, abort_flag, wait_ns);
+        if (!ok) break;
+        const int t = sched_tile[slot];
+        tc::mbar_arrive(&sched_empty[slot]);
+        if (t < 0) break;
         const int buf = i & 1;
         if (i >= 2) {
           ok = wait_or_abort(&acc_empty[buf], ((i >> 1) - 1) & 1, abort_flag, wait_ns);
@@ -521,7 +552,15 @@ __global__ void __launch_bounds__(192, 1) gemm_persistent_kernel(const __grid_co
     const int quarter = warp & 3;
     bool ok = true;
     int i = 0;
-    for (int t = gcta; t < total_tiles; t += gctas, ++i) {
+    for (;; ++i) {
+      const int slot = i & 3;
+      ok = wait_or_abort(&sched_full[slot], (i >> 2) & 1, abort_flag, wait_ns);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      const int t = sched_tile[slot];
+      __syncwarp();
+      if (lane == 0) tc::mbar_arrive(&sched_empty[slot]);
+      if (t < 0) break;
       int m_blk, n_blk, kb0;
       const int phase = tile_coords(t, m_blk, n_blk, kb0);
       const int buf = i & 1;
@@ -571,9 +610,32 @@ __global__ void __launch_bounds__(192, 1) gemm_persistent_kernel(const __grid_co
     tc::fence_after_sync();
     tc::tmem_dealloc(tmem_base, 2 * BN);
   }
+  if (f.sched_counter != nullptr && threadIdx.x == 0) {
+    // the CTA that leaves last rewinds the counters for the next launch that uses this slot
+    __threadfence();
+    if (atomicAdd(f.sched_counter + 1, 1u) + 1u == gridDim.x) {
+      atomicExch(f.sched_counter, 0u);
+      atomicExch(f.sched_counter + 1, 0u);
+    }
+  }
   // out of tiles: help with the reduction (the tile ring is idle now)
   if (f.mode == FUSE_REDUCE_SCATTER_D && *abort_flag == 0)
     reduce_scatter_role(f, g, epoch, smem, reinterpret_cast<ReduceShared*>(smem + L::kTiles + L::kGemmBarriers));
+}
+
+// Counter pairs {next tile, CTAs that have left} of the tile scheduler, one array per device.
+constexpr unsigned int kSchedSlots = 1024;
+__device__ unsigned int g_sched_counters[2 * kSchedSlots];
+unsigned int* sched_counters() {
+  static unsigned int* ptr[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (!ptr[dev]) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_sched_counters) != cudaSuccess) return nullptr;
+    ptr[dev] = static_cast<unsigned int*>(p);
+  }
+  return ptr[dev];
 }
 
 int sm_count() {
@@ -660,6 +722,19 @@ cudaError_t launch_persistent_cfg(const GemmArgs& a, const FusedDev& f_in, int m
     }
   }
 no_split:
+  // Plain GEMMs draw tiles from a device-wide counter (one of a ring of slots per launch; the last CTA of a
+  // launch rewinds its slot, and launches that share a slot are far apart in stream order).
+  static const bool dynamic_tiles = [] {
+    const char* v = std::getenv("MCCL_GEMM_DYNAMIC");
+    return !(v && v[0] == '0');
+  }();
+  if (dynamic_tiles && f.mode == FUSE_NONE) {
+    unsigned int* base = sched_counters();
+    if (base) {
+      static std::atomic<unsigned int> next_slot{0};
+      f.sched_counter = base + 2 * (next_slot.fetch_add(1) % kSchedSlots);
+    }
+  }
   int ctas = sm_count();
   if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
   // fused roles wait on one another inside the kernel: every CTA must be resident (one per SM)
