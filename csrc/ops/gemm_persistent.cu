@@ -724,9 +724,11 @@ cudaError_t launch_persistent_cfg(const GemmArgs& a, const FusedDev& f_in, int m
 no_split:
   // Plain GEMMs draw tiles from a device-wide counter (one of a ring of slots per launch; the last CTA of a
   // launch rewinds its slot, and launches that share a slot are far apart in stream order).
+  // Off by default: on the data-parallel step it measured neutral on one GPU and 0.1-0.3 ms slower on two
+  // (the extra scheduler hand-shake per tile costs more than the balancing gains); MCCL_GEMM_DYNAMIC=1 enables it.
   static const bool dynamic_tiles = [] {
     const char* v = std::getenv("MCCL_GEMM_DYNAMIC");
-    return !(v && v[0] == '0');
+    return v && v[0] == '1';
   }();
   if (dynamic_tiles && f.mode == FUSE_NONE) {
     unsigned int* base = sched_counters();

@@ -68,7 +68,7 @@ struct DeviceComm::Impl {
   int* status_dev = nullptr;
   size_t half_bytes = 0;
   unsigned long long timeout_ns = 0;
-  int max_ctas = 32;
+  int max_ctas = 64;
   int64_t nvls_above = 0;  // AUTO uses staged NVLS at or above this many wire bytes (0 = never)
 
   dev::DevComm ctx(int world, int rank_base, int nlocal, int channel) const {
@@ -117,7 +117,7 @@ void DeviceComm::init_common() {
   MCCL_CUDA_CHECK(cudaHostGetDevicePointer(&impl_->status_dev, impl_->status_host, 0));
   MCCL_CUDA_CHECK(cudaDeviceSynchronize());
   impl_->timeout_ns = static_cast<unsigned long long>(std::max<int64_t>(cfg_.device_timeout_ms, 1)) * 1000000ull;
-  int cap = cfg_.max_ctas > 0 ? cfg_.max_ctas : 32;
+  int cap = cfg_.max_ctas > 0 ? cfg_.max_ctas : 64;   // 64 CTAs of 256 threads
   impl_->max_ctas = std::min(cap, dev::kMaxCtas);
   impl_->nvls_above = env::i64("MCCL_NVLS_ABOVE", 0);
   if (nlocal_ > 1) impl_->max_ctas = std::max(1, std::min(impl_->max_ctas, 96 / nlocal_));  // all virtual ranks co-resident
