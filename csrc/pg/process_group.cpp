@@ -282,7 +282,7 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupMCCL::allreduce(std::vector<at::Tenso
   // Per-call knobs, read on the caller thread like the reference does.
   Algo req = requested_algo();
   WireDtype wire = requested_wire();
-  int64_t below = tree_below_bytes();
+  int64_t below = tensors[0].device().is_cuda() ? device_oneshot_below_bytes() : tree_below_bytes();
   uint64_t bytes = 0;
   for (auto& t : tensors) bytes += nbytes(t);
 
@@ -369,7 +369,7 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupMCCL::reduce(std::vector<at::Tensor>&
     // copy so their tensor keeps its value.
     bool is_root = getRank() == root;
     Algo req = requested_algo();
-    int64_t below = tree_below_bytes();
+    int64_t below = device_oneshot_below_bytes();
     return submitStream(c10d::OpType::REDUCE, "mccl:reduce", nbytes(t), "", {t}, {t}, t.device(),
                         [t, op, is_root, req, below](DeviceComm& dev, void* stream) {
                           at::Tensor src = device_reducible(t.scalar_type()) ? t : t.to(at::kInt);

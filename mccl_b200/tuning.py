@@ -61,10 +61,9 @@ def crossover_from_sweep(rows: List[dict]) -> int:
         if "oneshot" not in t:
             continue
         others = [v for k, v in t.items() if k != "oneshot"]
-        if not others or t["oneshot"] <= min(others):
+        # a tie within 3 % is noise; the crossover is the largest size at which one-shot still holds up
+        if not others or t["oneshot"] <= 1.03 * min(others):
             best = size
-        else:
-            break
     return best
 
 
