@@ -20,6 +20,7 @@
 #include "../core/errors.hpp"
 #include "../dmem/dmem_kernels.hpp"
 #include "../dmem/dmem_manager.hpp"
+#include "../dmem/shm_domain.hpp"
 #include "../pg/device_comm.hpp"
 #include "../runtime/kernel_dispatch.hpp"
 #include "../symm/symm_mesh.hpp"
@@ -309,16 +310,37 @@ void bind_runtime(py::module_& m) {
       });
 
   // ------------------------------------------------------------------ dmem --
-  py::class_<LocalFabric, std::shared_ptr<LocalFabric>>(m, "LocalFabric").def(py::init<int>(), py::arg("num_nodes"));
+  py::class_<DmemFabric, std::shared_ptr<DmemFabric>>(m, "DmemFabric");
+  py::class_<LocalFabric, DmemFabric, std::shared_ptr<LocalFabric>>(m, "LocalFabric").def(py::init<int>(), py::arg("num_nodes"));
+  py::class_<ShmFabric, DmemFabric, std::shared_ptr<ShmFabric>>(m, "ShmFabric")
+      .def(py::init<const std::string&, int, int, int>(), py::arg("name"), py::arg("node"), py::arg("num_nodes"),
+           py::arg("timeout_ms") = 10000, py::call_guard<py::gil_scoped_release>(),
+           "Fabric of one process of a job on this box: region directory, immediates and coherence mailboxes in POSIX "
+           "shared memory (node 0 creates them), host regions in shared heaps.")
+      .def("alloc_heap",
+           [](ShmFabric& f, uint64_t bytes) {
+             auto r = f.alloc_heap(bytes);
+             return py::make_tuple(r.first, reinterpret_cast<uintptr_t>(r.second));
+           },
+           py::arg("nbytes"), "Returns (heap id, address) of a zeroed heap every process of the job can map.")
+      .def("collect_imm", [](ShmFabric& f) {
+        py::list out;
+        for (auto& r : f.collect_imm()) out.append(py::make_tuple(r.src_node, r.region_id, r.offset, r.length, r.imm));
+        return out;
+      });
+  m.attr("REGION_HOST_HEAP") = static_cast<uint32_t>(REGION_HOST_HEAP);
   py::class_<DistributedMemoryManager>(m, "DmemManager")
-      .def(py::init([](int node, std::shared_ptr<LocalFabric> f) { return new DistributedMemoryManager(static_cast<uint16_t>(node), f); }),
+      .def(py::init([](int node, std::shared_ptr<DmemFabric> f) { return new DistributedMemoryManager(static_cast<uint16_t>(node), f); }),
            py::arg("node_id"), py::arg("fabric"), py::keep_alive<1, 3>())
       .def_property_readonly("node_id", &DistributedMemoryManager::node_id)
       .def("register_region",
-           [](DistributedMemoryManager& d, uintptr_t ptr, uint64_t n, uint32_t flags) {
-             return d.register_region(reinterpret_cast<void*>(ptr), n, flags);
+           [](DistributedMemoryManager& d, uintptr_t ptr, uint64_t n, uint32_t flags, uint32_t heap_id, uint64_t heap_offset) {
+             if (heap_id != 0 && !(flags & REGION_DEVICE)) flags |= REGION_HOST_HEAP;
+             return d.register_region(reinterpret_cast<void*>(ptr), n, flags, heap_id, heap_offset);
            },
-           py::arg("ptr"), py::arg("nbytes"), py::arg("flags") = static_cast<uint32_t>(REGION_READABLE | REGION_WRITABLE | REGION_SHARED))
+           py::arg("ptr"), py::arg("nbytes"), py::arg("flags") = static_cast<uint32_t>(REGION_READABLE | REGION_WRITABLE | REGION_SHARED),
+           py::arg("heap_id") = 0, py::arg("heap_offset") = 0,
+           "heap_id / heap_offset: the shared heap (ShmFabric.alloc_heap) the memory was carved from and its offset inside it.")
       .def("unregister_region", &DistributedMemoryManager::unregister_region)
       .def("put",
            [](DistributedMemoryManager& d, int node, uint32_t region, uint64_t off, uintptr_t src, uint64_t len) {
@@ -402,14 +424,17 @@ void bind_runtime(py::module_& m) {
   });
 
   // ------------------------------------------------------------- coherence --
-  py::class_<LocalBus, std::shared_ptr<LocalBus>>(m, "LocalBus")
+  py::class_<CoherenceBus, std::shared_ptr<CoherenceBus>>(m, "CoherenceBus");
+  py::class_<ShmBus, CoherenceBus, std::shared_ptr<ShmBus>>(m, "ShmBus")
+      .def(py::init<std::shared_ptr<ShmFabric>>(), py::arg("fabric"), "Coherence mailboxes of the job in shared memory.");
+  py::class_<LocalBus, CoherenceBus, std::shared_ptr<LocalBus>>(m, "LocalBus")
       .def(py::init<int>(), py::arg("num_nodes"))
       .def("drop_op", [](LocalBus& b, int op, int dst) {
         b.set_drop([op, dst](int d, const CoherenceMessage& msg) { return (op < 0 || msg.op == op) && (dst < 0 || d == dst); });
       }, py::arg("op"), py::arg("dst") = -1, "Test hook: drop messages with this opcode (-1 = any) sent to dst (-1 = anyone).")
       .def("drop_nothing", [](LocalBus& b) { b.set_drop(nullptr); });
   py::class_<CoherenceProtocol>(m, "CoherenceProtocol")
-      .def(py::init([](int node, std::shared_ptr<LocalBus> bus, DistributedMemoryManager* d, int timeout_ms) {
+      .def(py::init([](int node, std::shared_ptr<CoherenceBus> bus, DistributedMemoryManager* d, int timeout_ms) {
              return new CoherenceProtocol(node, bus, d, timeout_ms);
            }),
            py::arg("node"), py::arg("bus"), py::arg("dmem"), py::arg("timeout_ms") = 5000, py::keep_alive<1, 3>(), py::keep_alive<1, 4>())

@@ -46,7 +46,7 @@ uint32_t DistributedMemoryManager::register_region(void* ptr, uint64_t nbytes, u
     r.length = nbytes;
     r.heap_id = heap_id;
     r.generation = ++generations_[id];
-    r.flags = flags | (heap_id ? REGION_DEVICE : 0u);
+    r.flags = flags | ((heap_id && !(flags & REGION_HOST_HEAP)) ? REGION_DEVICE : 0u);
     regions_[id] = r;
     ++stats_.regions;
     e.local_addr = heap_id ? remote_base : reinterpret_cast<uint64_t>(ptr);

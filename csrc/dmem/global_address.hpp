@@ -55,6 +55,7 @@ enum RegionFlags : uint32_t {
   REGION_SHARED = 1u << 2,
   REGION_PRIVATE = 1u << 3,
   REGION_DEVICE = 1u << 4,   // lives in GPU memory (symmetric heap); otherwise host memory
+  REGION_HOST_HEAP = 1u << 5,  // carved from a shared-memory host heap (a heap id that does not mean GPU memory)
 };
 
 struct MemoryRegion {
