@@ -67,6 +67,7 @@ def _node(rank, world, name, barrier, queue):
             co.barrier_all()
             co.fence()
             stats = co.stats()
+            barrier.wait()      # nobody stops serving while a peer still waits for fence acknowledgements
         finally:
             co.shutdown()
         barrier.wait()
