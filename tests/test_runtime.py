@@ -1,7 +1,7 @@
 """Distributed runtime on the host: scheduler, node agent, cluster manager with
 heartbeat failure detection, distributed memory, coherence protocol, kernel
-dispatch.  None of this is tested in the reference (its SURVEY of tests lists
-dmem, coherence, scheduler, cluster manager and agent as untested); the cases
+dispatch.  The reference has no tests for dmem, coherence, scheduler, cluster
+manager or agent (its tests/ directory covers the process group only); the cases
 follow the behaviour its sources describe.  Failures are made on the host: an
 agent that stops answering, a dropped protocol message.
 """
