@@ -316,3 +316,37 @@ def _tp_model(rank, world):
 
 def test_tensor_parallel_decoder_fused_matches_collectives():
     spawn(_tp_model, _world(), timeout=300, _cuda=True)
+
+
+def _gpu_soak(rank, world):
+    dev = torch.device("cuda", torch.cuda.current_device())
+    expect_sum = world * (world + 1) / 2
+    t = torch.empty(1024, device=dev)
+    for i in range(2000):           # small messages back to back: epochs and arena halves keep alternating
+        t.fill_(float(rank + 1))
+        dist.all_reduce(t)
+    assert t[0].item() == expect_sum and t[-1].item() == expect_sum
+    for n in (1, 3, 1023, 4097, 65536, 262145, 1 << 20, 3 << 20, (16 << 20) + 5):    # odd sizes, every schedule of `auto`
+        x = torch.full((n,), float(rank + 1), device=dev)
+        dist.all_reduce(x)
+        assert x[0].item() == expect_sum and x[-1].item() == expect_sum, n
+    for i in range(200):            # interleaved collectives keep their order
+        a = torch.full((4096,), float(i + rank), device=dev)
+        dist.all_reduce(a)
+        b = torch.full((4096,), float(i), device=dev) if rank == i % world else torch.zeros(4096, device=dev)
+        dist.broadcast(b, i % world)
+        if i % 25 == 0:
+            dist.barrier()
+        assert b[0].item() == i and a[0].item() == world * i + world * (world - 1) / 2
+    big = torch.ones(32 << 20, device=dev)
+    for _ in range(5):
+        dist.all_reduce(big, op=dist.ReduceOp.AVG)
+    assert big[12345].item() == 1.0
+    torch.cuda.synchronize()
+    import mccl_b200
+    mccl_b200.get_backend().device_comm(dev.index).check_status()
+    return True
+
+
+def test_soak_on_gpus():
+    assert all(spawn(_gpu_soak, _world(), timeout=300, _cuda=True))
