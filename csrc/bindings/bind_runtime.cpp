@@ -105,8 +105,9 @@ py::dict dmem_stats_dict(const DmemStats& s) {
 
 // Process-wide manager behind the module-level dmem functions.
 struct GlobalDmem {
-  std::shared_ptr<LocalFabric> fabric;
-  std::vector<std::unique_ptr<DistributedMemoryManager>> nodes;  // node 0 = this process; others = in-process peers
+  std::shared_ptr<DmemFabric> fabric;
+  std::shared_ptr<ShmFabric> shm;   // set when the peers are other processes of this box
+  std::vector<std::unique_ptr<DistributedMemoryManager>> nodes;  // in-process emulation: one per node; otherwise only this node
   int self = 0;
 };
 GlobalDmem& gd() {
@@ -115,7 +116,7 @@ GlobalDmem& gd() {
 }
 DistributedMemoryManager& self_mgr() {
   MCCL_CHECK(!gd().nodes.empty(), "dmem is not initialised; call init_dmem(node_id, num_peers) first");
-  return *gd().nodes[static_cast<size_t>(gd().self)];
+  return *gd().nodes[gd().shm ? 0 : static_cast<size_t>(gd().self)];
 }
 
 // Stream-ordered acquire / release between the GPUs of a device communicator.
@@ -373,24 +374,44 @@ void bind_runtime(py::module_& m) {
 
   m.def(
       "init_dmem",
-      [](int node_id, int num_peers) {
+      [](int node_id, int num_peers, const std::string& shm_name) {
         GlobalDmem& g = gd();
         MCCL_CHECK(g.nodes.empty(), "dmem is already initialised");
         const int n = num_peers + 1;
         MCCL_CHECK(node_id >= 0 && node_id < n && n <= kDmemMaxNodes, "init_dmem: bad node_id / num_peers");
-        g.fabric = std::make_shared<LocalFabric>(n);
-        for (int i = 0; i < n; ++i) g.nodes.emplace_back(new DistributedMemoryManager(static_cast<uint16_t>(i), g.fabric));
         g.self = node_id;
+        if (!shm_name.empty()) {
+          // the peers are other processes of this box: directory and heaps in shared memory
+          g.shm = std::make_shared<ShmFabric>(shm_name, node_id, n);
+          g.fabric = g.shm;
+          g.nodes.emplace_back(new DistributedMemoryManager(static_cast<uint16_t>(node_id), g.fabric));
+          return;
+        }
+        auto local = std::make_shared<LocalFabric>(n);
+        g.fabric = local;
+        for (int i = 0; i < n; ++i) g.nodes.emplace_back(new DistributedMemoryManager(static_cast<uint16_t>(i), g.fabric));
       },
-      py::arg("node_id") = 0, py::arg("num_peers") = 0);
+      py::arg("node_id") = 0, py::arg("num_peers") = 0, py::arg("shm_name") = "", py::call_guard<py::gil_scoped_release>(),
+      "Without shm_name all nodes are emulated inside this process; with it the nodes are the processes of one box that "
+      "pass the same name (node 0 creates the shared directory).");
   m.def("shutdown_dmem", [] {
     gd().nodes.clear();
     gd().fabric.reset();
+    gd().shm.reset();
   });
+  m.def("alloc_dmem_heap", [](uint64_t nbytes) {
+    MCCL_CHECK(gd().shm != nullptr, "alloc_dmem_heap needs init_dmem(..., shm_name=...)");
+    auto r = gd().shm->alloc_heap(nbytes);
+    return py::make_tuple(r.first, reinterpret_cast<uintptr_t>(r.second));
+  }, py::arg("nbytes"), "Returns (heap id, address) of a zeroed host heap that the other processes of the job can reach.");
   m.def("dmem_initialised", [] { return !gd().nodes.empty(); });
   m.def("get_stats", [] { return gd().nodes.empty() ? dmem_stats_dict(DmemStats()) : dmem_stats_dict(self_mgr().stats()); });
-  m.def("register_region", [](uintptr_t ptr, uint64_t n, uint32_t flags) { return self_mgr().register_region(reinterpret_cast<void*>(ptr), n, flags); },
-        py::arg("ptr"), py::arg("nbytes"), py::arg("flags") = static_cast<uint32_t>(REGION_READABLE | REGION_WRITABLE | REGION_SHARED));
+  m.def("register_region", [](uintptr_t ptr, uint64_t n, uint32_t flags, uint32_t heap_id, uint64_t heap_offset) {
+          if (heap_id != 0 && !(flags & REGION_DEVICE)) flags |= REGION_HOST_HEAP;
+          return self_mgr().register_region(reinterpret_cast<void*>(ptr), n, flags, heap_id, heap_offset);
+        },
+        py::arg("ptr"), py::arg("nbytes"), py::arg("flags") = static_cast<uint32_t>(REGION_READABLE | REGION_WRITABLE | REGION_SHARED),
+        py::arg("heap_id") = 0, py::arg("heap_offset") = 0);
   m.def("register_region_on",
         [](int node, uintptr_t ptr, uint64_t n) {
           MCCL_CHECK(node >= 0 && node < static_cast<int>(gd().nodes.size()), "no such in-process node");

@@ -95,3 +95,56 @@ def test_dmem_and_coherence_between_processes():
     assert not bad, "\n".join(str(b[2]) for b in bad)
     assert all(r[2] > 0 for r in results)
     assert not [f for f in os.listdir("/dev/shm") if f.startswith(f"mccl-{name}")]   # segments are unlinked
+
+
+def _module_api(rank, world, name, barrier, queue):
+    try:
+        import mccl_b200
+        C = mccl_b200._C
+        C.init_dmem(node_id=rank, num_peers=world - 1, shm_name=name)
+        heap_id, ptr = C.alloc_dmem_heap(4096)
+        rid = C.register_region(ptr, 4096, heap_id=heap_id, heap_offset=0)
+        mine = _view(ptr, 4096)
+        barrier.wait()
+        peer = (rank + 1) % world
+        src = np.arange(256, dtype=np.uint8) ^ rank
+        assert C.put(peer, rid, 512, src.ctypes.data, 256) != 0
+        assert C.drain_pending() >= 0
+        barrier.wait()
+        left = (rank - 1) % world
+        assert (mine[512:768] == (np.arange(256, dtype=np.uint8) ^ left)).all()
+        back = np.zeros(256, dtype=np.uint8)
+        assert C.get(peer, rid, 512, back.ctypes.data, 256) != 0
+        assert (back == src).all()
+        st = C.get_stats()
+        assert st["total_put_ops"] == 1 and st["total_get_ops"] == 1 and st["total_errors"] == 0
+        # memory that is not in a shared heap cannot be reached from another process: the call fails cleanly
+        private = np.zeros(64, dtype=np.uint8)
+        prid = C.register_region(private.ctypes.data, 64)
+        barrier.wait()
+        assert C.put(peer, prid, 0, src.ctypes.data, 8) == 0
+        assert C.get_stats()["total_errors"] == 1
+        barrier.wait()
+        C.shutdown_dmem()
+        queue.put((rank, "ok", 1))
+    except BaseException as e:  # noqa: BLE001
+        queue.put((rank, "error", f"{type(e).__name__}: {e}\n{traceback.format_exc()}"))
+        try:
+            barrier.abort()
+        except Exception:
+            pass
+
+
+def test_module_level_dmem_between_processes():
+    world = 2
+    ctx = mp.get_context("spawn")
+    barrier, queue = ctx.Barrier(world), ctx.Queue()
+    name = f"m{os.getpid()}"
+    procs = [ctx.Process(target=_module_api, args=(r, world, name, barrier, queue), daemon=True) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [queue.get(timeout=120) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=10)
+    bad = [r for r in results if r[1] != "ok"]
+    assert not bad, "\n".join(str(b[2]) for b in bad)
