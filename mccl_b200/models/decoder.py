@@ -133,7 +133,8 @@ class Block(nn.Module):
         B, S, D = x.shape
         h = self.ln1(x, native)
         qkv = self.qkv(h, native).view(B, S, 3, cfg.n_heads, cfg.head_dim)
-        q, k, v = (qkv[:, :, i].transpose(1, 2) for i in range(3))
+        # unbind, not three selects: its backward is one stack instead of three zero-filled tensors and two adds
+        q, k, v = (t.transpose(1, 2) for t in qkv.unbind(2))
         if rope is not None:
             q, k = apply_rope(q, *rope), apply_rope(k, *rope)
         a = F.scaled_dot_product_attention(q, k, v, is_causal=True)

@@ -212,7 +212,7 @@ class ParallelAttention(nn.Module):
         from ..models.decoder import apply_rope
         B, S, H, D = self.batch, self.seq, self.heads_local, self.head_dim
         qkv = self.qkv(x).view(B, S, 3, H, D)
-        q, k, v = (qkv[:, :, i].transpose(1, 2) for i in range(3))
+        q, k, v = (t.transpose(1, 2) for t in qkv.unbind(2))
         if rope is not None:
             q, k = apply_rope(q, *rope), apply_rope(k, *rope)
         a = F.scaled_dot_product_attention(q, k, v, is_causal=True)
