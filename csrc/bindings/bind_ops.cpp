@@ -144,8 +144,15 @@ void bind_ops(py::module_& m) {
   m.def(
       "norm_bwd",
       [](const at::Tensor& dy, const at::Tensor& x, const at::Tensor& w, const at::Tensor& mean, const at::Tensor& rstd,
-         bool layernorm, const c10::optional<at::Tensor>& dw_out, const c10::optional<at::Tensor>& db_out, bool accumulate) {
+         bool layernorm, const c10::optional<at::Tensor>& dw_out, const c10::optional<at::Tensor>& db_out, bool accumulate,
+         const c10::optional<at::Tensor>& dx_add) {
         need(dy, at::kBFloat16, "norm_bwd(dy)");
+        const __nv_bfloat16* addp = nullptr;
+        if (dx_add.has_value() && dx_add->defined()) {
+          need(*dx_add, at::kBFloat16, "norm_bwd(dx_add)");
+          MCCL_CHECK_TENSOR(dx_add->numel() == x.numel(), "norm_bwd: dx_add must have the shape of x");
+          addp = bf(*dx_add);
+        }
         need(x, at::kBFloat16, "norm_bwd(x)");
         need(w, at::kFloat, "norm_bwd(weight)");
         need(mean, at::kFloat, "norm_bwd(mean)");
@@ -167,12 +174,13 @@ void bind_ops(py::module_& m) {
                                    dw.data_ptr<float>(), layernorm ? db.data_ptr<float>() : nullptr,
                                    accumulate ? nullptr : scratch.data_ptr<float>(),
                                    static_cast<int>(rows),
-                                   static_cast<int>(dim), layernorm, stream_of(x)),
+                                   static_cast<int>(dim), layernorm, stream_of(x), addp),
                      "norm_bwd");
         return std::make_tuple(dx, dw, db.defined() ? c10::optional<at::Tensor>(db) : c10::nullopt);
       },
       py::arg("dy"), py::arg("x"), py::arg("weight"), py::arg("mean"), py::arg("rstd"), py::arg("layernorm"),
-      py::arg("dw_out") = py::none(), py::arg("db_out") = py::none(), py::arg("accumulate") = false);
+      py::arg("dw_out") = py::none(), py::arg("db_out") = py::none(), py::arg("accumulate") = false,
+      py::arg("dx_add") = py::none());
 
   m.def(
       "adamw_flat",

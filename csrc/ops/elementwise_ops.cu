@@ -95,10 +95,12 @@ template <bool kLayerNorm>
 __global__ void __launch_bounds__(256) norm_bwd_dx_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                                                           const float* __restrict__ w, const float* __restrict__ mean,
                                                           const float* __restrict__ rstd, __nv_bfloat16* __restrict__ dx,
-                                                          int rows, int dim) {
+                                                          const __nv_bfloat16* __restrict__ dx_add, int rows, int dim) {
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (warp >= rows) return;
   const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<size_t>(warp) * dim);
+  // optional: a second gradient of the same tensor (the residual path), added before the one rounding to bf16
+  const uint4* ar = dx_add ? reinterpret_cast<const uint4*>(dx_add + static_cast<size_t>(warp) * dim) : nullptr;
   const uint4* gr = reinterpret_cast<const uint4*>(dy + static_cast<size_t>(warp) * dim);
   const int vecs = dim >> 3;
   const float mu = mean[warp], rs = rstd[warp];
@@ -127,6 +129,12 @@ __global__ void __launch_bounds__(256) norm_bwd_dx_kernel(const __nv_bfloat16* _
     const float ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
 #pragma unroll
     for (int i = 0; i < 8; ++i) o[i] = rs * (g[i] * ww[i] - c2 - (f[i] - mu) * rs * c1);
+    if (ar != nullptr) {
+      float a[8];
+      unpack8(ar[v], a);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[i] += a[i];
+    }
     dr[v] = pack8(o);
   }
 }
@@ -235,11 +243,11 @@ cudaError_t norm_fwd(const __nv_bfloat16* x, const float* w, const float* b, __n
 
 cudaError_t norm_bwd(const __nv_bfloat16* dy, const __nv_bfloat16* x, const float* w, const float* mean, const float* rstd,
                      __nv_bfloat16* dx, float* dw, float* db, float* scratch, int rows, int dim, bool layernorm,
-                     cudaStream_t stream) {
+                     cudaStream_t stream, const __nv_bfloat16* dx_add) {
   if (dim % 8 != 0) return cudaErrorNotSupported;
   const int blocks = (rows + 7) / 8;
-  if (layernorm) norm_bwd_dx_kernel<true><<<blocks, 256, 0, stream>>>(dy, x, w, mean, rstd, dx, rows, dim);
-  else norm_bwd_dx_kernel<false><<<blocks, 256, 0, stream>>>(dy, x, w, mean, rstd, dx, rows, dim);
+  if (layernorm) norm_bwd_dx_kernel<true><<<blocks, 256, 0, stream>>>(dy, x, w, mean, rstd, dx, dx_add, rows, dim);
+  else norm_bwd_dx_kernel<false><<<blocks, 256, 0, stream>>>(dy, x, w, mean, rstd, dx, dx_add, rows, dim);
   const int slabs = colsum_slabs(rows);
   dim3 grid((dim + 255) / 256, slabs);
   if (!scratch) {

@@ -26,10 +26,11 @@ cudaError_t norm_fwd(const __nv_bfloat16* x, const float* w, const float* b, __n
                      int rows, int dim, float eps, cudaStream_t stream);
 // dx: [rows, dim] bf16; dw, db: fp32 [dim].  With scratch (fp32, 2 * colsum_slabs(rows) * dim
 // elements) dw / db are overwritten by a two-stage, order-fixed reduction; with scratch == nullptr
-// the slab sums are added to dw / db atomically in one pass.
+// the slab sums are added to dw / db atomically in one pass.  dx_add (optional, [rows, dim] bf16) is a
+// second gradient of x (a residual path) that is added to dx before the one rounding to bf16.
 cudaError_t norm_bwd(const __nv_bfloat16* dy, const __nv_bfloat16* x, const float* w, const float* mean, const float* rstd,
                      __nv_bfloat16* dx, float* dw, float* db, float* scratch, int rows, int dim, bool layernorm,
-                     cudaStream_t stream);
+                     cudaStream_t stream, const __nv_bfloat16* dx_add = nullptr);
 // out[c] = sum over rows of in[r, c] (bias gradients).  scratch: colsum_slabs(rows) * dim floats,
 // or nullptr to add into out atomically in one pass.
 cudaError_t colsum_bf16(const __nv_bfloat16* in, float* out, float* scratch, int rows, int dim, cudaStream_t stream);

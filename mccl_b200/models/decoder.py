@@ -18,6 +18,7 @@ is also the numerics reference in the tests.
 from __future__ import annotations
 
 import dataclasses
+import os
 import math
 from typing import Optional
 
@@ -62,6 +63,10 @@ PRESETS = {
 }
 
 
+# Opt-in (not yet measured on a GPU): residual gradients are added inside the norm-backward kernel.
+_FUSE_RESIDUAL_GRAD = os.environ.get("MCCL_FUSE_RESIDUAL_GRAD", "0") == "1"
+
+
 def _rope_tables(seq: int, dim: int, device, base: float = 10000.0):
     inv = 1.0 / (base ** (torch.arange(0, dim, 2, device=device, dtype=torch.float32) / dim))
     t = torch.arange(seq, device=device, dtype=torch.float32)
@@ -92,6 +97,15 @@ class Norm(nn.Module):
             return F.layer_norm(x.float(), x.shape[-1:], self.weight, self.bias, self.eps).to(x.dtype)
         v = x.float()
         return (v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + self.eps) * self.weight).to(x.dtype)
+
+    def with_residual(self, x: torch.Tensor, native: bool):
+        """(norm(x), x as it should be fed to the residual connection).  With MCCL_FUSE_RESIDUAL_GRAD=1 the
+        native path hands x through the norm operator so that backward adds the residual gradient in the
+        norm-backward kernel; otherwise x is returned untouched."""
+        if native and _FUSE_RESIDUAL_GRAD:
+            from .. import ops
+            return ops.norm_residual(x, self.weight, self.bias, self.eps)
+        return self.forward(x, native), x
 
 
 class Linear(nn.Module):
@@ -131,7 +145,7 @@ class Block(nn.Module):
     def forward(self, x: torch.Tensor, rope, native: bool) -> torch.Tensor:
         cfg = self.cfg
         B, S, D = x.shape
-        h = self.ln1(x, native)
+        h, x = self.ln1.with_residual(x, native)
         qkv = self.qkv(h, native).view(B, S, 3, cfg.n_heads, cfg.head_dim)
         # unbind, not three selects: its backward is one stack instead of three zero-filled tensors and two adds
         q, k, v = (t.transpose(1, 2) for t in qkv.unbind(2))
@@ -139,7 +153,7 @@ class Block(nn.Module):
             q, k = apply_rope(q, *rope), apply_rope(k, *rope)
         a = F.scaled_dot_product_attention(q, k, v, is_causal=True)
         x = self.proj(a.transpose(1, 2).reshape(B, S, D), native, residual=x)
-        h = self.ln2(x, native)
+        h, x = self.ln2.with_residual(x, native)
         if cfg.act == "swiglu":
             g, u = self.gate_up(h, native).chunk(2, dim=-1)
             h = F.silu(g) * u

@@ -33,6 +33,15 @@ def norm(x: torch.Tensor, weight: torch.Tensor, bias, eps: float) -> torch.Tenso
     return (v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps) * weight).to(x.dtype)
 
 
+def norm_residual(x: torch.Tensor, weight: torch.Tensor, bias, eps: float):
+    """``(norm(x), x)``: use the second value as the residual input of the branch so that the two gradients
+    of x are added inside the norm-backward kernel."""
+    if x.is_cuda and _HAS["norm_fwd"]:
+        from .native import NormResidualFn
+        return NormResidualFn.apply(x, weight, bias, eps)
+    return norm(x, weight, bias, eps), x
+
+
 def linear(x: torch.Tensor, weight: torch.Tensor, bias=None, act: str = "none", residual=None) -> torch.Tensor:
     """act(x @ W^T + b) + residual, in one kernel on CUDA."""
     if x.is_cuda and _HAS["gemm_bf16"]:

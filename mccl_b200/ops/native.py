@@ -138,6 +138,38 @@ class NormFn(torch.autograd.Function):
         return dx, dw, db, None
 
 
+class NormResidualFn(torch.autograd.Function):
+    """Norm of a tensor that also continues as a residual: returns ``(norm(x), x)``.  In backward the
+    gradient that comes back along the residual is added inside the norm-backward kernel (before its
+    single rounding to bf16) instead of by a separate add kernel."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, eps):
+        xc = x if x.is_contiguous() else x.contiguous()
+        y, mean, rstd = _C.norm_fwd(xc, weight, bias, eps)
+        ctx.save_for_backward(xc, weight, mean, rstd)
+        ctx.layernorm = bias is not None
+        ctx.weight, ctx.bias = weight, bias
+        return y, xc.view_as(xc)
+
+    @staticmethod
+    def backward(ctx, dy, dres):
+        x, weight, mean, rstd = ctx.saved_tensors
+        if dy is None:
+            return dres, None, None, None
+        dyc = dy if dy.is_contiguous() else dy.contiguous()
+        add = None if dres is None else (dres if dres.is_contiguous() else dres.contiguous())
+        wsink, bsink = _sink(ctx.weight), (_sink(ctx.bias) if ctx.bias is not None else None)
+        if wsink is not None and (not ctx.layernorm or bsink is not None):
+            dx, _, _ = _C.norm_bwd(dyc, x, weight, mean, rstd, ctx.layernorm, wsink, bsink, True, add)
+            _notify(ctx.weight)
+            if ctx.bias is not None:
+                _notify(ctx.bias)
+            return dx, None, None, None
+        dx, dw, db = _C.norm_bwd(dyc, x, weight, mean, rstd, ctx.layernorm, None, None, False, add)
+        return dx, dw, db, None
+
+
 class LinearCrossEntropyFn(torch.autograd.Function):
     """mean CE(h @ W^T, targets).  The backward of the loss with respect to the logits is
     produced in the same pass that computes the loss, in place of the logits, assuming the

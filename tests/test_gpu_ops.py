@@ -217,3 +217,42 @@ def test_embedding_forward_backward(with_pos):
         pref = torch.zeros(S + 4, D, device="cuda")
         pref[:S] = dy.float().sum(0)
         assert _rel(pos.grad, pref) < 1e-5
+
+
+_OPTIN = pytest.mark.skipif(__import__("os").environ.get("MCCL_TEST_OPTIN", "0") != "1",
+                            reason="opt-in paths that are off by default; set MCCL_TEST_OPTIN=1")
+
+
+@_OPTIN
+@pytest.mark.parametrize("layernorm", [True, False])
+def test_norm_backward_adds_residual_gradient(layernorm):
+    C = _C()
+    torch.manual_seed(3)
+    rows, dim = 300, 512
+    x = torch.randn(rows, dim, device="cuda").bfloat16()
+    w = torch.randn(dim, device="cuda")
+    b = torch.randn(dim, device="cuda") if layernorm else None
+    dy = torch.randn(rows, dim, device="cuda").bfloat16()
+    dres = torch.randn(rows, dim, device="cuda").bfloat16()
+    _, mean, rstd = C.norm_fwd(x, w, b, 1e-5)
+    dx0, dw0, _ = C.norm_bwd(dy, x, w, mean, rstd, layernorm)
+    dx1, dw1, _ = C.norm_bwd(dy, x, w, mean, rstd, layernorm, None, None, False, dres)
+    assert torch.equal(dw0, dw1)
+    assert _rel(dx1, dx0.float() + dres.float()) < 1e-2
+
+
+@_OPTIN
+def test_norm_residual_function_matches_separate_add():
+    from mccl_b200 import ops
+    torch.manual_seed(4)
+    x = torch.randn(64, 256, device="cuda").bfloat16().requires_grad_(True)
+    w = torch.randn(256, device="cuda", requires_grad=True)
+    b = torch.randn(256, device="cuda", requires_grad=True)
+    y, xr = ops.norm_residual(x, w, b, 1e-5)
+    out = (y * 2).float().sum() + (xr.float() * 3).sum()
+    out.backward()
+    gx, gw = x.grad.clone(), w.grad.clone()
+    x.grad = w.grad = b.grad = None
+    out2 = (ops.norm(x, w, b, 1e-5) * 2).float().sum() + (x.float() * 3).sum()
+    out2.backward()
+    assert _rel(gx, x.grad) < 1e-2 and _rel(gw, w.grad) < 1e-4
