@@ -219,11 +219,6 @@ def test_embedding_forward_backward(with_pos):
         assert _rel(pos.grad, pref) < 1e-5
 
 
-_OPTIN = pytest.mark.skipif(__import__("os").environ.get("MCCL_TEST_OPTIN", "0") != "1",
-                            reason="opt-in paths that are off by default; set MCCL_TEST_OPTIN=1")
-
-
-@_OPTIN
 @pytest.mark.parametrize("layernorm", [True, False])
 def test_norm_backward_adds_residual_gradient(layernorm):
     C = _C()
@@ -241,7 +236,6 @@ def test_norm_backward_adds_residual_gradient(layernorm):
     assert _rel(dx1, dx0.float() + dres.float()) < 1e-2
 
 
-@_OPTIN
 def test_norm_residual_function_matches_separate_add():
     from mccl_b200 import ops
     torch.manual_seed(4)
