@@ -284,7 +284,6 @@ __device__ void reduce_scatter_role(const FusedDev& f, const GemmDev& g, uint32_
                 static_cast<const char*>(f.rs_partial[epoch & 1u][r]) + my_base + off, n, &sh->full[s]);
     return true;
   };
-  uint32_t consumed_loaded = 0;   // thread 0: loaded pieces consumed so far
   uint32_t j = 0;
   for (;; ++j) {
     const uint32_t s = j % kReduceStages;
@@ -315,7 +314,6 @@ __device__ void reduce_scatter_role(const FusedDev& f, const GemmDev& g, uint32_
       }
       break;
     }
-    if (tid == 0) ++consumed_loaded;
     unsigned long long off;
     uint32_t n;
     piece_range(p, off, n);
@@ -350,7 +348,6 @@ __device__ void reduce_scatter_role(const FusedDev& f, const GemmDev& g, uint32_
     for (uint32_t q = j; q < issued; ++q)
       if (sh->piece[q % kReduceStages] != kNoPiece) tc::mbar_wait(&sh->full[q % kReduceStages], (q / kReduceStages) & 1u, 1u << 22);
   }
-  (void)consumed_loaded;
 }
 
 // ++*epoch and, when given, *zeroed = 0 (the reduce-scatter fusion's piece counter).
