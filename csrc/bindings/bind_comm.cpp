@@ -173,6 +173,10 @@ void bind_comm(py::module_& m) {
       .def("clear_status", &DeviceComm::clear_status)
       .def("inject_skip_signals", &DeviceComm::inject_skip_signals, py::arg("count") = 1)
       .def("set_device_timeout_ms", &DeviceComm::set_device_timeout_ms)
+      .def_property_readonly("device_timeout_ms", &DeviceComm::device_timeout_ms)
+      .def_property_readonly("max_ctas", &DeviceComm::max_ctas)
+      .def_property_readonly("launch_threads", &DeviceComm::launch_threads)
+      .def("set_launch_shape", &DeviceComm::set_launch_shape, py::arg("max_ctas") = 0, py::arg("threads") = 0)
       .def("decide_allreduce",
            [](DeviceComm& c, const std::string& algo, int64_t numel, at::ScalarType dt, const std::string& op,
               const std::string& wire, int64_t tree_below) {
@@ -258,6 +262,45 @@ void bind_comm(py::module_& m) {
           },
           py::arg("ins"), py::arg("outs"), py::arg("in_splits"), py::arg("out_splits"),
           "Split sizes are element counts per peer, one list per local rank.")
+      .def(
+          "send",
+          [](DeviceComm& c, const at::Tensor& t, int peer) {
+            MCCL_CHECK_TENSOR(t.is_cuda() && t.is_contiguous() && t.get_device() == c.device(), "send: contiguous tensor on cuda:" << c.device() << " expected");
+            c10::cuda::CUDAGuard g(t.device());
+            c.send(t.data_ptr(), static_cast<size_t>(t.numel()) * t.element_size(), peer, cur_stream(c.device()));
+          },
+          py::arg("tensor"), py::arg("peer"))
+      .def(
+          "recv",
+          [](DeviceComm& c, at::Tensor t, int peer) {
+            MCCL_CHECK_TENSOR(t.is_cuda() && t.is_contiguous() && t.get_device() == c.device(), "recv: contiguous tensor on cuda:" << c.device() << " expected");
+            c10::cuda::CUDAGuard g(t.device());
+            c.recv(t.data_ptr(), static_cast<size_t>(t.numel()) * t.element_size(), peer, cur_stream(c.device()));
+          },
+          py::arg("tensor"), py::arg("peer"))
+      .def(
+          "p2p_emulated",
+          [](DeviceComm& c, std::vector<at::Tensor> bufs, std::vector<int> peers, std::vector<bool> is_send) {
+            MCCL_CHECK_TENSOR(static_cast<int>(bufs.size()) == c.nlocal() && peers.size() == bufs.size() && is_send.size() == bufs.size(),
+                              "p2p_emulated: one buffer, peer and direction per virtual rank expected");
+            std::vector<DeviceComm::P2POp> ops(bufs.size());
+            size_t nbytes = 0;
+            for (size_t v = 0; v < bufs.size(); ++v) {
+              if (peers[v] < 0) continue;
+              MCCL_CHECK_TENSOR(bufs[v].is_cuda() && bufs[v].is_contiguous(), "p2p_emulated: contiguous CUDA tensors expected");
+              const size_t nb = static_cast<size_t>(bufs[v].numel()) * bufs[v].element_size();
+              MCCL_CHECK_TENSOR(nbytes == 0 || nb == nbytes, "p2p_emulated: all transfers of one launch have the same size");
+              nbytes = nb;
+              ops[v].buf = bufs[v].data_ptr();
+              ops[v].peer = peers[v];
+              ops[v].is_send = is_send[v];
+            }
+            c10::cuda::CUDAGuard g(at::Device(at::kCUDA, static_cast<c10::DeviceIndex>(c.device())));
+            c.p2p_emulated(ops, nbytes, cur_stream(c.device()));
+          },
+          py::arg("bufs"), py::arg("peers"), py::arg("is_send"),
+          "Single-GPU emulation: virtual rank v sends bufs[v] to / receives bufs[v] from peers[v] (-1: idle), all in one launch.")
+      .def_property_readonly("p2p_slot_bytes", &DeviceComm::p2p_slot_bytes)
       .def("barrier", [](DeviceComm& c) {
         c10::cuda::CUDAGuard g(at::Device(at::kCUDA, static_cast<c10::DeviceIndex>(c.device())));
         c.barrier(cur_stream(c.device()));

@@ -7,6 +7,7 @@
 #include <torch/extension.h>
 
 #include "../core/errors.hpp"
+#include "../core/timeline.hpp"
 #include "../ops/ops.hpp"
 #include "../ops/tp_gemm.hpp"
 #include "../pg/device_comm.hpp"
@@ -46,6 +47,35 @@ int parse_epilogue(const std::string& s, bool has_bias) {
 void bind_ops(py::module_& m) {
   m.def("op_launch_count", [] { return ops::launch_count(); });
   m.def("gemm_error_flag", [] { return ops::gemm_error_flag(); });
+  m.def("set_gemm_cta_limit", &ops::set_gemm_cta_limit, py::arg("ctas"),
+        "Caps the CTAs (SMs) of plain GEMM launches from now on; 0 = one per SM.");
+  m.def("gemm_cta_limit", &ops::gemm_cta_limit);
+  m.def("gemm_sm_count", &ops::gemm_sm_count);
+
+  // ---- device timeline (kernels stamp %globaltimer; see csrc/core/timeline.hpp) ----
+  m.def("timeline_enable", [](int device, int capacity, int every) {
+    c10::cuda::CUDAGuard g(at::Device(at::kCUDA, static_cast<c10::DeviceIndex>(device)));
+    timeline_enable(capacity, every);
+  }, py::arg("device"), py::arg("capacity") = 65536, py::arg("every") = 1);
+  m.def("timeline_disable", [](int device) {
+    c10::cuda::CUDAGuard g(at::Device(at::kCUDA, static_cast<c10::DeviceIndex>(device)));
+    timeline_disable();
+  }, py::arg("device"));
+  m.def("timeline_drain", [](int device) {
+    c10::cuda::CUDAGuard g(at::Device(at::kCUDA, static_cast<c10::DeviceIndex>(device)));
+    std::vector<TimelineRec> recs = timeline_drain();
+    at::Tensor out = at::empty({static_cast<int64_t>(recs.size()), 6}, at::TensorOptions().dtype(at::kLong));
+    int64_t* p = out.data_ptr<int64_t>();
+    for (size_t i = 0; i < recs.size(); ++i) {
+      p[6 * i + 0] = static_cast<int64_t>(recs[i].t0);
+      p[6 * i + 1] = static_cast<int64_t>(recs[i].t1);
+      p[6 * i + 2] = recs[i].kind;
+      p[6 * i + 3] = recs[i].tag;
+      p[6 * i + 4] = recs[i].sm;
+      p[6 * i + 5] = recs[i].cta;
+    }
+    return out;
+  }, py::arg("device"), "Rows of (t0 ns, t1 ns, kind, tag, sm, cta), sorted by t0; rewinds the buffer.");
 
   // D[M,N] = A[M,K] · B[N,K]^T.  A and B are 2-D bf16 with unit inner stride
   // (row strides may exceed the row length).  With a_t (b_t) the operand is
@@ -185,7 +215,7 @@ void bind_ops(py::module_& m) {
   m.def(
       "adamw_flat",
       [](at::Tensor p, const at::Tensor& g, at::Tensor mm, at::Tensor v, const c10::optional<at::Tensor>& p16, double lr,
-         double b1, double b2, double eps, double wd, const at::Tensor& step, double grad_scale) {
+         double b1, double b2, double eps, double wd, const at::Tensor& step, double grad_scale, bool zero_grad) {
         need(p, at::kFloat, "adamw(p)");
         need(g, at::kFloat, "adamw(g)");
         need(mm, at::kFloat, "adamw(m)");
@@ -199,15 +229,15 @@ void bind_ops(py::module_& m) {
           MCCL_CHECK_TENSOR(p16->numel() == p.numel(), "adamw: bf16 copy size mismatch");
           p16p = bf(*p16);
         }
-        check_launch(ops::adamw_flat(p.data_ptr<float>(), g.data_ptr<float>(), mm.data_ptr<float>(), v.data_ptr<float>(), p16p,
-                                     p.numel(), static_cast<float>(lr), static_cast<float>(b1), static_cast<float>(b2),
-                                     static_cast<float>(eps), static_cast<float>(wd), step.data_ptr<float>(),
-                                     static_cast<float>(grad_scale), stream_of(p)),
+        check_launch(ops::adamw_flat(p.data_ptr<float>(), const_cast<float*>(g.data_ptr<float>()), mm.data_ptr<float>(),
+                                     v.data_ptr<float>(), p16p, p.numel(), static_cast<float>(lr), static_cast<float>(b1),
+                                     static_cast<float>(b2), static_cast<float>(eps), static_cast<float>(wd),
+                                     step.data_ptr<float>(), static_cast<float>(grad_scale), stream_of(p), zero_grad),
                      "adamw_flat");
       },
       py::arg("p"), py::arg("g"), py::arg("m"), py::arg("v"), py::arg("p_bf16") = py::none(), py::arg("lr") = 1e-3,
       py::arg("beta1") = 0.9, py::arg("beta2") = 0.999, py::arg("eps") = 1e-8, py::arg("weight_decay") = 0.01,
-      py::arg("step") = at::Tensor(), py::arg("grad_scale") = 1.0);
+      py::arg("step") = at::Tensor(), py::arg("grad_scale") = 1.0, py::arg("zero_grad") = false);
 
   m.def(
       "ce_fwd_bwd",

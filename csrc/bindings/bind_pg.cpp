@@ -43,6 +43,34 @@ void bind_pg(py::module_& m) {
       .def("last_algo", &ProcessGroupMCCL::lastAlgo)
       .def("check_device_status", &ProcessGroupMCCL::checkDeviceStatus)
       .def(
+          "allreduce_with",
+          [](ProcessGroupMCCL& pg, at::Tensor t, const std::string& op, const std::string& wire, const std::string& algo) {
+            auto parse_op = [](const std::string& s) {
+              if (s == "sum") return RedOp::SUM;
+              if (s == "avg" || s == "mean") return RedOp::AVG;
+              if (s == "min") return RedOp::MIN;
+              if (s == "max") return RedOp::MAX;
+              if (s == "product" || s == "prod") return RedOp::PRODUCT;
+              MCCL_CHECK(false, "allreduce_with: unknown reduce op '" << s << "'");
+              return RedOp::SUM;
+            };
+            auto parse_algo = [](const std::string& s) {
+              if (s.empty() || s == "auto") return Algo::AUTO;
+              if (s == "ring") return Algo::RING;
+              if (s == "tree") return Algo::TREE;
+              if (s == "butterfly" || s == "twoshot") return Algo::BUTTERFLY;
+              if (s == "oneshot") return Algo::ONESHOT;
+              if (s == "nvls") return Algo::NVLS;
+              MCCL_CHECK(false, "allreduce_with: unknown algorithm '" << s << "'");
+              return Algo::AUTO;
+            };
+            std::vector<at::Tensor> ts{t};
+            return pg.allreduceWith(ts, parse_op(op), parse_algo(algo), wire == "bf16" ? WireDtype::BF16 : WireDtype::NATIVE);
+          },
+          py::arg("tensor"), py::arg("op") = "sum", py::arg("wire") = "native", py::arg("algo") = "auto",
+          py::call_guard<py::gil_scoped_release>(),
+          "In-place allreduce with the wire dtype and algorithm as arguments (the environment is not consulted).")
+      .def(
           "set_p2p_factory",
           [](ProcessGroupMCCL& pg, py::function factory) {
             // The group may be destroyed on a thread without the GIL (or while
@@ -67,10 +95,13 @@ void bind_pg(py::module_& m) {
 
   m.def(
       "_create_process_group_mccl",
-      [](const c10::intrusive_ptr<c10d::Store>& store, int rank, int size, std::chrono::milliseconds timeout) {
-        return c10::make_intrusive<ProcessGroupMCCL>(store, rank, size, timeout);
+      [](const c10::intrusive_ptr<c10d::Store>& store, int rank, int size, std::chrono::milliseconds timeout, int64_t arena_mb) {
+        auto pg = c10::make_intrusive<ProcessGroupMCCL>(store, rank, size, timeout);
+        if (arena_mb > 0) pg->setArenaBytes(arena_mb << 20);
+        return pg;
       },
       py::arg("store"), py::arg("rank"), py::arg("size"), py::arg("timeout") = std::chrono::milliseconds(30 * 60 * 1000),
+      py::arg("arena_mb") = 0,
       py::call_guard<py::gil_scoped_release>());
 
   m.def("set_log_level", [](const std::string& name) { set_log_level(name); });

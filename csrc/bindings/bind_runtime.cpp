@@ -21,6 +21,8 @@
 #include "../dmem/dmem_kernels.hpp"
 #include "../dmem/dmem_manager.hpp"
 #include "../dmem/shm_domain.hpp"
+#include "../dmem/symm_fabric.hpp"
+#include "../pg/process_group.hpp"
 #include "../pg/device_comm.hpp"
 #include "../runtime/kernel_dispatch.hpp"
 #include "../symm/symm_mesh.hpp"
@@ -107,6 +109,9 @@ py::dict dmem_stats_dict(const DmemStats& s) {
 struct GlobalDmem {
   std::shared_ptr<DmemFabric> fabric;
   std::shared_ptr<ShmFabric> shm;   // set when the peers are other processes of this box
+  std::shared_ptr<SymmFabric> symm; // set when the peers are the GPUs of a process group (regions in the symmetric heap)
+  std::shared_ptr<DeviceComm> comm; // the group's device communicator (symm only)
+  c10::intrusive_ptr<ProcessGroupMCCL> pg;  // keeps the store alive (symm only)
   std::vector<std::unique_ptr<DistributedMemoryManager>> nodes;  // in-process emulation: one per node; otherwise only this node
   int self = 0;
 };
@@ -116,7 +121,12 @@ GlobalDmem& gd() {
 }
 DistributedMemoryManager& self_mgr() {
   MCCL_CHECK(!gd().nodes.empty(), "dmem is not initialised; call init_dmem(node_id, num_peers) first");
-  return *gd().nodes[gd().shm ? 0 : static_cast<size_t>(gd().self)];
+  return *gd().nodes[(gd().shm || gd().symm) ? 0 : static_cast<size_t>(gd().self)];
+}
+// Stream the module-level device copies run on: the current stream of the communicator's GPU.
+void* dmem_stream() {
+  if (!gd().comm) return nullptr;
+  return static_cast<void*>(at::cuda::getCurrentCUDAStream(static_cast<c10::DeviceIndex>(gd().comm->device())).stream());
 }
 
 // Stream-ordered acquire / release between the GPUs of a device communicator.
@@ -394,10 +404,41 @@ void bind_runtime(py::module_& m) {
       py::arg("node_id") = 0, py::arg("num_peers") = 0, py::arg("shm_name") = "", py::call_guard<py::gil_scoped_release>(),
       "Without shm_name all nodes are emulated inside this process; with it the nodes are the processes of one box that "
       "pass the same name (node 0 creates the shared directory).");
+  m.def(
+      "init_dmem_symm",
+      [](c10::intrusive_ptr<ProcessGroupMCCL> pg, int device_index) {
+        GlobalDmem& g = gd();
+        MCCL_CHECK(g.nodes.empty(), "dmem is already initialised");
+        MCCL_CHECK(pg->getSize() <= kDmemMaxNodes, "init_dmem_symm: group too large");
+        g.comm = pg->deviceComm(at::Device(at::kCUDA, static_cast<c10::DeviceIndex>(device_index)));
+        g.pg = pg;
+        g.self = pg->getRank();
+        auto rings = g.comm->symm_alloc(SymmFabric::ring_bytes(pg->getSize()));
+        g.symm = std::make_shared<SymmFabric>(pg->kv(), pg->getRank(), pg->getSize(), "mccl/dmem", pg->timeoutMs(), rings);
+        g.fabric = g.symm;
+        g.nodes.emplace_back(new DistributedMemoryManager(static_cast<uint16_t>(pg->getRank()), g.fabric));
+      },
+      py::arg("process_group"), py::arg("device_index"), py::call_guard<py::gil_scoped_release>(),
+      "Collective over a backend='mccl' group with one GPU per rank: the nodes are the ranks, regions live in symmetric "
+      "heaps (alloc_symm_heap) that every rank maps over NVLink, and put / get / put_with_imm run on the current CUDA stream.");
+  m.def(
+      "alloc_symm_heap",
+      [](uint64_t nbytes) {
+        MCCL_CHECK(gd().symm != nullptr, "alloc_symm_heap needs init_dmem_symm(process_group, device)");
+        auto a = gd().comm->symm_alloc(nbytes);
+        const uint32_t heap_id = a->id + 1;   // 0 means "not in a heap"
+        gd().symm->add_heap(heap_id, a);
+        return py::make_tuple(heap_id, a);
+      },
+      py::arg("nbytes"), py::call_guard<py::gil_scoped_release>(),
+      "Collective.  Returns (heap id, SymmAlloc): device memory of `nbytes` on every rank, each block mapped in every process.");
   m.def("shutdown_dmem", [] {
     gd().nodes.clear();
     gd().fabric.reset();
     gd().shm.reset();
+    gd().symm.reset();
+    gd().comm.reset();
+    gd().pg.reset();
   });
   m.def("alloc_dmem_heap", [](uint64_t nbytes) {
     MCCL_CHECK(gd().shm != nullptr, "alloc_dmem_heap needs init_dmem(..., shm_name=...)");
@@ -420,11 +461,27 @@ void bind_runtime(py::module_& m) {
         "Registers memory on behalf of an in-process peer node (single-process emulation of a cluster).");
   m.def("unregister_region", [](uint32_t id) { return self_mgr().unregister_region(id); });
   m.def("put", [](int node, uint32_t region, uint64_t off, uintptr_t src, uint64_t len) {
-    return self_mgr().put(GlobalAddress(static_cast<uint16_t>(node), region, off), reinterpret_cast<const void*>(src), len);
+    return self_mgr().put(GlobalAddress(static_cast<uint16_t>(node), region, off), reinterpret_cast<const void*>(src), len, dmem_stream());
   });
   m.def("get", [](int node, uint32_t region, uint64_t off, uintptr_t dst, uint64_t len) {
-    return self_mgr().get(reinterpret_cast<void*>(dst), GlobalAddress(static_cast<uint16_t>(node), region, off), len);
+    return self_mgr().get(reinterpret_cast<void*>(dst), GlobalAddress(static_cast<uint16_t>(node), region, off), len, dmem_stream());
   });
+  m.def("put_with_imm", [](int node, uint32_t region, uint64_t off, uintptr_t src, uint64_t len, uint32_t imm) {
+    return self_mgr().put_with_imm(GlobalAddress(static_cast<uint16_t>(node), region, off), reinterpret_cast<const void*>(src), len, imm,
+                                   dmem_stream());
+  });
+  m.def("take_immediates", [] {
+    // immediates that peers posted into this rank's rings (symmetric-heap fabric) join the local queue first
+    if (gd().symm)
+      for (auto& r : gd().symm->collect_imm()) self_mgr().push_immediate(r);
+    if (gd().shm)
+      for (auto& r : gd().shm->collect_imm()) self_mgr().push_immediate(r);
+    py::list out;
+    for (auto& r : self_mgr().take_immediates()) out.append(py::make_tuple(r.src_node, r.region_id, r.offset, r.length, r.imm));
+    return out;
+  }, "List of (source node, region, offset, length, immediate) delivered to this node since the last call.");
+  m.def("dmem_fence", [] { self_mgr().fence(dmem_stream()); },
+        "Orders every copy issued so far before later work on the current stream.");
   m.def("poll_completion", [](uint64_t wr) { return self_mgr().poll_completion(wr); });
   m.def("drain_pending", [] { return self_mgr().drain_pending(); });
   m.def("device_sync", [] {
@@ -436,6 +493,7 @@ void bind_runtime(py::module_& m) {
   m.attr("REGION_WRITABLE") = static_cast<uint32_t>(REGION_WRITABLE);
   m.attr("REGION_SHARED") = static_cast<uint32_t>(REGION_SHARED);
   m.attr("REGION_PRIVATE") = static_cast<uint32_t>(REGION_PRIVATE);
+  m.attr("REGION_DEVICE") = static_cast<uint32_t>(REGION_DEVICE);
   m.def("global_address_wire", [](int node, uint32_t region, uint64_t off) {
     uint8_t buf[GlobalAddress::kWireBytes];
     GlobalAddress g(static_cast<uint16_t>(node), region, off);

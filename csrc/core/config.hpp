@@ -96,7 +96,8 @@ struct EnvConfig {
   std::vector<std::string> iface_priority;  // IPv4 prefixes, empty = accept all
   std::string socket_ifname;                // restrict to one interface name
   int64_t arena_bytes = 0;                  // symmetric staging arena per rank
-  int64_t device_timeout_ms = 0;            // bound of every device-side wait
+  int64_t device_timeout_ms = 0;            // bound of every device-side wait; 0 = derive from the group's timeout
+  int64_t device_timeout_cap_ms = 0;        // upper bound of the derived value
   int nvls = -1;                            // -1 auto, 0 off, 1 required
   bool blocking_wait = false;               // Work::wait blocks the host
   bool debug_bounds = false;                // kernels check peer pointers
@@ -111,7 +112,11 @@ struct EnvConfig {
     c.iface_priority = env::csv("MCCL_IFACE_PRIORITY");
     c.socket_ifname = env::str("MCCL_SOCKET_IFNAME");
     c.arena_bytes = env::i64("MCCL_ARENA_MB", 512) << 20;
-    c.device_timeout_ms = env::i64("MCCL_DEVICE_TIMEOUT_MS", 10000);
+    // Unset: the device limit follows the timeout the process group was created with (capped by
+    // MCCL_DEVICE_TIMEOUT_CAP_MS, five minutes by default), so ordinary rank skew - a checkpoint or an
+    // evaluation on one rank, a data stall - does not end a collective that c10d would still wait for.
+    c.device_timeout_ms = env::i64("MCCL_DEVICE_TIMEOUT_MS", 0);
+    c.device_timeout_cap_ms = env::i64("MCCL_DEVICE_TIMEOUT_CAP_MS", 300000);
     std::string n = env::str("MCCL_NVLS", "auto");
     c.nvls = (n == "auto" || n.empty()) ? -1 : (env::flag("MCCL_NVLS", true) ? 1 : 0);
     c.blocking_wait = env::flag("MCCL_BLOCKING_WAIT", false);

@@ -35,6 +35,18 @@ __global__ void coherence_acquire_kernel(const unsigned int* my_flags, int world
   }
 }
 
+// The record's payload first, then its sequence number with a system-scope release: a receiver that
+// sees the number also sees the payload and the data the stream copied before this kernel.
+__global__ void dmem_post_imm_kernel(ImmWire* slot, ImmWire rec) {
+  slot->imm = rec.imm;
+  slot->region_id = rec.region_id;
+  slot->src_node = rec.src_node;
+  slot->offset = rec.offset;
+  slot->length = rec.length;
+  __threadfence_system();
+  dmem::signal(&slot->seq, rec.seq);
+}
+
 __global__ void dmem_atomic_selftest_kernel(unsigned int* remote_counter, unsigned long long* remote_slot, float* remote_sum,
                                             int adds) {
   for (int i = threadIdx.x; i < adds; i += blockDim.x) {
@@ -54,6 +66,11 @@ cudaError_t launch_dmem_copy(void* dst, const void* src, size_t n, cudaStream_t 
   size_t want = (n + (64u << 10) - 1) / (64u << 10);
   int ctas = static_cast<int>(want < 1 ? 1 : (want > 64 ? 64 : want));
   dmem_copy_kernel<<<ctas, 512, 0, stream>>>(static_cast<char*>(dst), static_cast<const char*>(src), n);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_dmem_post_imm(ImmWire* slot, const ImmWire& rec, cudaStream_t stream) {
+  dmem_post_imm_kernel<<<1, 1, 0, stream>>>(slot, rec);
   return cudaGetLastError();
 }
 

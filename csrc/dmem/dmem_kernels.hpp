@@ -5,7 +5,21 @@
 
 #include <cstddef>
 
+#include <cstdint>
+
 namespace mccl {
+
+// One immediate as it sits in a receiver's ring (32 bytes; seq is written last, with release semantics).
+struct ImmWire {
+  uint32_t seq;
+  uint32_t imm;
+  uint32_t region_id;
+  uint32_t src_node;
+  uint64_t offset;
+  uint64_t length;
+};
+// Writes `rec` into `slot` (a ring entry in a peer's symmetric memory) after everything the stream did before.
+cudaError_t launch_dmem_post_imm(ImmWire* slot, const ImmWire& rec, cudaStream_t stream);
 
 // SM-driven copy of n bytes; either pointer may be a peer mapping.
 cudaError_t launch_dmem_copy(void* dst, const void* src, size_t n, cudaStream_t stream);

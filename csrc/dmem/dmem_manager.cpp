@@ -186,18 +186,20 @@ uint64_t DistributedMemoryManager::put_with_imm(const GlobalAddress& dst, const 
                                                 void* stream) {
   uint64_t wr = put(dst, src, len, stream);
   if (!wr) return 0;
-  // The immediate must not overtake the data: wait for the copy when it is asynchronous.
-  if (!poll_completion(wr)) {
-    std::lock_guard<std::mutex> g(mu_);
-    ++stats_.total_errors;
-    return 0;
-  }
   ImmRecord r;
   r.src_node = node_id_;
   r.region_id = dst.region_id;
   r.offset = dst.offset;
   r.length = len;
   r.imm = imm;
+  // The immediate must not overtake the data.  A fabric that can post it on the stream that carried
+  // the copy keeps the order on the device; otherwise wait for the copy here first.
+  if (dst.node_id != node_id_ && fabric_->deliver_imm_stream(dst.node_id, r, stream)) return wr;
+  if (!poll_completion(wr)) {
+    std::lock_guard<std::mutex> g(mu_);
+    ++stats_.total_errors;
+    return 0;
+  }
   if (dst.node_id == node_id_) push_immediate(r);
   else fabric_->deliver_imm(dst.node_id, r);
   return wr;

@@ -53,6 +53,10 @@ class DmemFabric {
   // Pointer through which `me` can reach `remote_addr` of `node` (nullptr when it cannot).
   virtual void* map(uint16_t me, uint16_t node, const RegionDirectoryEntry& e, uint64_t remote_addr) = 0;
   virtual void deliver_imm(uint16_t node, const ImmRecord& r) = 0;
+  // Stream-ordered delivery: the immediate becomes visible after everything `stream` did before.
+  // Returns false when the fabric cannot do that (the caller then waits for the data on the host
+  // and uses deliver_imm).
+  virtual bool deliver_imm_stream(uint16_t, const ImmRecord&, void* /*stream*/) { return false; }
 };
 
 struct DmemStats {

@@ -38,6 +38,14 @@ struct A2AArgs {
   unsigned long long slot_bytes;                     // arena bytes reserved per destination
 };
 
+// Point-to-point transfer: one entry per virtual rank of the launch.
+struct P2PArgs {
+  void* buf[kArgRanks];              // send source or receive destination
+  int peer[kArgRanks];               // -1: this virtual rank takes no part
+  int is_send[kArgRanks];
+  unsigned long long nbytes;
+};
+
 // Chunk length in elements: ceil(numel / world) rounded up to 16 elements so
 // that every chunk starts on a 16-byte boundary for every element size.
 inline long long chunk_elems(long long numel, int world) {

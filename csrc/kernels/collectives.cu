@@ -130,7 +130,7 @@ __global__ void __launch_bounds__(kThreads) twoshot_kernel(DevComm c, CollArgs a
     }
   }
   if (barrier_all(c, vr, rank, s, PH_PUSH)) {
-    cta_end(c, vr, s);
+    cta_end(c, vr, s, TL_ALLREDUCE);
     return;
   }
 
@@ -168,11 +168,11 @@ __global__ void __launch_bounds__(kThreads) twoshot_kernel(DevComm c, CollArgs a
     }
   }
   if constexpr (kScatter) {
-    cta_end(c, vr, s);
+    cta_end(c, vr, s, TL_ALLREDUCE);
     return;
   } else {
     if (barrier_all(c, vr, rank, s, PH_REDUCE)) {
-      cta_end(c, vr, s);
+      cta_end(c, vr, s, TL_ALLREDUCE);
       return;
     }
     // Phase 3: pull every other rank's reduced chunk.  All loads of a batch are
@@ -213,7 +213,7 @@ __global__ void __launch_bounds__(kThreads) twoshot_kernel(DevComm c, CollArgs a
     if (N <= 2) pull(std::integral_constant<int, 8>{}, std::integral_constant<int, 1>{});
     else if (N <= 4) pull(std::integral_constant<int, 3>{}, std::integral_constant<int, 3>{});
     else pull(std::integral_constant<int, 1>{}, std::integral_constant<int, kMaxRanks - 1>{});
-    cta_end(c, vr, s);
+    cta_end(c, vr, s, TL_ALLREDUCE);
   }
 }
 
@@ -256,7 +256,7 @@ __global__ void __launch_bounds__(kThreads) oneshot_kernel(DevComm c, CollArgs a
     }
   }
   if (barrier_all(c, vr, rank, s, PH_PUSH)) {
-    cta_end(c, vr, s);
+    cta_end(c, vr, s, TL_ALLREDUCE);
     return;
   }
   // Phase 2: reduce the N slots in rank order.
@@ -289,7 +289,7 @@ __global__ void __launch_bounds__(kThreads) oneshot_kernel(DevComm c, CollArgs a
     }
     store_pack<T, E, Acc>(out + e0, acc, nv, al_out);
   }
-  cta_end(c, vr, s);
+  cta_end(c, vr, s, TL_ALLREDUCE);
 }
 
 // =================================================================== ring ==
@@ -338,7 +338,7 @@ __global__ void __launch_bounds__(kThreads) ring_kernel(DevComm c, CollArgs a) {
   }
   s.epoch = e0v + 2 * (N - 1);
   if (failed) {
-    cta_end(c, vr, s);
+    cta_end(c, vr, s, TL_ALLREDUCE);
     return;
   }
   // Finish the chunk this rank owns and start the allgather with it.
@@ -374,7 +374,7 @@ __global__ void __launch_bounds__(kThreads) ring_kernel(DevComm c, CollArgs a) {
       if (nv > 0) store_pack<T, E, Acc>(out + el, v, nv, aligned16(out + el));
     }
   }
-  cta_end(c, vr, s);
+  cta_end(c, vr, s, TL_ALLREDUCE);
 }
 
 // =================================================================== tree ==
@@ -442,7 +442,7 @@ __global__ void __launch_bounds__(kThreads) tree_kernel(DevComm c, CollArgs a) {
     }
   }
   if (failed) {
-    cta_end(c, vr, s);
+    cta_end(c, vr, s, TL_ALLREDUCE);
     return;
   }
   // Binomial broadcast from rank 0.
@@ -466,7 +466,7 @@ __global__ void __launch_bounds__(kThreads) tree_kernel(DevComm c, CollArgs a) {
     while (!(rank & low)) low <<= 1;  // lowest set bit: parent = rank - low
     failed = wait_one(c, vr, rank, rank - low, e0v + R + 1, PH_TREE);
     if (failed) {
-      cta_end(c, vr, s);
+      cta_end(c, vr, s, TL_ALLREDUCE);
       return;
     }
     for (long long i = pb + threadIdx.x; i < pe; i += blockDim.x) {
@@ -485,7 +485,7 @@ __global__ void __launch_bounds__(kThreads) tree_kernel(DevComm c, CollArgs a) {
           *reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(bbuf(rank)) + static_cast<size_t>(i) * 16);
     signal_one(c, rank, child, e0v + R + 1, s);
   }
-  cta_end(c, vr, s);
+  cta_end(c, vr, s, TL_ALLREDUCE);
 }
 
 // =================================================================== NVLS ==
@@ -565,7 +565,7 @@ __global__ void __launch_bounds__(kThreads) nvls_kernel(DevComm c, CollArgs a, c
     stage_mc = result_mc = mc_sym;
   }
   if (barrier_all(c, 0, rank, s, PH_NVLS)) {
-    cta_end(c, 0, s);
+    cta_end(c, 0, s, TL_ALLREDUCE);
     return;
   }
   // Phase 1: reduce chunk `rank` in the switch and broadcast it back.
@@ -592,7 +592,7 @@ __global__ void __launch_bounds__(kThreads) nvls_kernel(DevComm c, CollArgs a, c
     }
   }
   if (barrier_all(c, 0, rank, s, PH_NVLS)) {
-    cta_end(c, 0, s);
+    cta_end(c, 0, s, TL_ALLREDUCE);
     return;
   }
   if constexpr (kStage) {
@@ -610,7 +610,7 @@ __global__ void __launch_bounds__(kThreads) nvls_kernel(DevComm c, CollArgs a, c
       }
     }
   }
-  cta_end(c, 0, s);
+  cta_end(c, 0, s, TL_ALLREDUCE);
 }
 
 // ====================================================== symmetric in-place ==
@@ -678,7 +678,7 @@ __global__ void __launch_bounds__(kThreads) symm_allreduce_kernel(DevComm c, Col
     }
     barrier_all(c, vr, rank, s, PH_GATHER);
   }
-  cta_end(c, vr, s);
+  cta_end(c, vr, s, TL_ALLREDUCE);
 }
 
 // ============================================================== allgather ==
@@ -779,6 +779,79 @@ __global__ void __launch_bounds__(kThreads) alltoall_kernel(DevComm c, A2AArgs a
   cta_end(c, vr, s);
 }
 
+// ============================================================= send / recv ==
+// One launch moves one message between a pair of ranks: blockIdx.y selects the virtual rank
+// (single-GPU emulation runs a sender and a receiver as one cooperative launch), each CTA moves
+// its own byte range of every chunk and talks only to the CTA of the same index on the other side.
+__global__ void __launch_bounds__(kThreads) p2p_kernel(P2PComm c, P2PArgs a) {
+  const int vr = blockIdx.y, rank = c.rank_base + vr, peer = a.peer[vr];
+  if (peer < 0) return;
+  const bool sending = a.is_send[vr] != 0;
+  P2PState* st = c.state[vr];
+  const uint32_t base = sending ? st->send_seq[peer] : st->recv_seq[peer];
+  const unsigned long long slot = c.slot_bytes;
+  const unsigned long long chunks = (a.nbytes + slot - 1) / slot;
+  char* user = static_cast<char*>(a.buf[vr]);
+  bool failed = false;
+  auto wait_flag = [&](const uint32_t* flag, uint32_t value, int phase) -> bool {
+    bool bad = false;
+    if (threadIdx.x == 0) {
+      const unsigned long long t0 = globaltimer_ns();
+      unsigned spins = 0;
+      for (;;) {
+        if (static_cast<int32_t>(ld_acquire_sys(flag) - value) >= 0) break;
+        if ((++spins & 63u) == 0 && globaltimer_ns() - t0 > c.timeout_ns) {
+          volatile int* sw = c.status[vr];
+          if (*sw == 0) *sw = encode_status(phase, peer);
+          __threadfence_system();
+          bad = true;
+          break;
+        }
+      }
+    }
+    return __syncthreads_or(bad ? 1 : 0) != 0;
+  };
+  for (unsigned long long k = 0; k < chunks && !failed; ++k) {
+    const uint32_t seq = base + static_cast<uint32_t>(k) + 1u;
+    const unsigned long long off = k * slot;
+    const unsigned long long len = a.nbytes - off < slot ? a.nbytes - off : slot;
+    unsigned long long b0, b1;
+    cta_byte_span(len, b0, b1);
+    if (sending) {
+      // buffer seq & 1 last held chunk seq - 2: the receiver must have copied that one out
+      failed = wait_flag(c.free_[rank] + blockIdx.x * kMaxRanks + peer, seq - 2u, PH_SEND);
+      if (failed) break;
+      char* dst = c.region[peer] + (static_cast<size_t>(rank) * 2 + (seq & 1u)) * slot;
+      cta_copy_bytes(dst + b0, user + off + b0, b1 - b0);
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        __threadfence_system();
+        st_release_sys(c.ready[peer] + blockIdx.x * kMaxRanks + rank, seq);
+      }
+    } else {
+      failed = wait_flag(c.ready[rank] + blockIdx.x * kMaxRanks + peer, seq, PH_RECV);
+      if (failed) break;
+      const char* src = c.region[rank] + (static_cast<size_t>(peer) * 2 + (seq & 1u)) * slot;
+      cta_copy_bytes(user + off + b0, src + b0, b1 - b0);
+      __syncthreads();
+      if (threadIdx.x == 0) st_release_sys(c.free_[peer] + blockIdx.x * kMaxRanks + rank, seq);
+    }
+  }
+  // The last CTA to finish advances the pair's sequence number (also after a timeout, so that both
+  // sides keep counting the same messages).
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    uint32_t* done = sending ? &st->send_done[peer] : &st->recv_done[peer];
+    __threadfence();
+    if (atomicAdd(done, 1u) + 1u == gridDim.x) {
+      *done = 0;
+      if (sending) st->send_seq[peer] = base + static_cast<uint32_t>(chunks);
+      else st->recv_seq[peer] = base + static_cast<uint32_t>(chunks);
+      __threadfence();
+    }
+  }
+}
+
 // ================================================================ barrier ==
 __global__ void __launch_bounds__(32) barrier_kernel(DevComm c) {
   const int vr = blockIdx.y, rank = c.rank_base + vr;
@@ -792,15 +865,19 @@ namespace {
 
 template <typename... KArgs, typename... Args>
 cudaError_t launch(void (*kernel)(KArgs...), const LaunchCfg& cfg, int threads, Args... args) {
-  // Threads per CTA: MCCL_COMM_THREADS (128..512), 256 by default.  A 256-thread collective CTA needs half
-  // a register file, so it shares an SM with a persistent GEMM CTA instead of holding the SM alone while it
-  // waits for its peers; measured on the data-parallel step, that is worth 0.15-0.3 ms of 8.4.
+  // Threads per CTA: cfg.threads when the caller chose (128..512), else MCCL_COMM_THREADS, else 256.  A
+  // 256-thread collective CTA needs half a register file, so it can share an SM with a persistent GEMM CTA; a
+  // 512-thread CTA needs a whole one and therefore only lands on an SM no GEMM CTA occupies, which is what a
+  // trainer wants when it keeps a few SMs free of GEMM work for the gradient collectives.
   static const int env_threads = [] {
     const char* v = std::getenv("MCCL_COMM_THREADS");
     const int t = v && *v ? std::atoi(v) : 256;
     return t >= 128 && t <= kThreads ? (t / 32) * 32 : 256;
   }();
-  if (env_threads > 0 && threads == kThreads) threads = env_threads;
+  if (threads == kThreads) {
+    const int want = cfg.threads > 0 ? cfg.threads : env_threads;
+    threads = want >= 128 && want <= kThreads ? (want / 32) * 32 : 256;
+  }
   dim3 grid(cfg.ctas, cfg.nlocal > 1 ? cfg.nlocal : 1);
   if (cfg.nlocal > 1) {
     void* params[] = {static_cast<void*>(&args)...};
@@ -890,6 +967,9 @@ cudaError_t launch_broadcast(const DevComm& c, const CollArgs& a, const LaunchCf
 }
 cudaError_t launch_alltoall(const DevComm& c, const A2AArgs& a, const LaunchCfg& cfg) {
   return launch(alltoall_kernel, cfg, kThreads, c, a);
+}
+cudaError_t launch_p2p(const P2PComm& c, const P2PArgs& a, const LaunchCfg& cfg) {
+  return launch(p2p_kernel, cfg, kThreads, c, a);
 }
 cudaError_t launch_barrier(const DevComm& c, const LaunchCfg& cfg) {
   LaunchCfg one = cfg;

@@ -12,11 +12,13 @@ namespace mccl {
 namespace dev {
 
 struct DevComm;  // comm_device.cuh
+struct P2PComm;  // comm_device.cuh
 
 enum class ElemType : int { F32 = 0, F16, BF16, F64, I32, I64 };
 
 struct LaunchCfg {
   int ctas = 1;
+  int threads = 0;   // threads per CTA; 0 = default (MCCL_COMM_THREADS or 256)
   int nlocal = 1;
   cudaStream_t stream = nullptr;
 };
@@ -38,6 +40,8 @@ cudaError_t launch_allgather(const DevComm& c, const CollArgs& a, const LaunchCf
 cudaError_t launch_broadcast(const DevComm& c, const CollArgs& a, const LaunchCfg& cfg);   // a.numel = bytes, a.out = data
 cudaError_t launch_alltoall(const DevComm& c, const A2AArgs& a, const LaunchCfg& cfg);
 cudaError_t launch_barrier(const DevComm& c, const LaunchCfg& cfg);
+// One message between pairs of ranks (send / recv); cfg.ctas must agree on both sides of a pair.
+cudaError_t launch_p2p(const P2PComm& c, const P2PArgs& a, const LaunchCfg& cfg);
 
 // Element-wise kernels (standalone forms of what the collectives fuse).
 // op is dev::Op; n elements; pointers may have any alignment.

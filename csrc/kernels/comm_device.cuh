@@ -20,6 +20,7 @@
 
 #include <cstdint>
 
+#include "../core/timeline.hpp"
 #include "coll_args.hpp"
 
 namespace mccl {
@@ -50,9 +51,36 @@ struct DevComm {
   int* status[kMaxRanks];        // indexed by virtual rank; 0 = healthy
   unsigned long long half_bytes; // size of one arena half
   unsigned long long timeout_ns;
+  TimelineBuf* tl;               // device timeline, or nullptr (off)
 };
 
-enum Phase : int { PH_BARRIER = 1, PH_PUSH = 2, PH_REDUCE = 3, PH_GATHER = 4, PH_RING = 5, PH_TREE = 6, PH_NVLS = 7 };
+// ---- point-to-point (send / recv) ----
+// Every rank owns an inbound region in peer-mapped memory with two buffers of slot_bytes per source
+// rank.  The sender writes chunk number `seq` of the pair's stream into buffer seq & 1 of the
+// receiver's region and raises ready[cta][src] = seq on the receiver's pad; the receiver copies the
+// chunk out and raises free[cta][dst] = seq on the sender's pad, which lets chunk seq + 2 be written.
+// Sequence numbers live in device memory per (rank, peer, direction), so the n-th send to a peer
+// pairs with the n-th receive from it and the kernels can be replayed from a CUDA graph.
+struct P2PState {
+  uint32_t send_seq[kMaxRanks];
+  uint32_t recv_seq[kMaxRanks];
+  uint32_t send_done[kMaxRanks];   // CTAs of the running send kernel that have finished, per peer
+  uint32_t recv_done[kMaxRanks];
+};
+struct P2PComm {
+  int world;
+  int rank_base;
+  char* region[kMaxRanks];       // rank r's inbound region as mapped here: [src][2][slot_bytes]
+  uint32_t* ready[kMaxRanks];    // rank r's pad, "chunk written" flags: [cta][src]
+  uint32_t* free_[kMaxRanks];    // rank r's pad, "chunk consumed" flags: [cta][dst]
+  P2PState* state[kMaxRanks];    // indexed by virtual rank
+  int* status[kMaxRanks];        // indexed by virtual rank
+  unsigned long long slot_bytes;
+  unsigned long long timeout_ns;
+};
+constexpr int kP2PMaxCtas = 16;
+
+enum Phase : int { PH_BARRIER = 1, PH_PUSH = 2, PH_REDUCE = 3, PH_GATHER = 4, PH_RING = 5, PH_TREE = 6, PH_NVLS = 7, PH_SEND = 8, PH_RECV = 9 };
 
 __host__ __device__ inline int encode_status(int phase, int peer) { return (1 << 30) | (phase << 8) | (peer & 0xff); }
 
@@ -81,6 +109,7 @@ struct CtaSync {
   uint32_t epoch;
   uint32_t half;   // which arena half this launch uses
   bool skip;       // host-made fault: do not signal
+  unsigned long long tl_t0;  // timeline entry stamp (0: this CTA does not record)
 };
 
 // Called by every thread at kernel start.
@@ -90,15 +119,17 @@ __device__ __forceinline__ CtaSync cta_begin(const DevComm& c, int vr) {
   s.epoch = st->epoch[blockIdx.x];
   s.half = st->seq & 1u;
   s.skip = st->skip_signals != 0;
+  s.tl_t0 = tl_begin(c.tl);
   return s;
 }
 
 // Called by every thread at kernel end (also on the failure path).  The last
 // CTA to finish advances the sequence number, which flips the arena half for
 // the next launch; all CTAs of this launch have read it by then.
-__device__ __forceinline__ void cta_end(const DevComm& c, int vr, const CtaSync& s) {
+__device__ __forceinline__ void cta_end(const DevComm& c, int vr, const CtaSync& s, uint32_t tl_kind = TL_OTHER_COLL) {
   __syncthreads();
   if (threadIdx.x == 0) {
+    tl_end(c.tl, s.tl_t0, tl_kind, gridDim.x);
     RankState* st = c.state[vr];
     st->epoch[blockIdx.x] = s.epoch;
     __threadfence();

@@ -280,10 +280,10 @@ cudaError_t colsum_bf16(const __nv_bfloat16* in, float* out, float* scratch, int
 }
 
 // ------------------------------------------------------------------ AdamW --
-__global__ void __launch_bounds__(256) adamw_kernel(float* __restrict__ p, const float* __restrict__ g, float* __restrict__ m,
+__global__ void __launch_bounds__(256) adamw_kernel(float* __restrict__ p, float* __restrict__ g, float* __restrict__ m,
                                                     float* __restrict__ v, __nv_bfloat16* __restrict__ p16, long long n4, long long n,
                                                     float lr, float b1, float b2, float eps, float wd,
-                                                    const float* __restrict__ step_ptr, float gscale) {
+                                                    const float* __restrict__ step_ptr, float gscale, int zero_grad) {
   const float step = *step_ptr;
   const float bc1 = 1.f - powf(b1, step), bc2 = 1.f - powf(b2, step);
   const float inv_bc1 = 1.f / bc1, inv_sqrt_bc2 = rsqrtf(bc2), decay = 1.f - lr * wd;
@@ -303,6 +303,7 @@ __global__ void __launch_bounds__(256) adamw_kernel(float* __restrict__ p, const
     reinterpret_cast<float4*>(p)[i] = pp;
     reinterpret_cast<float4*>(m)[i] = mm;
     reinterpret_cast<float4*>(v)[i] = vv;
+    if (zero_grad) reinterpret_cast<float4*>(g)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
     if (p16) {
       __nv_bfloat162 lo = __floats2bfloat162_rn(pp.x, pp.y), hi = __floats2bfloat162_rn(pp.z, pp.w);
       uint2 packed;
@@ -320,13 +321,14 @@ __global__ void __launch_bounds__(256) adamw_kernel(float* __restrict__ p, const
       v[i] = vk;
       const float pk = p[i] * decay - lr * (mk * inv_bc1) / (sqrtf(vk) * inv_sqrt_bc2 + eps);
       p[i] = pk;
+      if (zero_grad) g[i] = 0.f;
       if (p16) p16[i] = __float2bfloat16_rn(pk);
     }
   }
 }
 
-cudaError_t adamw_flat(float* p, const float* g, float* m, float* v, __nv_bfloat16* p16, long long n, float lr, float beta1,
-                       float beta2, float eps, float wd, const float* step, float grad_scale, cudaStream_t stream) {
+cudaError_t adamw_flat(float* p, float* g, float* m, float* v, __nv_bfloat16* p16, long long n, float lr, float beta1,
+                       float beta2, float eps, float wd, const float* step, float grad_scale, cudaStream_t stream, bool zero_grad) {
   if (n <= 0) return cudaSuccess;
   if ((reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(m) |
        reinterpret_cast<uintptr_t>(v)) & 15u)
@@ -335,7 +337,8 @@ cudaError_t adamw_flat(float* p, const float* g, float* m, float* v, __nv_bfloat
   long long blocks = (n4 + 255) / 256;
   if (blocks > 148 * 8) blocks = 148 * 8;
   if (blocks < 1) blocks = 1;
-  adamw_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(p, g, m, v, p16, n4, n, lr, beta1, beta2, eps, wd, step, grad_scale);
+  adamw_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(p, g, m, v, p16, n4, n, lr, beta1, beta2, eps, wd, step, grad_scale,
+                                                             zero_grad ? 1 : 0);
   count_launch();
   return cudaGetLastError();
 }

@@ -6,6 +6,7 @@
 #include "ops.hpp"
 #include "tcgen05.cuh"
 
+#include "../core/timeline.hpp"
 #include "../symm/cu_driver.hpp"
 
 namespace mccl {
@@ -27,6 +28,7 @@ struct GemmDev {
   int epilogue;
   int atomic_add;  // fp32 output accumulated with red.global.add (split-K partial sums)
   int* err;  // device word set non-zero when a pipeline wait runs out
+  TimelineBuf* tl;  // device timeline, or nullptr (off)
 };
 
 // Device address of the error word (one per process and device context).

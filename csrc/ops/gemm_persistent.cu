@@ -379,6 +379,7 @@ __global__ void __launch_bounds__(192, 1) gemm_persistent_kernel(const __grid_co
   uint64_t* sched_empty = sched_full + 4;
   volatile int* sched_tile = reinterpret_cast<volatile int*>(sched_empty + 4);
 
+  const unsigned long long tl_t0 = tl_begin(g.tl);
   const uint32_t epoch = f.mode != FUSE_NONE ? *f.epoch_ptr : 0u;
   if (f.mode != FUSE_NONE && static_cast<int>(blockIdx.x) < f.copy_ctas) {
     // these CTAs move data; the others compute
@@ -607,6 +608,7 @@ __global__ void __launch_bounds__(192, 1) gemm_persistent_kernel(const __grid_co
     tc::fence_after_sync();
     tc::tmem_dealloc(tmem_base, 2 * BN);
   }
+  tl_end(g.tl, tl_t0, TL_GEMM, (static_cast<uint32_t>(m_tiles) << 16) | static_cast<uint32_t>(n_tiles * splits));
   if (f.sched_counter != nullptr && threadIdx.x == 0) {
     // the CTA that leaves last rewinds the counters for the next launch that uses this slot
     __threadfence();
@@ -619,6 +621,9 @@ __global__ void __launch_bounds__(192, 1) gemm_persistent_kernel(const __grid_co
   if (f.mode == FUSE_REDUCE_SCATTER_D && *abort_flag == 0)
     reduce_scatter_role(f, g, epoch, smem, reinterpret_cast<ReduceShared*>(smem + L::kTiles + L::kGemmBarriers));
 }
+
+// Process-wide cap on the CTAs of plain GEMM launches (0 = one per SM); see set_gemm_cta_limit().
+std::atomic<int> g_gemm_cta_limit{0};
 
 // Counter pairs {next tile, CTAs that have left} of the tile scheduler, one array per device.
 constexpr unsigned int kSchedSlots = 1024;
@@ -699,6 +704,7 @@ cudaError_t launch_persistent_cfg(const GemmArgs& a, const FusedDev& f_in, int m
   g.atomic_add = 0;
   g.err = gemm_error_device_ptr();
   if (!g.err) return cudaErrorNotSupported;
+  g.tl = timeline_device_ptr();
   int tiles = ((a.m + BM - 1) / BM) * ((a.n + BN - 1) / BN);
   f.k_splits = 1;
   static const bool allow_split = [] {
@@ -735,6 +741,7 @@ no_split:
     }
   }
   int ctas = sm_count();
+  if (max_ctas <= 0) max_ctas = g_gemm_cta_limit.load(std::memory_order_relaxed);
   if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
   // fused roles wait on one another inside the kernel: every CTA must be resident (one per SM)
   int gemm_ctas = ctas - f.copy_ctas;
@@ -746,6 +753,10 @@ no_split:
 }
 
 }  // namespace
+
+void set_gemm_cta_limit(int ctas) { g_gemm_cta_limit.store(ctas > 0 ? ctas : 0, std::memory_order_relaxed); }
+int gemm_cta_limit() { return g_gemm_cta_limit.load(std::memory_order_relaxed); }
+int gemm_sm_count() { return sm_count(); }
 
 cudaError_t launch_bump_epoch(uint32_t* epoch, uint32_t* zeroed, cudaStream_t stream) {
   bump_epoch_kernel<<<1, 1, 0, stream>>>(epoch, zeroed);

@@ -191,6 +191,7 @@ cudaError_t launch_cfg(const GemmArgs& a, cudaStream_t stream) {
   g.atomic_add = 0;
   g.err = gemm_error_device_ptr();
   if (!g.err) return unsupported("no device error word");
+  g.tl = nullptr;
   dim3 grid((a.n + BN - 1) / BN, (a.m + BM - 1) / BM);
   gemm_bf16_kernel<BN, STAGES, kAMn, kBMn><<<grid, 192, L::kTotal, stream>>>(ma, mb, g);
   count_launch();

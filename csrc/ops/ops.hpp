@@ -37,9 +37,11 @@ cudaError_t colsum_bf16(const __nv_bfloat16* in, float* out, float* scratch, int
 int colsum_slabs(int rows);
 
 // ---- fused AdamW over flat fp32 buffers; step is a device scalar (float) so the
-// launch can be replayed from a CUDA graph.  p16 (optional) receives bf16(p).
-cudaError_t adamw_flat(float* p, const float* g, float* m, float* v, __nv_bfloat16* p16, long long n, float lr, float beta1,
-                       float beta2, float eps, float wd, const float* step, float grad_scale, cudaStream_t stream);
+// launch can be replayed from a CUDA graph.  p16 (optional) receives bf16(p).  With zero_grad the gradient
+// is cleared in the same pass (it has just been read), which replaces the memset at the start of the next step.
+cudaError_t adamw_flat(float* p, float* g, float* m, float* v, __nv_bfloat16* p16, long long n, float lr, float beta1,
+                       float beta2, float eps, float wd, const float* step, float grad_scale, cudaStream_t stream,
+                       bool zero_grad = false);
 
 // ---- softmax cross entropy, forward and backward in one pass over the logits:
 // loss_rows[t] = logsumexp(logits[t]) - logits[t, target[t]];
@@ -87,6 +89,12 @@ struct GemmArgs {
 // Returns cudaErrorNotSupported for shapes the kernel does not cover
 // (K % 64 != 0, N % 8 != 0, unaligned pointers); the caller falls back.
 cudaError_t gemm_bf16_tn(const GemmArgs& args, cudaStream_t stream);
+// Caps the number of CTAs (= SMs) plain GEMM launches occupy from now on; 0 restores one CTA per SM.  A
+// data-parallel trainer lowers it during backward so that a few SMs stay free for the gradient collectives
+// that run beside the GEMMs.  The value is read at launch time, so it is baked into a captured CUDA graph.
+void set_gemm_cta_limit(int ctas);
+int gemm_cta_limit();
+int gemm_sm_count();
 // Why the last gemm_bf16_tn call on this thread returned cudaErrorNotSupported ("" otherwise).
 const char* gemm_last_reason();
 // Non-zero when a pipeline wait inside a GEMM kernel ran out (kernel returned early).

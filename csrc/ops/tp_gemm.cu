@@ -50,7 +50,7 @@ int env_int(const char* name, int def, int lo, int hi) {
 void fill_common(FusedDev& f, DeviceComm& comm, const SymmAlloc& sig, int* status_dev) {
   f.world = comm.world();
   f.rank = comm.rank();
-  f.timeout_ns = 10ull * 1000 * 1000 * 1000;
+  f.timeout_ns = static_cast<unsigned long long>(comm.device_timeout_ms()) * 1000000ull;   // same bound as the collectives
   f.status = status_dev;
   for (int r = 0; r < f.world; ++r) f.sig[r] = static_cast<uint32_t*>(sig.ptrs[r]);
 }

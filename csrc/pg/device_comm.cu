@@ -4,9 +4,11 @@
 
 #include <algorithm>
 #include <cstring>
+#include <mutex>
 
 #include "../core/errors.hpp"
 #include "../core/log.hpp"
+#include "../core/timeline.hpp"
 #include "../kernels/collectives.hpp"
 #include "../kernels/comm_device.cuh"
 #include "../symm/cu_driver.hpp"
@@ -63,13 +65,53 @@ const char* phase_name(int ph) {
 struct DeviceComm::Impl {
   std::shared_ptr<SymmAlloc> arena;  // two halves, multicast-bound when possible
   std::shared_ptr<SymmAlloc> pads;   // kChannels signal pads
+  std::shared_ptr<SymmAlloc> p2p;    // inbound send/recv slots: [source][2][p2p_slot]
+  size_t p2p_slot = 0;
+  dev::P2PState* p2p_state = nullptr;  // device: [nlocal]
   dev::RankState* state = nullptr;   // device: [nlocal][kChannels]
   int* status_host = nullptr;        // pinned, mapped: [kMaxRanks]
   int* status_dev = nullptr;
   size_t half_bytes = 0;
   unsigned long long timeout_ns = 0;
   int max_ctas = 64;
+  int threads = 0;         // threads per collective CTA, 0 = kernel default
   int64_t nvls_above = 0;  // AUTO uses staged NVLS at or above this many wire bytes (0 = never)
+  // Launch ordering across streams: the arena halves, flags and epochs are shared by every launch of this
+  // communicator, so two collectives must never overlap on the device.  Each launch records `last_done` on its
+  // stream; a launch on another stream first waits for it.  (Skipped while a stream is being captured: a graph
+  // orders its own nodes and must not depend on events outside the capture.)
+  cudaEvent_t last_done = nullptr;
+  cudaStream_t last_stream = nullptr;
+  bool have_last = false;
+  std::mutex order_mu;
+
+  static bool capturing(cudaStream_t s) {
+    cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(s, &st) != cudaSuccess) {
+      (void)cudaGetLastError();
+      return false;
+    }
+    return st != cudaStreamCaptureStatusNone;
+  }
+  void order_before(cudaStream_t s) {
+    std::lock_guard<std::mutex> g(order_mu);
+    if (!have_last || s == last_stream || capturing(s)) return;
+    cudaStreamWaitEvent(s, last_done, 0);
+  }
+  void order_after(cudaStream_t s) {
+    std::lock_guard<std::mutex> g(order_mu);
+    if (capturing(s)) return;
+    if (!last_done) cudaEventCreateWithFlags(&last_done, cudaEventDisableTiming);
+    cudaEventRecord(last_done, s);
+    last_stream = s;
+    have_last = true;
+  }
+  struct Ordered {   // scope of one public collective call
+    Impl* impl;
+    cudaStream_t s;
+    Ordered(Impl* i, void* stream) : impl(i), s(static_cast<cudaStream_t>(stream)) { impl->order_before(s); }
+    ~Ordered() { impl->order_after(s); }
+  };
 
   dev::DevComm ctx(int world, int rank_base, int nlocal, int channel) const {
     dev::DevComm c{};
@@ -86,13 +128,14 @@ struct DeviceComm::Impl {
     }
     c.half_bytes = half_bytes;
     c.timeout_ns = timeout_ns;
+    c.tl = timeline_device_ptr();
     return c;
   }
 };
 
 DeviceComm::DeviceComm(KVStore* store, int rank, int world, int device, const std::string& prefix, const EnvConfig& cfg,
                        int64_t timeout_ms)
-    : rank_(rank), world_(world), device_(device), nlocal_(1), cfg_(cfg) {
+    : rank_(rank), world_(world), device_(device), nlocal_(1), cfg_(cfg), group_timeout_ms_(timeout_ms) {
   mesh_.reset(new SymmMesh(store, rank, world, device, prefix, cfg, timeout_ms));
   init_common();
 }
@@ -110,13 +153,23 @@ void DeviceComm::init_common() {
   impl_->arena = mesh_->alloc(arena, /*want_multicast=*/true);
   impl_->half_bytes = (impl_->arena->bytes / 2) / 256 * 256;
   impl_->pads = mesh_->alloc(static_cast<size_t>(dev::kChannels) * dev::kFlagWordsPerChannel * sizeof(uint32_t), false);
+  impl_->p2p_slot = static_cast<size_t>(std::max<int64_t>(env::i64("MCCL_P2P_SLOT_MB", 4), 1)) << 20;
+  if (nlocal_ > 1) impl_->p2p_slot = std::min<size_t>(impl_->p2p_slot, 1u << 20);
+  impl_->p2p = mesh_->alloc(impl_->p2p_slot * 2 * static_cast<size_t>(world_), /*want_multicast=*/false);
+  MCCL_CUDA_CHECK(cudaMalloc(&impl_->p2p_state, sizeof(dev::P2PState) * nlocal_));
+  MCCL_CUDA_CHECK(cudaMemset(impl_->p2p_state, 0, sizeof(dev::P2PState) * nlocal_));
   MCCL_CUDA_CHECK(cudaMalloc(&impl_->state, sizeof(dev::RankState) * dev::kChannels * nlocal_));
   MCCL_CUDA_CHECK(cudaMemset(impl_->state, 0, sizeof(dev::RankState) * dev::kChannels * nlocal_));
   MCCL_CUDA_CHECK(cudaHostAlloc(&impl_->status_host, sizeof(int) * dev::kMaxRanks, cudaHostAllocMapped));
   std::memset(impl_->status_host, 0, sizeof(int) * dev::kMaxRanks);
   MCCL_CUDA_CHECK(cudaHostGetDevicePointer(&impl_->status_dev, impl_->status_host, 0));
   MCCL_CUDA_CHECK(cudaDeviceSynchronize());
-  impl_->timeout_ns = static_cast<unsigned long long>(std::max<int64_t>(cfg_.device_timeout_ms, 1)) * 1000000ull;
+  {
+    // explicit MCCL_DEVICE_TIMEOUT_MS wins; otherwise the group's own timeout, capped; 10 s without a group
+    int64_t ms = cfg_.device_timeout_ms;
+    if (ms <= 0) ms = group_timeout_ms_ > 0 ? std::min<int64_t>(group_timeout_ms_, std::max<int64_t>(cfg_.device_timeout_cap_ms, 1000)) : 10000;
+    impl_->timeout_ns = static_cast<unsigned long long>(std::max<int64_t>(ms, 1)) * 1000000ull;
+  }
   int cap = cfg_.max_ctas > 0 ? cfg_.max_ctas : 64;   // 64 CTAs of 256 threads
   impl_->max_ctas = std::min(cap, dev::kMaxCtas);
   impl_->nvls_above = env::i64("MCCL_NVLS_ABOVE", 0);
@@ -126,7 +179,9 @@ void DeviceComm::init_common() {
 
 DeviceComm::~DeviceComm() {
   if (impl_) {
+    if (impl_->last_done) cudaEventDestroy(impl_->last_done);
     if (impl_->state) cudaFree(impl_->state);
+    if (impl_->p2p_state) cudaFree(impl_->p2p_state);
     if (impl_->status_host) cudaFreeHost(impl_->status_host);
   }
 }
@@ -168,6 +223,19 @@ void DeviceComm::set_device_timeout_ms(int64_t ms) {
   impl_->timeout_ns = static_cast<unsigned long long>(std::max<int64_t>(ms, 1)) * 1000000ull;
 }
 
+int64_t DeviceComm::device_timeout_ms() const { return static_cast<int64_t>(impl_->timeout_ns / 1000000ull); }
+
+void DeviceComm::set_launch_shape(int max_ctas, int threads) {
+  if (max_ctas > 0) {
+    impl_->max_ctas = std::min(max_ctas, dev::kMaxCtas);
+    if (nlocal_ > 1) impl_->max_ctas = std::max(1, std::min(impl_->max_ctas, 96 / nlocal_));
+  }
+  if (threads > 0) impl_->threads = std::max(128, std::min(threads, dev::kThreads)) / 32 * 32;
+  if (threads < 0) impl_->threads = 0;   // back to the kernels' default
+}
+int DeviceComm::launch_threads() const { return impl_->threads; }
+int DeviceComm::max_ctas() const { return impl_->max_ctas; }
+
 std::shared_ptr<SymmAlloc> DeviceComm::symm_alloc(size_t bytes) { return mesh_->alloc(bytes, true); }
 
 // ------------------------------------------------------------------ helpers --
@@ -204,6 +272,7 @@ Algo DeviceComm::allreduce(const void* const* ins, void* const* outs, size_t num
                            WireDtype wire, int64_t tree_below, void* stream) {
   MCCL_CHECK(world_ >= 2, "device allreduce needs at least two ranks");
   if (numel == 0) return Algo::ONESHOT;
+  Impl::Ordered ordered(impl_.get(), stream);
   const dev::ElemType et = to_elem(t);
   const bool bw = wire == WireDtype::BF16 && t == DType::F32;
   const size_t es = dtype_size(t), wes = bw ? 2 : es;
@@ -244,6 +313,7 @@ Algo DeviceComm::allreduce(const void* const* ins, void* const* outs, size_t num
     a.inv_world = 1.0f / static_cast<float>(world_);
     dev::LaunchCfg cfg;
     cfg.nlocal = nlocal_;
+    cfg.threads = impl_->threads;
     cfg.stream = st;
     const bool whole = algo == Algo::ONESHOT || algo == Algo::TREE;  // these split the whole message over CTAs
     cfg.ctas = ctas_for(static_cast<size_t>(n) * wes / (whole ? 1 : world_), impl_->max_ctas);
@@ -265,6 +335,7 @@ Algo DeviceComm::allreduce(const void* const* ins, void* const* outs, size_t num
 Algo DeviceComm::allreduce_symm(const SymmAlloc& buf, size_t byte_offset, size_t numel, DType t, RedOp op, void* stream) {
   MCCL_CHECK(world_ >= 2, "device allreduce needs at least two ranks");
   MCCL_CHECK(op == RedOp::SUM || op == RedOp::AVG || buf.mc_ptr == nullptr, "in-switch reduction supports SUM and AVG");
+  Impl::Ordered ordered(impl_.get(), stream);
   const size_t es = dtype_size(t);
   const long long per = dev::chunk_elems(static_cast<long long>(numel), world_);
   MCCL_CHECK(byte_offset % 16 == 0, "symmetric allreduce: offset must be a multiple of 16 bytes");
@@ -277,6 +348,7 @@ Algo DeviceComm::allreduce_symm(const SymmAlloc& buf, size_t byte_offset, size_t
   a.inv_world = 1.0f / static_cast<float>(world_);
   dev::LaunchCfg cfg;
   cfg.nlocal = nlocal_;
+    cfg.threads = impl_->threads;
   cfg.stream = static_cast<cudaStream_t>(stream);
   cfg.ctas = ctas_for(static_cast<size_t>(per) * es, impl_->max_ctas);
   dev::DevComm c = impl_->ctx(world_, rank_, nlocal_, 1);
@@ -299,6 +371,7 @@ void DeviceComm::reduce_scatter(const void* const* ins, void* const* outs, size_
                                 WireDtype wire, void* stream) {
   MCCL_CHECK(world_ >= 2, "device reduce_scatter needs at least two ranks");
   if (numel == 0) return;
+  Impl::Ordered ordered(impl_.get(), stream);
   const dev::ElemType et = to_elem(t);
   const bool bw = wire == WireDtype::BF16 && t == DType::F32;
   const size_t es = dtype_size(t), wes = bw ? 2 : es;
@@ -322,6 +395,7 @@ void DeviceComm::reduce_scatter(const void* const* ins, void* const* outs, size_
     a.inv_world = 1.0f / static_cast<float>(world_);
     dev::LaunchCfg cfg;
     cfg.nlocal = nlocal_;
+    cfg.threads = impl_->threads;
     cfg.stream = static_cast<cudaStream_t>(stream);
     cfg.ctas = ctas_for(static_cast<size_t>(n) * wes, impl_->max_ctas);
     dev::DevComm c = impl_->ctx(world_, rank_, nlocal_, 0);
@@ -334,6 +408,7 @@ void DeviceComm::reduce_scatter(const void* const* ins, void* const* outs, size_
 void DeviceComm::allgather(const void* const* ins, void* const* outs, size_t nbytes, void* stream) {
   MCCL_CHECK(world_ >= 2, "device allgather needs at least two ranks");
   if (nbytes == 0) return;
+  Impl::Ordered ordered(impl_.get(), stream);
   const size_t half = impl_->half_bytes;
   const size_t piece = std::min(nbytes, half / 16 * 16);
   for (size_t done = 0; done < nbytes; done += piece) {
@@ -349,6 +424,7 @@ void DeviceComm::allgather(const void* const* ins, void* const* outs, size_t nby
     a.stride = static_cast<long long>(nbytes);  // distance between ranks' blocks in the output
     dev::LaunchCfg cfg;
     cfg.nlocal = nlocal_;
+    cfg.threads = impl_->threads;
     cfg.stream = static_cast<cudaStream_t>(stream);
     cfg.ctas = ctas_for(n, impl_->max_ctas);
     dev::DevComm c = impl_->ctx(world_, rank_, nlocal_, 0);
@@ -361,6 +437,7 @@ void DeviceComm::allgather(const void* const* ins, void* const* outs, size_t nby
 void DeviceComm::broadcast(void* const* datas, size_t nbytes, int root, void* stream) {
   MCCL_CHECK(world_ >= 2, "device broadcast needs at least two ranks");
   if (nbytes == 0) return;
+  Impl::Ordered ordered(impl_.get(), stream);
   const size_t half = impl_->half_bytes;
   // each launch scatters a piece into world slices of at most `half` bytes
   const size_t piece = std::min(nbytes, (half / 16 * 16) * static_cast<size_t>(world_) / 2);
@@ -372,6 +449,7 @@ void DeviceComm::broadcast(void* const* datas, size_t nbytes, int root, void* st
     a.root = root;
     dev::LaunchCfg cfg;
     cfg.nlocal = nlocal_;
+    cfg.threads = impl_->threads;
     cfg.stream = static_cast<cudaStream_t>(stream);
     cfg.ctas = ctas_for(n / world_, impl_->max_ctas);
     dev::DevComm c = impl_->ctx(world_, rank_, nlocal_, 0);
@@ -386,6 +464,7 @@ void DeviceComm::alltoallv(const void* const* ins, void* const* outs, const std:
                            const std::vector<std::vector<size_t>>& out_off,
                            const std::vector<std::vector<size_t>>& out_len, void* stream) {
   MCCL_CHECK(world_ >= 2, "device alltoall needs at least two ranks");
+  Impl::Ordered ordered(impl_.get(), stream);
   const size_t slot = (impl_->half_bytes / static_cast<size_t>(world_)) / 16 * 16;
   size_t longest = 0;
   for (int v = 0; v < nlocal_; ++v)
@@ -408,6 +487,7 @@ void DeviceComm::alltoallv(const void* const* ins, void* const* outs, const std:
   a.slot_bytes = slot;
   dev::LaunchCfg cfg;
   cfg.nlocal = nlocal_;
+    cfg.threads = impl_->threads;
   cfg.stream = static_cast<cudaStream_t>(stream);
   cfg.ctas = ctas_for(longest, impl_->max_ctas);
   // The CTA count must agree across ranks although segment sizes differ, so it
@@ -419,10 +499,71 @@ void DeviceComm::alltoallv(const void* const* ins, void* const* outs, const std:
   ++launches_;
 }
 
-void DeviceComm::barrier(void* stream) {
-  if (world_ < 2) return;
+// ---------------------------------------------------------------- send/recv --
+namespace {
+int p2p_ctas(size_t nbytes, size_t slot) {
+  // both sides derive the same count from the message size alone
+  const size_t per_chunk = std::min(nbytes, slot);
+  const size_t want = (per_chunk + (256u << 10) - 1) / (256u << 10);
+  return static_cast<int>(std::max<size_t>(1, std::min<size_t>(want, dev::kP2PMaxCtas)));
+}
+}  // namespace
+
+size_t DeviceComm::p2p_slot_bytes() const { return impl_->p2p_slot; }
+
+void DeviceComm::p2p_emulated(const std::vector<P2POp>& ops, size_t nbytes, void* stream) {
+  MCCL_CHECK(static_cast<int>(ops.size()) == nlocal_, "p2p: expected one entry per local rank");
+  if (nbytes == 0) return;
+  dev::P2PComm c{};
+  c.world = world_;
+  c.rank_base = rank_;
+  for (int r = 0; r < world_; ++r) {
+    c.region[r] = static_cast<char*>(impl_->p2p->ptrs[r]);
+    c.ready[r] = static_cast<uint32_t*>(impl_->pads->ptrs[r]) + 2 * static_cast<size_t>(dev::kFlagWordsPerChannel);
+    c.free_[r] = static_cast<uint32_t*>(impl_->pads->ptrs[r]) + 3 * static_cast<size_t>(dev::kFlagWordsPerChannel);
+  }
+  for (int v = 0; v < nlocal_; ++v) {
+    c.state[v] = impl_->p2p_state + v;
+    c.status[v] = impl_->status_dev + v;
+  }
+  c.slot_bytes = impl_->p2p_slot;
+  c.timeout_ns = impl_->timeout_ns;
+  dev::P2PArgs a{};
+  for (int v = 0; v < dev::kArgRanks; ++v) a.peer[v] = -1;
+  for (int v = 0; v < nlocal_; ++v) {
+    if (ops[v].peer < 0) continue;
+    const int me = rank_ + v;
+    MCCL_CHECK(ops[v].peer < world_ && ops[v].peer != me, "p2p: bad peer rank " << ops[v].peer);
+    a.buf[v] = ops[v].buf;
+    a.peer[v] = ops[v].peer;
+    a.is_send[v] = ops[v].is_send ? 1 : 0;
+  }
+  a.nbytes = nbytes;
   dev::LaunchCfg cfg;
   cfg.nlocal = nlocal_;
+  cfg.threads = 256;
+  cfg.stream = static_cast<cudaStream_t>(stream);
+  cfg.ctas = p2p_ctas(nbytes, impl_->p2p_slot);
+  cudaError_t rc = dev::launch_p2p(c, a, cfg);
+  MCCL_CHECK_T(rc == cudaSuccess, CudaError, "send/recv launch failed: " << cudaGetErrorString(rc));
+  ++launches_;
+}
+
+void DeviceComm::send(const void* data, size_t nbytes, int peer, void* stream) {
+  MCCL_CHECK(nlocal_ == 1, "send: use p2p_emulated with virtual ranks");
+  p2p_emulated({P2POp{const_cast<void*>(data), peer, true}}, nbytes, stream);
+}
+void DeviceComm::recv(void* data, size_t nbytes, int peer, void* stream) {
+  MCCL_CHECK(nlocal_ == 1, "recv: use p2p_emulated with virtual ranks");
+  p2p_emulated({P2POp{data, peer, false}}, nbytes, stream);
+}
+
+void DeviceComm::barrier(void* stream) {
+  if (world_ < 2) return;
+  Impl::Ordered ordered(impl_.get(), stream);
+  dev::LaunchCfg cfg;
+  cfg.nlocal = nlocal_;
+    cfg.threads = impl_->threads;
   cfg.stream = static_cast<cudaStream_t>(stream);
   dev::DevComm c = impl_->ctx(world_, rank_, nlocal_, 0);
   cudaError_t rc = dev::launch_barrier(c, cfg);

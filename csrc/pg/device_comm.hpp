@@ -12,6 +12,15 @@
 // names are the same (ring / tree / butterfly), but the data moves by loads
 // and stores to peer GPUs' memory issued from inside the kernels.
 //
+// One collective at a time: all launches of a communicator share its arena
+// halves, flags and epochs, so they are ordered on the device.  Launches on
+// the same stream are ordered by the stream; a launch on a different stream
+// than the previous one first waits for an event recorded after that one.
+// Inside a CUDA graph capture the caller's capture dependencies must provide
+// the order (fork the comm stream from, and join it back into, the capturing
+// stream), and a captured graph must not run concurrently with eager
+// collectives of the same communicator.
+//
 // A communicator built with the single-process constructor carries `world`
 // virtual ranks on one GPU; its methods then take one pointer per virtual
 // rank and run all ranks as one cooperative launch.  The kernel tests use
@@ -77,6 +86,23 @@ class DeviceComm {
                  const std::vector<std::vector<size_t>>& out_len, void* stream);
   void barrier(void* stream);
 
+  // Point-to-point: the n-th send to a peer pairs with the n-th recv from it on the other side (tags are
+  // not matched, as with NCCL).  The data travels through a two-buffer slot per (receiver, source) in
+  // peer-mapped memory, so a message of up to two slots (MCCL_P2P_SLOT_MB each, 4 MiB by default) is
+  // sent without the receiver having arrived; longer ones are streamed as the receiver drains them.
+  // These launches use flags and memory of their own and are not ordered against the collectives, so a
+  // process group may run sends, receives and collectives on three different streams.
+  void send(const void* data, size_t nbytes, int peer, void* stream);
+  void recv(void* data, size_t nbytes, int peer, void* stream);
+  // Single-GPU emulation: ops[v] = {buffer, peer or -1, is_send} for virtual rank v, one cooperative launch.
+  struct P2POp {
+    void* buf = nullptr;
+    int peer = -1;
+    bool is_send = false;
+  };
+  void p2p_emulated(const std::vector<P2POp>& ops, size_t nbytes, void* stream);
+  size_t p2p_slot_bytes() const;
+
   // Single-pointer conveniences for the one-process-per-GPU case.
   Algo allreduce(const void* in, void* out, size_t numel, DType t, RedOp op, Algo requested, WireDtype wire,
                  int64_t tree_below, void* stream) {
@@ -113,6 +139,13 @@ class DeviceComm {
   void inject_skip_signals(int count);
   // Overrides the bound of every device-side wait (milliseconds).
   void set_device_timeout_ms(int64_t ms);
+  int64_t device_timeout_ms() const;
+  // Geometry of the collective kernels launched from now on: at most `max_ctas` CTAs of `threads` threads
+  // (0 keeps the current value, threads < 0 restores the default).  512-thread CTAs need a whole register file and so only run on SMs that
+  // hold no persistent GEMM CTA; a trainer that leaves k SMs free of GEMM work asks for (k, 512).
+  void set_launch_shape(int max_ctas, int threads);
+  int max_ctas() const;
+  int launch_threads() const;   // 0 = kernel default
 
   SymmMesh& mesh() { return *mesh_; }
   uint64_t launches() const { return launches_; }
@@ -125,6 +158,7 @@ class DeviceComm {
   std::unique_ptr<SymmMesh> mesh_;
   std::unique_ptr<Impl> impl_;
   uint64_t launches_ = 0;
+  int64_t group_timeout_ms_ = 0;
 };
 
 }  // namespace mccl

@@ -6,7 +6,10 @@
 #include <c10/cuda/CUDAStream.h>
 #include <cuda_runtime_api.h>
 
+#include <condition_variable>
+#include <deque>
 #include <map>
+#include <thread>
 
 #include "../core/errors.hpp"
 #include "../core/log.hpp"
@@ -88,9 +91,19 @@ bool device_reducible(at::ScalarType t) {
 
 class EventCompletion : public StreamCompletion {
  public:
-  EventCompletion(std::shared_ptr<DeviceComm> dev, c10::DeviceIndex idx, bool host_sync_on_wait)
-      : dev_(std::move(dev)), idx_(idx), host_sync_(host_sync_on_wait) {}
+  EventCompletion(std::shared_ptr<DeviceComm> dev, c10::DeviceIndex idx, bool host_sync_on_wait, bool timed)
+      : ev_(timed ? cudaEventDefault : cudaEventDisableTiming), start_(timed ? cudaEventDefault : cudaEventDisableTiming),
+        dev_(std::move(dev)), idx_(idx), host_sync_(host_sync_on_wait), timed_(timed) {}
+  void record_start(const c10::cuda::CUDAStream& s) {
+    if (timed_) start_.record(s);
+  }
   void record(const c10::cuda::CUDAStream& s) { ev_.record(s); }
+  // Device time between the two events in milliseconds (only after query() returned true); < 0 when untimed.
+  double device_ms() {
+    if (!timed_) return -1.0;
+    return static_cast<double>(start_.elapsed_time(ev_));
+  }
+  int device_status() { return dev_ ? dev_->status() : 0; }
   bool query() override { return ev_.query(); }
   void block_current_stream() override {
     ev_.block(c10::cuda::getCurrentCUDAStream(idx_));
@@ -122,17 +135,30 @@ class EventCompletion : public StreamCompletion {
     return st != cudaStreamCaptureStatusNone;
   }
   at::cuda::CUDAEvent ev_;
+  at::cuda::CUDAEvent start_;
   std::shared_ptr<DeviceComm> dev_;
   c10::DeviceIndex idx_;
   bool host_sync_;
+  bool timed_;
 };
+
+bool stream_capturing(const c10::cuda::CUDAStream& s) {
+  cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(s.stream(), &st) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return false;
+  }
+  return st != cudaStreamCaptureStatusNone;
+}
 
 std::mutex g_stream_mu;
 std::map<std::pair<const void*, int>, c10::cuda::CUDAStream> g_comm_streams;
 
-c10::cuda::CUDAStream comm_stream_for(const void* pg, c10::DeviceIndex idx) {
+// lane 0: collectives; lane 1: sends; lane 2: receives (a rank's send and receive of one exchange must be
+// able to run at the same time, and neither may queue behind a collective that waits for other ranks).
+c10::cuda::CUDAStream comm_stream_for(const void* pg, c10::DeviceIndex idx, int lane = 0) {
   std::lock_guard<std::mutex> g(g_stream_mu);
-  auto key = std::make_pair(pg, static_cast<int>(idx));
+  auto key = std::make_pair(pg, static_cast<int>(idx) * 4 + lane);
   auto it = g_comm_streams.find(key);
   if (it == g_comm_streams.end())
     it = g_comm_streams.emplace(key, c10::cuda::getStreamFromPool(/*isHighPriority=*/true, idx)).first;
@@ -141,12 +167,132 @@ c10::cuda::CUDAStream comm_stream_for(const void* pg, c10::DeviceIndex idx) {
 
 }  // namespace
 
+// ------------------------------------------------------- completion thread --
+// Follows every CUDA collective that was enqueued outside a graph capture: when its end event
+// has fired it stores the device time (CUDA event pair) in the metrics record, and when the
+// pinned status word says that a bounded device wait ran out it fails THAT Work with a
+// TimeoutError, the counterpart of the reference's finishWithException on its progress thread
+// (csrc/backend/ProcessGroupMCCL.cpp:60-68).
+class StreamWatcher {
+ public:
+  struct Item {
+    c10::intrusive_ptr<WorkMCCL> work;
+    std::shared_ptr<EventCompletion> done;
+    uint64_t metric_seq = 0;
+  };
+  StreamWatcher() : thread_([this] { run(); }) {}
+  ~StreamWatcher() { stop(); }
+  void watch(Item item) {
+    {
+      std::lock_guard<std::mutex> g(mu_);
+      if (stopping_) {
+        Metrics::global().op_end(item.metric_seq, false);
+        return;
+      }
+      q_.push_back(std::move(item));
+    }
+    cv_.notify_one();
+  }
+  // Returns once every watched op has been seen to finish (or `ms` passed).
+  void drain(int64_t ms) {
+    auto deadline = std::chrono::steady_clock::now() + std::chrono::milliseconds(ms);
+    std::unique_lock<std::mutex> g(mu_);
+    idle_cv_.wait_until(g, deadline, [&] { return q_.empty() && !busy_; });
+  }
+  void stop() {
+    {
+      std::lock_guard<std::mutex> g(mu_);
+      if (stopping_) return;
+      stopping_ = true;
+    }
+    cv_.notify_all();
+    if (thread_.joinable()) thread_.join();
+  }
+  bool failed() const { return failed_.load(); }
+
+ private:
+  void run() {
+    for (;;) {
+      Item item;
+      {
+        std::unique_lock<std::mutex> g(mu_);
+        cv_.wait(g, [&] { return stopping_ || !q_.empty(); });
+        if (q_.empty()) return;   // stopping and nothing left
+        item = std::move(q_.front());
+        q_.pop_front();
+        busy_ = true;
+      }
+      finish(item);
+      {
+        std::lock_guard<std::mutex> g(mu_);
+        busy_ = false;
+      }
+      idle_cv_.notify_all();
+    }
+  }
+  void finish(Item& item) {
+    // After stop() the remaining ops get two seconds; a process that is going away must not hang here.
+    auto give_up = std::chrono::steady_clock::time_point::max();
+    bool done = false;
+    int spins = 0;
+    try {
+      for (;;) {
+        if (item.done->query()) {
+          done = true;
+          break;
+        }
+        bool stopping;
+        {
+          std::lock_guard<std::mutex> g(mu_);
+          stopping = stopping_;
+        }
+        if (stopping) {
+          if (give_up == std::chrono::steady_clock::time_point::max())
+            give_up = std::chrono::steady_clock::now() + std::chrono::seconds(2);
+          if (std::chrono::steady_clock::now() > give_up) break;
+        }
+        if (++spins < 200) std::this_thread::yield();
+        else std::this_thread::sleep_for(std::chrono::microseconds(50));
+      }
+      if (done) {
+        const double ms = item.done->device_ms();
+        if (ms >= 0) Metrics::global().record_phase(item.metric_seq, "device", ms);
+      }
+      bool bad = false;
+      if (done && item.done->device_status() != 0) {
+        try {
+          item.done->check_status();
+        } catch (...) {
+          bad = true;
+          failed_.store(true);
+          item.work->markStreamFailed(std::current_exception());
+        }
+      }
+      Metrics::global().op_end(item.metric_seq, bad);
+    } catch (...) {
+      // a CUDA error while querying (context torn down, sticky fault): the op cannot be vouched for
+      failed_.store(true);
+      item.work->markStreamFailed(std::current_exception());
+      Metrics::global().op_end(item.metric_seq, true);
+    }
+  }
+
+  std::mutex mu_;
+  std::condition_variable cv_, idle_cv_;
+  std::deque<Item> q_;
+  bool stopping_ = false, busy_ = false;
+  std::atomic<bool> failed_{false};
+  std::thread thread_;
+};
+
 // ------------------------------------------------------------- construction --
 ProcessGroupMCCL::ProcessGroupMCCL(const c10::intrusive_ptr<c10d::Store>& store, int rank, int size,
                                    std::chrono::milliseconds timeout)
     : c10d::Backend(rank, size), store_(store), kv_(new StoreAdapter(store)), cfg_(EnvConfig::from_env()),
       timeout_(timeout) {
   set_log_rank(rank);
+  device_metrics_ = env::flag("MCCL_DEVICE_METRICS", true);
+  use_nccl_p2p_ = env::str("MCCL_P2P") == "nccl";
   if (size > 1) {
     mesh_.reset(new TcpMesh(kv_.get(), rank, size, timeout.count(), "mccl", cfg_));
     engine_.reset(new Progress(static_cast<size_t>(cfg_.max_queue_depth)));
@@ -169,7 +315,17 @@ c10::intrusive_ptr<c10d::Backend> ProcessGroupMCCL::create(const c10::intrusive_
   return c10::make_intrusive<ProcessGroupMCCL>(store, rank, size, timeout);
 }
 
+StreamWatcher& ProcessGroupMCCL::watcher() {
+  std::lock_guard<std::mutex> g(watcher_mu_);
+  if (!watcher_) watcher_.reset(new StreamWatcher());
+  return *watcher_;
+}
+
 void ProcessGroupMCCL::shutdown() {
+  {
+    std::lock_guard<std::mutex> g(watcher_mu_);
+    if (watcher_) watcher_->stop();
+  }
   if (engine_) engine_->shutdown();
   if (mesh_) Metrics::global().record_transport_bytes(mesh_->bytes_sent(), mesh_->bytes_received());
 }
@@ -241,25 +397,30 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupMCCL::submitHost(c10d::OpType op, con
 c10::intrusive_ptr<c10d::Work> ProcessGroupMCCL::submitStream(
     c10d::OpType op, const char* title, uint64_t bytes, const std::string& algo, std::vector<at::Tensor> inputs,
     std::vector<at::Tensor> outputs, at::Device device,
-    const std::function<void(DeviceComm&, void*)>& launch) {
+    const std::function<void(DeviceComm&, void*)>& launch, int lane) {
   MCCL_CHECK(!aborted_, "process group was aborted");
   ++op_seq_;
   auto dev = deviceComm(device);
   if (dev->status() != 0) dev->check_status();
   c10::cuda::CUDAGuard guard(device);
   auto cur = c10::cuda::getCurrentCUDAStream(device.index());
-  auto comm = comm_stream_for(this, device.index());
+  auto comm = comm_stream_for(this, device.index(), lane);
   uint64_t mseq = Metrics::global().op_start(title, bytes, algo);
 
   at::cuda::CUDAEvent ready;
   ready.record(cur);
   ready.block(comm);
 
+  // Outside a graph capture the op is timed with an event pair and handed to the completion thread.
+  const bool watched = !stream_capturing(cur);
+  const bool timed = watched && device_metrics_;
   auto work = c10::make_intrusive<WorkMCCL>(getRank(), op, title, outputs);
+  std::shared_ptr<EventCompletion> done;
   {
     c10::cuda::CUDAStreamGuard sg(comm);
+    done = std::make_shared<EventCompletion>(dev, device.index(), op == c10d::OpType::BARRIER, timed);
+    done->record_start(comm);
     launch(*dev, static_cast<void*>(comm.stream()));
-    auto done = std::make_shared<EventCompletion>(dev, device.index(), op == c10d::OpType::BARRIER);
     done->record(comm);
     work->attachStream(done, cfg_.blocking_wait);
   }
@@ -267,21 +428,28 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupMCCL::submitStream(
     if (t.defined() && t.device().is_cuda()) c10::cuda::CUDACachingAllocator::recordStream(t.storage().data_ptr(), comm);
   for (auto& t : outputs)
     if (t.defined() && t.device().is_cuda()) c10::cuda::CUDACachingAllocator::recordStream(t.storage().data_ptr(), comm);
-  Metrics::global().op_end(mseq, false);
+  if (watched) {
+    Metrics::global().op_execute_start(mseq);
+    watcher().watch({work, done, mseq});
+  } else {
+    Metrics::global().op_end(mseq, false);
+  }
   return work;
 }
 
 // ---------------------------------------------------------------- allreduce --
 c10::intrusive_ptr<c10d::Work> ProcessGroupMCCL::allreduce(std::vector<at::Tensor>& tensors,
                                                            const c10d::AllreduceOptions& opts) {
+  // Per-call knobs, read on the caller thread like the reference does.
+  return allreduceWith(tensors, to_redop(opts.reduceOp), requested_algo(), requested_wire());
+}
+
+c10::intrusive_ptr<c10d::Work> ProcessGroupMCCL::allreduceWith(std::vector<at::Tensor>& tensors, RedOp op, Algo req,
+                                                               WireDtype wire) {
   MCCL_CHECK_TENSOR(!tensors.empty(), "allreduce: empty tensor list");
   for (auto& t : tensors) check_tensor(t, "allreduce");
-  RedOp op = to_redop(opts.reduceOp);
   if (getSize() == 1) return WorkMCCL::completed(getRank(), c10d::OpType::ALLREDUCE, "mccl:allreduce", tensors);
 
-  // Per-call knobs, read on the caller thread like the reference does.
-  Algo req = requested_algo();
-  WireDtype wire = requested_wire();
   int64_t below = tensors[0].device().is_cuda() ? device_oneshot_below_bytes() : tree_below_bytes();
   uint64_t bytes = 0;
   for (auto& t : tensors) bytes += nbytes(t);
@@ -777,7 +945,12 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupMCCL::send(std::vector<at::Tensor>& t
   check_single(tensors, "send");
   MCCL_CHECK(dst >= 0 && dst < getSize() && dst != getRank(), "send: bad destination rank " << dst);
   at::Tensor t = tensors[0];
-  if (t.device().is_cuda()) return p2p()->send(tensors, dst, tag);
+  if (t.device().is_cuda()) {
+    if (use_nccl_p2p_) return p2p()->send(tensors, dst, tag);
+    if (t.numel() == 0) return WorkMCCL::completed(getRank(), c10d::OpType::SEND, "mccl:send", {});
+    return submitStream(c10d::OpType::SEND, "mccl:send", nbytes(t), "", {t}, {}, t.device(),
+                        [t, dst](DeviceComm& dev, void* stream) { dev.send(t.data_ptr(), nbytes(t), dst, stream); }, 1);
+  }
   return submitHost(c10d::OpType::SEND, "mccl:send", nbytes(t), {},
                     [this, t, dst, tag] { send_tagged(mesh(), dst, t.data_ptr(), nbytes(t), tag); });
 }
@@ -786,7 +959,12 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupMCCL::recv(std::vector<at::Tensor>& t
   check_single(tensors, "recv");
   MCCL_CHECK(src >= 0 && src < getSize() && src != getRank(), "recv: bad source rank " << src);
   at::Tensor t = tensors[0];
-  if (t.device().is_cuda()) return p2p()->recv(tensors, src, tag);
+  if (t.device().is_cuda()) {
+    if (use_nccl_p2p_) return p2p()->recv(tensors, src, tag);
+    if (t.numel() == 0) return WorkMCCL::completed(getRank(), c10d::OpType::RECV, "mccl:recv", {t});
+    return submitStream(c10d::OpType::RECV, "mccl:recv", nbytes(t), "", {}, {t}, t.device(),
+                        [t, src](DeviceComm& dev, void* stream) { dev.recv(t.data_ptr(), nbytes(t), src, stream); }, 2);
+  }
   return submitHost(c10d::OpType::RECV, "mccl:recv", nbytes(t), {t},
                     [this, t, src, tag] { recv_tagged(mesh(), src, t.data_ptr(), nbytes(t), tag); });
 }
@@ -794,8 +972,10 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupMCCL::recv(std::vector<at::Tensor>& t
 // ------------------------------------------------------------------ barrier --
 c10::intrusive_ptr<c10d::Work> ProcessGroupMCCL::barrier(const c10d::BarrierOptions& opts) {
   if (getSize() == 1) return WorkMCCL::completed(getRank(), c10d::OpType::BARRIER, "mccl:barrier", {});
-  // A group that has talked on a GPU (or is told which GPU to use) meets on
-  // the device; otherwise the ranks meet over the TCP mesh.
+  // The ranks always meet over the TCP mesh first and tell one another, in the token they exchange,
+  // whether they hold a device communicator (or were told which GPU to use).  Only when every rank
+  // does, the barrier kernel follows on the comm stream, so the path is chosen from group-wide state
+  // and two ranks can never wait for each other on different planes.
   std::shared_ptr<DeviceComm> dev;
   {
     std::lock_guard<std::mutex> g(dev_mu_);
@@ -805,17 +985,25 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupMCCL::barrier(const c10d::BarrierOpti
   if (dev) device = at::Device(at::kCUDA, static_cast<c10::DeviceIndex>(dev->device()));
   else if (opts.device.has_value() && opts.device->is_cuda()) device = opts.device;
   else if (!opts.device_ids.empty()) device = at::Device(at::kCUDA, static_cast<c10::DeviceIndex>(opts.device_ids[0]));
-  if (device.has_value()) {
-    return submitStream(c10d::OpType::BARRIER, "mccl:barrier", 0, "", {}, {}, *device,
-                        [](DeviceComm& d, void* stream) { d.barrier(stream); });
-  }
-  uint64_t seq = barrier_seq_++;
-  (void)seq;
-  return submitHost(c10d::OpType::BARRIER, "mccl:barrier", 0, {}, [this] {
-    uint8_t token = 1;
-    std::vector<uint8_t> all(static_cast<size_t>(getSize()));
-    mccl::allgather(mesh(), &token, all.data(), 1);
+  barrier_seq_++;
+  const uint8_t mine = device.has_value() ? 2 : 1;
+  auto tokens = std::make_shared<std::vector<uint8_t>>(static_cast<size_t>(getSize()), 0);
+  auto host = submitHost(c10d::OpType::BARRIER, "mccl:barrier", 0, {}, [this, tokens, mine] {
+    uint8_t token = mine;
+    mccl::allgather(mesh(), &token, tokens->data(), 1);
   });
+  if (!device.has_value()) return host;   // at least this rank has no GPU side: the host meeting is the barrier
+  host->wait();
+  bool all_device = true;
+  for (uint8_t t : *tokens) all_device = all_device && t == 2;
+  if (!all_device) {
+    // Some rank has no device side: keep the promise that this rank's GPU work is finished.
+    c10::cuda::CUDAGuard guard(*device);
+    cudaStreamSynchronize(c10::cuda::getCurrentCUDAStream(device->index()).stream());
+    return host;
+  }
+  return submitStream(c10d::OpType::BARRIER, "mccl:barrier", 0, "", {}, {}, *device,
+                      [](DeviceComm& d, void* stream) { d.barrier(stream); });
 }
 
 }  // namespace mccl

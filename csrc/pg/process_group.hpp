@@ -29,11 +29,13 @@
 #include "../engine/progress.hpp"
 #include "../net/kv_store.hpp"
 #include "../net/tcp_mesh.hpp"
+#include "dtypes.hpp"
 #include "work.hpp"
 
 namespace mccl {
 
-class DeviceComm;  // csrc/pg/device_comm.hpp
+class DeviceComm;     // csrc/pg/device_comm.hpp
+class StreamWatcher;  // completion thread for CUDA collectives (process_group.cpp)
 
 // c10d::Store seen through the transport-level KVStore interface.
 class StoreAdapter : public KVStore {
@@ -116,7 +118,11 @@ class ProcessGroupMCCL : public c10d::Backend {
   void eagerConnectSingleDevice(at::Device device) override;
 
   // ---- extras reachable from Python ----
-  // Supplies the lazily built NCCL group used for CUDA send/recv.
+  // allreduce with the algorithm and the wire dtype given as arguments instead of being read from
+  // MCCL_ALLREDUCE_ALGO / MCCL_WIRE_DTYPE (what a DDP communication hook needs: it runs on autograd's
+  // thread and must not edit the process environment around each bucket).
+  c10::intrusive_ptr<c10d::Work> allreduceWith(std::vector<at::Tensor>& tensors, RedOp op, Algo algo, WireDtype wire);
+  // Supplies the lazily built NCCL group used for CUDA send/recv when MCCL_P2P=nccl.
   void setP2PFactory(std::function<c10::intrusive_ptr<c10d::Backend>()> f) { p2p_factory_ = std::move(f); }
   // Device communicator of this group for `device` (built collectively on first use).
   std::shared_ptr<DeviceComm> deviceComm(at::Device device);
@@ -124,6 +130,12 @@ class ProcessGroupMCCL : public c10d::Backend {
   std::string lastAlgo() const;
   // Throws if a device-side wait of this group timed out.
   void checkDeviceStatus();
+  // Size of the symmetric staging arena this group's device communicator will allocate (before its first
+  // CUDA collective).  Sub-groups get a smaller arena than the world group: messages beyond it go in pieces.
+  void setArenaBytes(int64_t bytes) { cfg_.arena_bytes = bytes; }
+  // The group's key-value store and timeout (used by the distributed-memory fabric).
+  KVStore* kv() { return kv_.get(); }
+  int64_t timeoutMs() const { return timeout_.count(); }
 
  private:
   using Body = std::function<void()>;
@@ -132,9 +144,11 @@ class ProcessGroupMCCL : public c10d::Backend {
   c10::intrusive_ptr<c10d::Work> submitStream(c10d::OpType op, const char* title, uint64_t bytes,
                                               const std::string& algo, std::vector<at::Tensor> inputs,
                                               std::vector<at::Tensor> outputs, at::Device device,
-                                              const std::function<void(DeviceComm&, void* /*cudaStream_t*/)>& launch);
+                                              const std::function<void(DeviceComm&, void* /*cudaStream_t*/)>& launch,
+                                              int lane = 0);
   c10::intrusive_ptr<c10d::Backend> p2p();
   TcpMesh& mesh();
+  StreamWatcher& watcher();
 
   c10::intrusive_ptr<c10d::Store> store_;
   std::unique_ptr<StoreAdapter> kv_;
@@ -151,6 +165,10 @@ class ProcessGroupMCCL : public c10d::Backend {
   mutable std::mutex algo_mu_;
   std::string last_algo_;
   std::atomic<bool> aborted_{false};
+  std::mutex watcher_mu_;
+  std::shared_ptr<StreamWatcher> watcher_;
+  bool use_nccl_p2p_ = false;    // MCCL_P2P=nccl: CUDA send/recv through the NCCL comparison arm
+  bool device_metrics_ = true;   // MCCL_DEVICE_METRICS: time CUDA collectives with an event pair
 };
 
 }  // namespace mccl

@@ -40,7 +40,9 @@ bool WorkMCCL::isCompleted() {
 
 bool WorkMCCL::isSuccess() const {
   std::lock_guard<std::mutex> g(wmu_);
-  return done_ && !error_;
+  if (error_) return false;
+  if (stream_done_) return stream_done_->query();
+  return done_;
 }
 
 std::exception_ptr WorkMCCL::exception() const {
@@ -50,12 +52,19 @@ std::exception_ptr WorkMCCL::exception() const {
 
 bool WorkMCCL::wait(std::chrono::milliseconds timeout) {
   if (stream_done_) {
+    {
+      std::lock_guard<std::mutex> g(wmu_);
+      if (error_) std::rethrow_exception(error_);
+    }
     if (blocking_wait_) {
       bool ok = stream_done_->synchronize(timeout == kNoTimeout ? -1 : timeout.count());
       if (!ok) return false;
       stream_done_->check_status();
     } else {
       stream_done_->block_current_stream();
+      // Stream-ordered wait: the host does not block.  If the device has already finished this
+      // collective, a wait that ran out inside it is known now and is reported on this Work.
+      if (stream_done_->query()) stream_done_->check_status();
     }
     return true;
   }
@@ -96,6 +105,11 @@ void WorkMCCL::markFailed(std::exception_ptr e) {
   }
   wcv_.notify_all();
   if (!future_->completed()) future_->setError(e);
+}
+
+void WorkMCCL::markStreamFailed(std::exception_ptr e) {
+  std::lock_guard<std::mutex> g(wmu_);
+  if (!error_) error_ = e;
 }
 
 void WorkMCCL::attachStream(std::shared_ptr<StreamCompletion> sc, bool blocking_wait) {

@@ -55,6 +55,9 @@ class WorkMCCL : public c10d::Work {
   // Stream work: attaches the completion event and completes the Future.
   // Must be called with the comm stream set as the current stream.
   void attachStream(std::shared_ptr<StreamCompletion> sc, bool blocking_wait);
+  // Stream work: the completion thread found that the collective failed on the device (a bounded
+  // wait ran out).  wait(), isSuccess() and exception() report it from then on.
+  void markStreamFailed(std::exception_ptr e);
 
  private:
   std::vector<at::Tensor> outputs_;

@@ -11,10 +11,12 @@ import mccl_b200 as _impl
 from mccl_b200 import *  # noqa: F401,F403
 from mccl_b200 import _C, __version__, __protocol_version__  # noqa: F401
 
-for _name in ("_backend", "config", "tuning", "version", "metrics", "check", "cli", "distributed", "ddp", "tp", "pp"):
-    try:
-        sys.modules[__name__ + "." + _name] = importlib.import_module("mccl_b200." + _name)
-        globals()[_name] = sys.modules[__name__ + "." + _name]
-    except ImportError:
-        pass
+for _name in ("_backend", "config", "tuning", "version", "metrics", "check", "cli", "distributed", "parallel", "models",
+              "ops", "utils"):
+    sys.modules[__name__ + "." + _name] = importlib.import_module("mccl_b200." + _name)
+    globals()[_name] = sys.modules[__name__ + "." + _name]
+# short names for the parallelism modules
+for _name, _target in (("ddp", "parallel.ddp"), ("tp", "parallel.tp"), ("pp", "parallel.pp"), ("trainer", "parallel.trainer")):
+    sys.modules[__name__ + "." + _name] = importlib.import_module("mccl_b200." + _target)
+    globals()[_name] = sys.modules[__name__ + "." + _name]
 sys.modules[__name__ + "._C"] = _C

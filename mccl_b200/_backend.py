@@ -47,7 +47,18 @@ def _nccl_p2p_factory(store, rank: int, world_size: int, timeout: timedelta):
 
 def _create(store, rank: int, world_size: int, timeout: timedelta):
     from . import _C
-    pg = _C._create_process_group_mccl(store, rank, world_size, timeout)
+    # The first group of a process is the world group and gets the full staging arena (MCCL_ARENA_MB,
+    # 512 MB).  Groups made later with new_group() are sub-groups (tensor / pipeline / data-parallel
+    # dimensions): several of them coexist on a GPU, so each gets MCCL_SUBGROUP_ARENA_MB (128 MB) and
+    # larger messages are staged in pieces.
+    arena_mb = 0
+    try:
+        is_sub = dist.distributed_c10d._world.default_pg is not None
+    except Exception:  # private attribute moved: treat every group as a world group
+        is_sub = False
+    if is_sub:
+        arena_mb = int(os.environ.get("MCCL_SUBGROUP_ARENA_MB", "128"))
+    pg = _C._create_process_group_mccl(store, rank, world_size, timeout, arena_mb)
     pg.set_p2p_factory(_nccl_p2p_factory(store, rank, world_size, timeout))
     return pg
 

@@ -64,7 +64,7 @@ class DistributedRuntime:
             dist.barrier(group=self.group)
 
     def transfer_tensor(self, t: torch.Tensor, src: int, dst: int) -> Optional[torch.Tensor]:
-        """Point-to-point move of a tensor between two ranks (NCCL p2p for CUDA tensors)."""
+        """Point-to-point move of a tensor between two ranks (the backend's send / recv kernels for CUDA tensors)."""
         if self.rank == src:
             dist.send(t, dst, group=self.group)
             return None
@@ -76,20 +76,32 @@ class DistributedRuntime:
     def dispatch_pipeline(self, stage_fn: Callable[[torch.Tensor], torch.Tensor], micro_batches: Sequence[torch.Tensor],
                           act_shape, dtype, device) -> List[torch.Tensor]:
         """Runs `stage_fn` as stage `rank` of a `world`-stage pipeline (fill, steady, drain).  Stage 0
-        consumes `micro_batches`; the last stage returns its outputs; activations are received into
-        two alternating buffers so that a transfer can overlap the previous micro-batch's compute."""
-        n = len(micro_batches) if self.rank == 0 else int(act_shape[0] and len(micro_batches))
+        consumes `micro_batches`; the last stage returns its outputs.  Activations arrive in two
+        alternating buffers: the receive of micro-batch i + 1 is posted before micro-batch i is
+        computed, and sends are asynchronous, so transfers overlap the neighbouring compute."""
+        n = len(micro_batches)
         outs: List[torch.Tensor] = []
+        if n == 0:
+            return outs
         bufs = [torch.empty(act_shape, dtype=dtype, device=device) for _ in range(2)]
-        for mb in range(len(micro_batches)):
+        pending_recv = None
+        if self.rank > 0:
+            pending_recv = dist.irecv(bufs[0], self.rank - 1, group=self.group)
+        sends = []
+        for mb in range(n):
             if self.rank == 0:
                 x = micro_batches[mb]
             else:
+                pending_recv.wait()
                 x = bufs[mb & 1]
-                dist.recv(x, self.rank - 1, group=self.group)
+                if mb + 1 < n:   # the other buffer was consumed by micro-batch mb - 1, whose compute was enqueued before
+                    pending_recv = dist.irecv(bufs[(mb + 1) & 1], self.rank - 1, group=self.group)
             y = stage_fn(x)
             if self.rank < self.world - 1:
-                dist.send(y.contiguous(), self.rank + 1, group=self.group)
+                y = y.contiguous()
+                sends.append((dist.isend(y, self.rank + 1, group=self.group), y))
             else:
                 outs.append(y)
+        for work, _ in sends:
+            work.wait()
         return outs

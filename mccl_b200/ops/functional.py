@@ -74,11 +74,12 @@ def linear_cross_entropy(h: torch.Tensor, weight: torch.Tensor, targets: torch.T
     return F.cross_entropy(logits.float(), targets)
 
 
-def adamw_step(p, g, m, v, lr, beta1, beta2, eps, wd, step, p_bf16=None, grad_scale=1.0):
-    """In-place fused AdamW over flat fp32 tensors (optionally refreshing a bf16 copy of p)."""
+def adamw_step(p, g, m, v, lr, beta1, beta2, eps, wd, step, p_bf16=None, grad_scale=1.0, zero_grad=False):
+    """In-place fused AdamW over flat fp32 tensors (optionally refreshing a bf16 copy of p and clearing g)."""
     if p.is_cuda and _HAS["adamw_flat"]:
-        _C.adamw_flat(p, g, m, v, p_bf16, lr, beta1, beta2, eps, wd, step, grad_scale)
+        _C.adamw_flat(p, g, m, v, p_bf16, lr, beta1, beta2, eps, wd, step, grad_scale, zero_grad)
         return
+    g_buf = g
     g = g * grad_scale if grad_scale != 1.0 else g
     m.mul_(beta1).add_(g, alpha=1 - beta1)
     v.mul_(beta2).addcmul_(g, g, value=1 - beta2)
@@ -86,3 +87,5 @@ def adamw_step(p, g, m, v, lr, beta1, beta2, eps, wd, step, p_bf16=None, grad_sc
     p.mul_(1 - lr * wd).addcdiv_(m / bc1, (v / bc2).sqrt_().add_(eps), value=-lr)
     if p_bf16 is not None:
         p_bf16.copy_(p)
+    if zero_grad:
+        g_buf.zero_()

@@ -32,8 +32,15 @@ def wire_dtype(name: str):
 
 
 def bf16_wire_hook(group, bucket: dist.GradBucket) -> torch.futures.Future[torch.Tensor]:
-    """``model.register_comm_hook(group, bf16_wire_hook)``: averaged gradients, bf16 on the wire."""
+    """``model.register_comm_hook(group, bf16_wire_hook)``: averaged gradients, bf16 on the wire.
+
+    The wire dtype is an argument of the backend call, so nothing here touches ``os.environ`` (the hook
+    runs on autograd's thread while other threads may be issuing collectives of their own)."""
+    from .._backend import get_backend
     buf = bucket.buffer()
-    with wire_dtype("bf16" if buf.dtype == torch.float32 else ""):
+    be = get_backend(group)
+    if be is None:   # not an mccl group: plain averaged allreduce
         work = dist.all_reduce(buf, op=dist.ReduceOp.AVG, group=group, async_op=True)
+    else:
+        work = be.allreduce_with(buf, op="avg", wire="bf16" if buf.dtype == torch.float32 else "native")
     return work.get_future().then(lambda fut: fut.value()[0])

@@ -6,20 +6,27 @@ this backend too (see ``mccl_b200.parallel.ddp``).  This engine is the
 B200-first form of the same job:
 
 * all parameters live in one flat fp32 buffer and all gradients in one flat
-  fp32 buffer allocated from the group's symmetric heap, ordered so that the
-  gradients that finish first in backward sit in the first bucket;
+  fp32 buffer, ordered so that the gradients that finish first in backward sit
+  in the first bucket; the last bucket is kept small, because it is the one
+  whose collective cannot hide behind backward;
 * when the last gradient of a bucket has been accumulated, the bucket is
-  all-reduced in place on a side stream while backward continues: in-switch
-  (``multimem.ld_reduce``) when the fabric offers it, otherwise by direct peer
-  loads, or staged through the arena with bf16 on the wire and fp32
-  accumulation (``wire="bf16"``), with the 1/world scale fused in every case;
-* AdamW is one fused kernel over the flat buffers;
+  all-reduced in place on a side stream while backward continues: staged
+  through the arena with bf16 on the wire and fp32 accumulation
+  (``wire="bf16"``), or in-switch (``multimem.ld_reduce``) / by direct peer
+  loads on a gradient buffer in the symmetric heap (``wire="native"``), with
+  the 1/world scale fused in every case;
+* right behind its collective, on the same side stream, the bucket's slice of
+  the fused AdamW kernel runs (it also clears the gradients it has consumed),
+  so most of the optimizer pass overlaps backward as well and only the last
+  bucket's reduction and update are left when backward ends;
+* during backward the GEMMs can leave ``comm_sms`` SMs unoccupied for the
+  collectives, which then run as that many 512-thread CTAs (a CTA of that size
+  only fits on an SM that holds no persistent GEMM CTA);
 * forward, backward, the bucket collectives and the optimizer are captured
   once into a CUDA graph and replayed, so a step costs one launch on the host.
 """
 from __future__ import annotations
 
-import math
 import os
 from typing import List, Optional
 
@@ -30,10 +37,12 @@ from .. import _C, ops
 
 
 class _Bucket:
-    __slots__ = ("start", "numel", "pending", "total", "late")
+    __slots__ = ("start", "numel", "pending", "total", "late", "tail", "fired")
 
     def __init__(self, start: int):
         self.start, self.numel, self.pending, self.total = start, 0, 0, 0
+        self.tail = False    # completes when backward ends: nothing is left to share the GPU with
+        self.fired = -1      # step in which the bucket was last reduced / updated
         # True once a gradient of this bucket has arrived through autograd's own accumulation: such a
         # bucket is reduced after backward() has returned (the engine has then joined the stream that
         # accumulated it with the caller's stream), not from inside the hook.
@@ -43,7 +52,9 @@ class _Bucket:
 class DDPTrainer:
     def __init__(self, model: torch.nn.Module, device: torch.device, lr: float = 3e-4, betas=(0.9, 0.999),
                  eps: float = 1e-8, weight_decay: float = 0.01, group=None, wire: str = "bf16",
-                 bucket_mb: float = 25.0, overlap: bool = True, use_graph: bool = True, algo: str = "auto"):
+                 bucket_mb: float = 25.0, overlap: bool = True, use_graph: bool = True, algo: str = "auto",
+                 comm_sms: Optional[int] = None, comm_threads: Optional[int] = None,
+                 overlap_optimizer: Optional[bool] = None, last_bucket_mb: float = 4.0):
         self.model, self.device = model, device
         self.lr, self.betas, self.eps, self.wd = lr, betas, eps, weight_decay
         self.wire, self.overlap, self.use_graph, self.algo = wire, overlap, use_graph, algo
@@ -51,17 +62,34 @@ class DDPTrainer:
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.comm = None
         self._late: List[_Bucket] = []
+        self._step_id = 0
         if self.world > 1:
             import mccl_b200
             be = mccl_b200.get_backend(group)
             if be is None:
                 raise RuntimeError("DDPTrainer needs a process group created with backend='mccl'")
             self.comm = be.device_comm(device.index)
-        self._flatten(bucket_mb)
+        # SMs kept free of GEMM CTAs during backward for the bucket collectives (0: none, the collectives
+        # then share SMs with the GEMMs as 256-thread CTAs).
+        if comm_sms is None:
+            comm_sms = int(os.environ.get("MCCL_DDP_COMM_SMS", "0"))
+        self.comm_sms = comm_sms if (self.world > 1 and overlap) else 0
+        if comm_threads is None:
+            comm_threads = int(os.environ.get("MCCL_DDP_COMM_THREADS", "512" if self.comm_sms > 0 else "0"))
+        self.comm_threads = comm_threads
+        # The optimizer runs bucket by bucket behind the collectives (CUDA only: it needs the fused kernel).
+        if overlap_optimizer is None:
+            overlap_optimizer = os.environ.get("MCCL_DDP_OVERLAP_OPTIMIZER", "1") != "0"
+        self.overlap_optimizer = bool(overlap_optimizer and overlap and device.type == "cuda"
+                                      and ops.native_ops_available().get("adamw_flat"))
+        # Hooks are needed whenever something happens per bucket.
+        self._per_bucket = self.world > 1 or self.overlap_optimizer
+        self._flatten(bucket_mb, last_bucket_mb)
         self.step_t = torch.zeros((), device=device, dtype=torch.float32)
         self.m = torch.zeros_like(self.flat_p)
         self.v = torch.zeros_like(self.flat_p)
-        self.comm_stream = torch.cuda.Stream(device=device, priority=-1) if self.world > 1 else None
+        self.comm_stream = (torch.cuda.Stream(device=device, priority=-1)
+                            if (self._per_bucket and device.type == "cuda") else None)
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.static_tokens = None
         self.static_targets = None
@@ -71,21 +99,47 @@ class DDPTrainer:
             self._sync_initial_params(group)
 
     # ------------------------------------------------------------ buffers --
-    def _flatten(self, bucket_mb: float) -> None:
+    def _flatten(self, bucket_mb: float, last_bucket_mb: float) -> None:
         params = [p for p in self.model.parameters() if p.requires_grad]
         # Backward produces gradients roughly in reverse registration order.
         order = list(reversed(params))
         align = 16 * max(self.world, 1)  # chunk boundaries of the collectives stay 16-element aligned
         bucket_cap = int(bucket_mb * (1 << 20) / 4)
+        last_cap = int(max(last_bucket_mb, 0.0) * (1 << 20) / 4)
+        # The tail: the parameters whose gradients arrive last.  Their collectives (and optimizer slices)
+        # run after backward has ended, so they go into buckets of their own: every parameter larger than
+        # last_cap alone, the small ones before it together up to last_cap.
+        tail_from = len(order)
+        if self._per_bucket and last_cap > 0 and len(order) > 1:
+            acc = 0
+            i = len(order) - 1
+            while i >= 0 and order[i].numel() > last_cap:   # large trailing parameters (a tied embedding table)
+                i -= 1
+            j = i
+            while j >= 0 and acc + order[j].numel() <= last_cap:
+                acc += order[j].numel()
+                j -= 1
+            tail_from = j + 1
         offsets, total = [], 0
         self.buckets: List[_Bucket] = [_Bucket(0)]
-        for p in order:
+
+        def close_bucket():
+            nonlocal total
+            total = (total + align - 1) // align * align
+            self.buckets[-1].numel = total - self.buckets[-1].start
+            self.buckets.append(_Bucket(total))
+
+        for k, p in enumerate(order):
             b = self.buckets[-1]
-            if b.numel > 0 and b.numel + p.numel() > bucket_cap:
-                total = (total + align - 1) // align * align
-                b.numel = total - b.start
-                self.buckets.append(_Bucket(total))
+            in_tail = k >= tail_from
+            cap = bucket_cap
+            new = b.numel > 0 and b.numel + p.numel() > cap
+            if in_tail and b.numel > 0 and (k == tail_from or p.numel() > last_cap or order[k - 1].numel() > last_cap):
+                new = True
+            if new:
+                close_bucket()
                 b = self.buckets[-1]
+            b.tail = in_tail
             offsets.append(total)
             n = (p.numel() + 7) // 8 * 8  # every parameter starts 16-byte aligned in fp32 and in bf16
             total += n
@@ -118,7 +172,7 @@ class DDPTrainer:
             self._param_bucket[p] = bi
             # native operators write gradients straight into the flat buffer ...
             p._grad_sink = p.grad
-            if self.world > 1:
+            if self._per_bucket:
                 # ... and say so; gradients that come back through autograd fire its hook instead
                 p._grad_ready = (lambda q=p: self._on_grad_ready(q))
                 p.register_post_accumulate_grad_hook(self._on_autograd_grad)
@@ -138,6 +192,12 @@ class DDPTrainer:
 
     # ------------------------------------------------------- communication --
     def _on_grad_ready(self, p: torch.Tensor) -> None:
+        # A parameter reports once per step.  (autograd's post-accumulate hook also fires when a native
+        # operator returned None for the gradient because it had written it into the sink itself, and
+        # that second report must not count: it would mark every bucket as late and reduce it twice.)
+        if getattr(p, "_ready_step", -1) == self._step_id:
+            return
+        p._ready_step = self._step_id
         b = self.buckets[self._param_bucket[p]]
         b.pending += 1
         if b.pending == b.total:
@@ -148,36 +208,77 @@ class DDPTrainer:
                 self._reduce_bucket(b)
 
     def _on_autograd_grad(self, p: torch.Tensor) -> None:
+        if getattr(p, "_ready_step", -1) == self._step_id:
+            return   # already reported by the native operator that wrote the gradient
         self.buckets[self._param_bucket[p]].late = True
         self._on_grad_ready(p)
 
+    def _adamw(self, start: int, numel: int) -> None:
+        end = start + numel
+        ops.adamw_step(self.flat_p[start:end], self.flat_g[start:end], self.m[start:end], self.v[start:end], self.lr,
+                       self.betas[0], self.betas[1], self.eps, self.wd, self.step_t,
+                       p_bf16=None if self.flat_p16 is None else self.flat_p16[start:end], zero_grad=True)
+
     def _reduce_bucket(self, b: _Bucket) -> None:
+        """Collective (world > 1) and optimizer slice (overlap_optimizer) of one bucket, on the side stream."""
+        b.fired = self._step_id
         main = torch.cuda.current_stream(self.device)
-        stream = self.comm_stream if self.overlap else main
+        stream = self.comm_stream if (self.overlap and self.comm_stream is not None) else main
         if stream is not main:
             stream.wait_stream(main)
+        shaped = self.comm is not None and (self.comm_sms > 0 or self.comm_threads > 0) and self._in_backward and not b.tail
+        if shaped:
+            saved = (self.comm.max_ctas, self.comm.launch_threads)
+            self.comm.set_launch_shape(self.comm_sms, self.comm_threads)
         with torch.cuda.stream(stream):
-            if self.wire == "bf16":
-                g = self.flat_g[b.start:b.start + b.numel]
-                self.comm.allreduce([g], [g], op="avg", algo=("twoshot" if self.algo == "auto" else self.algo),
-                                    wire="bf16")
-            else:
-                self.comm.allreduce_symm(self.symm, b.start * 4, b.numel, torch.float32, "avg")
+            if self.comm is not None:
+                if self.wire == "bf16":
+                    g = self.flat_g[b.start:b.start + b.numel]
+                    self.comm.allreduce([g], [g], op="avg", algo=("twoshot" if self.algo == "auto" else self.algo),
+                                        wire="bf16")
+                else:
+                    self.comm.allreduce_symm(self.symm, b.start * 4, b.numel, torch.float32, "avg")
+            if self.overlap_optimizer:
+                self._adamw(b.start, b.numel)
+        if shaped:
+            self.comm.set_launch_shape(saved[0], saved[1] if saved[1] > 0 else -1)
 
     # ---------------------------------------------------------------- step --
     def _step_body(self, tokens: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
-        self.flat_g.zero_()
+        self._step_id += 1
+        for b in self.buckets:
+            b.pending = 0
+        self.step_t.add_(1.0)
+        if not self.overlap_optimizer:
+            self.flat_g.zero_()   # otherwise the optimizer slices cleared what they consumed
         loss = self.model(tokens, targets)
-        loss.backward()
+        if self.comm_sms > 0:
+            _C.set_gemm_cta_limit(max(_C.gemm_sm_count() - self.comm_sms, 1))
+        self._in_backward = True
+        try:
+            loss.backward()
+        finally:
+            self._in_backward = False
+            if self.comm_sms > 0:
+                _C.set_gemm_cta_limit(0)
         for b in self._late:
             self._reduce_bucket(b)
         self._late.clear()
+        if self._per_bucket:
+            for b in self.buckets:   # buckets none of whose parameters took part in this step's graph
+                if b.fired != self._step_id and b.pending == 0:
+                    self._reduce_bucket(b)
+                elif b.fired != self._step_id:   # some parameters of the bucket had no gradient: it is complete now
+                    b.pending = 0
+                    self._reduce_bucket(b)
         if self.comm_stream is not None and self.overlap:
             torch.cuda.current_stream(self.device).wait_stream(self.comm_stream)
-        self.step_t.add_(1.0)
-        ops.adamw_step(self.flat_p, self.flat_g, self.m, self.v, self.lr, self.betas[0], self.betas[1], self.eps,
-                       self.wd, self.step_t, p_bf16=self.flat_p16)
+        if not self.overlap_optimizer:
+            ops.adamw_step(self.flat_p, self.flat_g, self.m, self.v, self.lr, self.betas[0], self.betas[1], self.eps,
+                           self.wd, self.step_t, p_bf16=self.flat_p16)
         return loss.detach()
+
+    _in_backward = False
 
     def _capture(self, tokens: torch.Tensor, targets: torch.Tensor) -> None:
         self.static_tokens = tokens.clone()
@@ -196,7 +297,10 @@ class DDPTrainer:
         self.launches_per_step = ops.launch_count() + (self.comm.launches if self.comm is not None else 0) - before
 
     def step(self, tokens: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
-        """One optimizer step on device-resident tokens; returns the loss (device tensor)."""
+        """One optimizer step on device-resident tokens; returns the loss (device tensor).
+
+        With ``overlap_optimizer`` the gradient buffer is cleared by the optimizer as it consumes it, so
+        ``p.grad`` reads as zero after a step."""
         if not self.use_graph:
             before = ops.launch_count() + (self.comm.launches if self.comm is not None else 0)
             loss = self._step_body(tokens, targets)
@@ -204,6 +308,7 @@ class DDPTrainer:
             return loss
         if self.graph is None:
             self._capture(tokens, targets)
+        self.check()   # a wait that ran out in an earlier step raises here, before its gradients are used again
         self.static_tokens.copy_(tokens, non_blocking=True)
         self.static_targets.copy_(targets, non_blocking=True)
         self.graph.replay()
@@ -217,11 +322,14 @@ class DDPTrainer:
             self.static_tokens.copy_(tokens_pinned, non_blocking=True)
             self.static_targets.copy_(targets_pinned, non_blocking=True)
             self.graph.replay()
-            return float(self.static_loss.item())
+            loss = float(self.static_loss.item())
+            self.check()
+            return loss
         loss = self._step_body(tokens_pinned.to(self.device, non_blocking=True),
                                targets_pinned.to(self.device, non_blocking=True))
         return float(loss.item())
 
     def check(self) -> None:
-        if self.comm is not None:
+        """Raises TimeoutError when a device-side wait of this trainer's collectives ran out."""
+        if self.comm is not None and self.comm.status() != 0:
             self.comm.check_status()

@@ -231,6 +231,41 @@ def test_replay_in_cuda_graph(comm):
         assert ((outs[0].double().cpu() - gold).abs().max() / gold.abs().max()).item() < 1e-5, it
 
 
+@pytest.mark.parametrize("world", [2, 4])
+def test_send_recv_emulated(world):
+    """send / recv through the per-pair slots: a sender and a receiver run as two virtual ranks of one
+    cooperative launch.  Sizes cover one partial chunk, an unaligned tail and a message longer than the
+    two slot buffers (streamed: the sender waits for the receiver to drain)."""
+    C = _C()
+    c = C.DeviceComm(world, 0)
+    slot = c.p2p_slot_bytes
+    dev = torch.device("cuda", 0)
+    for it, nbytes in enumerate([100, 4096, (1 << 20) + 3, 2 * slot, 5 * slot + 17]):
+        src_rank, dst_rank = it % world, (it + 1) % world
+        g = torch.Generator().manual_seed(it)
+        payload = torch.randint(0, 256, (nbytes,), generator=g, dtype=torch.uint8).to(dev)
+        bufs, peers, sends = [], [], []
+        for v in range(world):
+            if v == src_rank:
+                bufs.append(payload); peers.append(dst_rank); sends.append(True)
+            elif v == dst_rank:
+                bufs.append(torch.zeros(nbytes, dtype=torch.uint8, device=dev)); peers.append(src_rank); sends.append(False)
+            else:
+                bufs.append(torch.zeros(1, dtype=torch.uint8, device=dev)); peers.append(-1); sends.append(False)
+        c.p2p_emulated(bufs, peers, sends)
+        torch.cuda.synchronize()
+        assert c.status() == 0, nbytes
+        assert torch.equal(bufs[dst_rank], payload), nbytes
+    # the same pair again, many small messages: sequence numbers and buffer parity keep alternating
+    for i in range(20):
+        payload = torch.full((1000,), float(i), device=dev)
+        out = torch.zeros(1000, device=dev)
+        bufs = [payload, out] + [torch.zeros(1, device=dev)] * (world - 2)
+        c.p2p_emulated(bufs, [1, 0] + [-1] * (world - 2), [True, False] + [False] * (world - 2))
+    torch.cuda.synchronize()
+    assert c.status() == 0 and out[0].item() == 19.0
+
+
 def test_bounded_wait_reports_timeout_and_context_survives():
     """A rank that withholds its signal makes the peers' waits run out: the kernels
     return, the status word names the silent peer, and the GPU stays usable."""
