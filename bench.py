@@ -17,12 +17,17 @@ Arms:
   reference  the unmodified reference package from baseline/_ref; it only builds on
              macOS/arm64 (Metal), so this arm reports itself unavailable
 
-Timing: W warm-up steps, then exactly K steps between CUDA events, bracketed by
-barrier + synchronize on both sides, max over ranks.  The working set of one
-step (fp32 parameters, gradients and both Adam moments, >1 GB) is far larger
-than the 126 MB L2, so no explicit flush is needed between steps.  The
-end-to-end figure repeats the K steps through DDPTrainer.step_from_host:
-pinned-host tokens copied to the device and the loss read back every step.
+Timing: W warm-up steps, then a region of exactly K steps between CUDA events,
+bracketed by barrier + synchronize on both sides, max over ranks.  The region
+is repeated R times (--repeats, 5 by default); `value` is the median region and
+`repeats` carries every region's time.  The working set of one step (fp32
+parameters, gradients and both Adam moments, >1 GB) is far larger than the
+126 MB L2, so no explicit flush is needed between steps.  The end-to-end figure
+repeats the K steps through DDPTrainer.step_from_host: pinned-host tokens copied
+to the device and the loss read back every step.  SM clocks and throttle reasons
+are sampled with nvidia-smi over the whole measured span.  Unless --no-nccl-arm
+is given, the same invocation then times the `nccl` arm (same model, data, K and
+W) and reports it under `nccl_arm`, so one record carries both.
 """
 from __future__ import annotations
 
@@ -36,7 +41,9 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
-PUBLISHED_SAMPLES_PER_S = {"70m": 56.9, "110m": 35.9}  # reference, 3x Mac mini M4 (README.md:50,54)
+# The reference's published numbers are for other hardware (3x Mac mini M4 over Thunderbolt, README.md:50,54); they
+# are carried as context, not as a denominator: nothing was published for this hardware, so vs_baseline is null.
+PUBLISHED_OTHER_HARDWARE = {"70m": 56.9, "110m": 35.9}
 
 
 def parse() -> argparse.Namespace:
@@ -53,6 +60,9 @@ def parse() -> argparse.Namespace:
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-overlap", action="store_true")
     ap.add_argument("--bucket-mb", type=float, default=25.0)
+    ap.add_argument("--repeats", type=int, default=5, help="timed regions of --steps steps each; the median is reported")
+    ap.add_argument("--no-nccl-arm", action="store_true", help="do not also time the nccl arm in this invocation")
+    ap.add_argument("--comm-sms", type=int, default=None)
     return ap.parse_args()
 
 
@@ -104,39 +114,7 @@ def main() -> None:
     dev_tokens = [t.to(device) for t in host_tokens]
     dev_targets = [t.to(device) for t in host_targets]
 
-    launches = 0
-    if args.impl == "mccl":
-        from mccl_b200.parallel import DDPTrainer
-        trainer = DDPTrainer(model, device, lr=3e-4, wire=args.wire, bucket_mb=args.bucket_mb,
-                             overlap=not args.no_overlap, use_graph=not args.no_graph, algo=args.algo)
-
-        def run_step(i):
-            return trainer.step(dev_tokens[i % n_batches], dev_targets[i % n_batches])
-
-        def run_step_e2e(i):
-            return trainer.step_from_host(host_tokens[i % n_batches], host_targets[i % n_batches])
-    else:
-        from torch.nn.parallel import DistributedDataParallel as DDP
-        net = DDP(model, device_ids=[local_rank], bucket_cap_mb=args.bucket_mb, gradient_as_bucket_view=True) if world > 1 else model
-        opt = torch.optim.AdamW(model.parameters(), lr=3e-4, fused=True)
-
-        def run_step(i):
-            opt.zero_grad(set_to_none=True)
-            with torch.autocast("cuda", dtype=torch.bfloat16):
-                loss = net(dev_tokens[i % n_batches], dev_targets[i % n_batches])
-            loss.backward()
-            opt.step()
-            return loss.detach()
-
-        def run_step_e2e(i):
-            tok = host_tokens[i % n_batches].to(device, non_blocking=True)
-            tgt = host_targets[i % n_batches].to(device, non_blocking=True)
-            opt.zero_grad(set_to_none=True)
-            with torch.autocast("cuda", dtype=torch.bfloat16):
-                loss = net(tok, tgt)
-            loss.backward()
-            opt.step()
-            return float(loss.item())
+    import statistics
 
     def sync():
         if world > 1:
@@ -159,24 +137,98 @@ def main() -> None:
             ms = float(t.item())
         return ms, last
 
-    for i in range(max(args.warmup, 3)):
-        run_step(i)
-    sampler = ClockSampler(local_rank).start() if rank == 0 else None
-    ms, last_loss = timed(run_step, args.steps)
-    clocks = sampler.stop() if sampler is not None else None
+    def make_mccl_arm():
+        from mccl_b200.parallel import DDPTrainer
+        trainer = DDPTrainer(model, device, lr=3e-4, wire=args.wire, bucket_mb=args.bucket_mb,
+                             overlap=not args.no_overlap, use_graph=not args.no_graph, algo=args.algo, comm_sms=args.comm_sms)
+
+        def run_step(i):
+            return trainer.step(dev_tokens[i % n_batches], dev_targets[i % n_batches])
+
+        def run_step_e2e(i):
+            return trainer.step_from_host(host_tokens[i % n_batches], host_targets[i % n_batches])
+        return trainer, run_step, run_step_e2e
+
+    def make_nccl_arm(net_model, group):
+        from torch.nn.parallel import DistributedDataParallel as DDP
+        net = (DDP(net_model, device_ids=[local_rank], bucket_cap_mb=args.bucket_mb, gradient_as_bucket_view=True,
+                   process_group=group) if world > 1 else net_model)
+        opt = torch.optim.AdamW(net_model.parameters(), lr=3e-4, fused=True)
+
+        def run_step(i):
+            opt.zero_grad(set_to_none=True)
+            with torch.autocast("cuda", dtype=torch.bfloat16):
+                loss = net(dev_tokens[i % n_batches], dev_targets[i % n_batches])
+            loss.backward()
+            opt.step()
+            return loss.detach()
+
+        def run_step_e2e(i):
+            tok = host_tokens[i % n_batches].to(device, non_blocking=True)
+            tgt = host_targets[i % n_batches].to(device, non_blocking=True)
+            opt.zero_grad(set_to_none=True)
+            with torch.autocast("cuda", dtype=torch.bfloat16):
+                loss = net(tok, tgt)
+            loss.backward()
+            opt.step()
+            return float(loss.item())
+        return run_step, run_step_e2e
+
+    def measure(run_step, run_step_e2e, repeats):
+        """W warm-up steps, `repeats` regions of K steps each, then the same through the end-to-end call."""
+        for i in range(max(args.warmup, 3)):
+            run_step(i)
+        regions, last = [], None
+        for _ in range(max(repeats, 1)):
+            ms, last = timed(run_step, args.steps)
+            regions.append(ms)
+        for i in range(3):
+            run_step_e2e(i)
+        e2e_regions, last_e2e = [], None
+        for _ in range(max(min(repeats, 3), 1)):
+            ms, last_e2e = timed(run_step_e2e, args.steps)
+            e2e_regions.append(ms)
+        return regions, e2e_regions, last
+
+    launches = 0
+    trainer = None
+    sampler = ClockSampler(local_rank, period_ms=100).start() if rank == 0 else None
     if args.impl == "mccl":
+        trainer, run_step, run_step_e2e = make_mccl_arm()
+    else:
+        run_step, run_step_e2e = make_nccl_arm(model, None)
+    regions, e2e_regions, last_loss = measure(run_step, run_step_e2e, args.repeats)
+    clocks = sampler.stop() if sampler is not None else None
+    ms = statistics.median(regions)
+    ms_e2e = statistics.median(e2e_regions)
+    if trainer is not None:
         launches = trainer.launches_per_step * args.steps
         trainer.check()
 
-    for i in range(3):
-        run_step_e2e(i)
-    ms_e2e, last_e2e = timed(run_step_e2e, args.steps)
+    # The comparison arm in the same invocation: stock eager model, DistributedDataParallel over NCCL, fused AdamW.
+    nccl_arm = None
+    if args.impl == "mccl" and not args.no_nccl_arm:
+        try:
+            torch.manual_seed(0)
+            ref_model = build_decoder(args.model, native=False, max_seq=args.seq).to(device)
+            group = dist.new_group(backend="nccl") if world > 1 else None
+            r_step, r_e2e = make_nccl_arm(ref_model, group)
+            r_regions, r_e2e_regions, _ = measure(r_step, r_e2e, min(args.repeats, 3))
+            r_ms, r_ms_e2e = statistics.median(r_regions), statistics.median(r_e2e_regions)
+            nccl_arm = {
+                "value": round(B * world * args.steps / (r_ms / 1e3), 2),
+                "ms_per_step": round(r_ms / args.steps, 4),
+                "e2e": round(B * world * args.steps / (r_ms_e2e / 1e3), 2),
+                "what": "stock eager PyTorch model, DistributedDataParallel over backend nccl, autocast bf16, fused AdamW; "
+                        "same data, steps and warm-up",
+            }
+        except Exception as e:  # noqa: BLE001  (the comparison arm must not take the headline number with it)
+            nccl_arm = {"unavailable": f"{type(e).__name__}: {e}"[:200]}
 
     if rank == 0:
         global_batch = B * world
         value = global_batch * args.steps / (ms / 1e3)
         e2e_value = global_batch * args.steps / (ms_e2e / 1e3)
-        pub = PUBLISHED_SAMPLES_PER_S.get(args.model)
         line = {
             "metric": "ddp_train_samples_per_sec",
             "value": round(value, 2),
@@ -188,7 +240,9 @@ def main() -> None:
             "ms_per_step": round(ms / args.steps, 4),
             "higher_is_better": True,
             "scaling": "weak",
-            "vs_baseline": round(value / pub, 2) if pub else None,
+            "vs_baseline": None,
+            "published_other_hardware": {"samples_per_s": PUBLISHED_OTHER_HARDWARE.get(args.model),
+                                         "hardware": "3x Mac mini M4 over Thunderbolt (reference README.md:50,54)"},
             "dtype": "bf16",
             "data": "synthetic: token ids uniform in [0, vocab) from seed 0; random-init weights",
             "config": {
@@ -204,6 +258,10 @@ def main() -> None:
                 "cuda_graph": (args.impl == "mccl" and not args.no_graph),
             },
             "clocks": clocks,
+            "repeats": {"n": len(regions), "ms_per_step_min": round(min(regions) / args.steps, 4),
+                        "ms_per_step_max": round(max(regions) / args.steps, 4),
+                        "ms_per_step_all": [round(r / args.steps, 4) for r in regions], "value_is": "median region"},
+            "nccl_arm": nccl_arm,
             "e2e": {
                 "value": round(e2e_value, 2),
                 "unit": "samples/s",

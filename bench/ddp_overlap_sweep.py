@@ -26,6 +26,9 @@ CONFIGS = {
     "inline": (False, 0, 0, "bf16", 25.0, False),
     "shared256": (True, 0, 0, "bf16", 25.0, True),
     "shared256_noopt": (True, 0, 0, "bf16", 25.0, False),
+    "sm12": (True, 12, 512, "bf16", 25.0, True),
+    "sm20": (True, 20, 512, "bf16", 25.0, True),
+    "sm12nvls": (True, 12, 512, "native", 25.0, True),
     "sm8": (True, 8, 512, "bf16", 25.0, True),
     "sm16": (True, 16, 512, "bf16", 25.0, True),
     "sm16_noopt": (True, 16, 512, "bf16", 25.0, False),

@@ -171,6 +171,9 @@ void bind_comm(py::module_& m) {
       .def("status", &DeviceComm::status)
       .def("check_status", &DeviceComm::check_status)
       .def("clear_status", &DeviceComm::clear_status)
+      .def("check_canaries", &DeviceComm::check_canaries)
+      .def_property_readonly("debug_bounds", &DeviceComm::debug_bounds)
+      .def("set_debug_arena_limit", &DeviceComm::set_debug_arena_limit, py::arg("nbytes"))
       .def("inject_skip_signals", &DeviceComm::inject_skip_signals, py::arg("count") = 1)
       .def("set_device_timeout_ms", &DeviceComm::set_device_timeout_ms)
       .def_property_readonly("device_timeout_ms", &DeviceComm::device_timeout_ms)

@@ -7,6 +7,7 @@
 #include <torch/extension.h>
 
 #include "../core/errors.hpp"
+#include "../core/launch.hpp"
 #include "../core/timeline.hpp"
 #include "../ops/ops.hpp"
 #include "../ops/tp_gemm.hpp"
@@ -47,6 +48,10 @@ int parse_epilogue(const std::string& s, bool has_bias) {
 void bind_ops(py::module_& m) {
   m.def("op_launch_count", [] { return ops::launch_count(); });
   m.def("gemm_error_flag", [] { return ops::gemm_error_flag(); });
+  // ---- launch tracer: every kernel of this package goes through MCCL_LAUNCH (csrc/core/launch.hpp) ----
+  m.def("launch_counts", [] { return launch_counts(); }, "Launches per kernel name since the process started.");
+  m.def("launch_counts_reset", [] { launch_counts_reset(); });
+  m.def("launch_total", [] { return launch_total(); });
   m.def("set_gemm_cta_limit", &ops::set_gemm_cta_limit, py::arg("ctas"),
         "Caps the CTAs (SMs) of plain GEMM launches from now on; 0 = one per SM.");
   m.def("gemm_cta_limit", &ops::gemm_cta_limit);

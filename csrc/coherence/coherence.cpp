@@ -123,22 +123,40 @@ void* CoherenceProtocol::read_page(const GlobalAddress& g, bool write) {
   const uint64_t page = page_index(g.offset);
   const GlobalAddress start(g.node_id, g.region_id, page * COHERENCE_PAGE_SIZE);
   const uint64_t key = CoherenceDirectory::key(g.region_id, page);
+  const PageKey pk{g.node_id, key};
   const bool home_is_me = g.node_id == node_;
   {
     std::lock_guard<std::mutex> lk(mu_);
     if (!home_is_me) {
-      auto it = cache_.find({g.node_id, key});
-      if (it != cache_.end() && (it->second.state == PageState::EXCLUSIVE || (!write && it->second.state == PageState::SHARED)))
+      auto it = cache_.find(pk);
+      if (it != cache_.end() && (it->second.state == PageState::EXCLUSIVE || (!write && it->second.state == PageState::SHARED))) {
+        if (write) it->second.pinned = true;
         return it->second.data.data();
+      }
+      // From here until the data is installed, an INVALIDATE or a recall for this page must not be answered
+      // as if this node held nothing: the grant may already be on its way.
+      inflight_[pk] = Inflight();
     }
     write ? ++stats_.write_misses : ++stats_.read_misses;
   }
   const uint64_t seq = next_seq_.fetch_add(1);
   send(g.node_id, write ? CoherenceOp::EXCLUSIVE_REQ : CoherenceOp::READ_REQ, g.node_id, g.region_id, page, epoch_.load(), seq);
   CoherenceOp got;
-  MCCL_CHECK_T(wait_reply(seq, &got), TimeoutError,
-               "coherence: node " << g.node_id << " did not answer a " << (write ? "write" : "read") << " request for page "
-                                  << page << " of region " << g.region_id << " within " << timeout_ms_ << " ms");
+  if (!wait_reply(seq, &got)) {
+    Inflight f;
+    {
+      std::lock_guard<std::mutex> lk(mu_);
+      auto it = inflight_.find(pk);
+      if (it != inflight_.end()) {
+        f = it->second;
+        inflight_.erase(it);
+      }
+    }
+    if (f.recall) send(f.recall_msg.sender, CoherenceOp::WRITEBACK_DATA, f.recall_msg.home, f.recall_msg.region, f.recall_msg.page, f.recall_msg.epoch);
+    MCCL_CHECK_T(false, TimeoutError,
+                 "coherence: node " << g.node_id << " did not answer a " << (write ? "write" : "read") << " request for page "
+                                    << page << " of region " << g.region_id << " within " << timeout_ms_ << " ms");
+  }
   if (home_is_me) {
     AddrResolution a = dmem_->resolve(start);
     MCCL_CHECK(a.ok, "coherence: local page is not registered");
@@ -148,21 +166,67 @@ void* CoherenceProtocol::read_page(const GlobalAddress& g, bool write) {
   CachedPage cp;
   cp.data.resize(len);
   uint64_t wr = dmem_->get(cp.data.data(), start, len);
-  MCCL_CHECK(wr != 0 && dmem_->poll_completion(wr, timeout_ms_), "coherence: fetching the page data failed");
+  const bool fetched = wr != 0 && dmem_->poll_completion(wr, timeout_ms_);
   cp.state = write ? PageState::EXCLUSIVE : PageState::SHARED;
-  std::lock_guard<std::mutex> lk(mu_);
-  auto& slot = cache_[{g.node_id, key}];
+  std::unique_lock<std::mutex> lk(mu_);
+  Inflight f;
+  {
+    auto it = inflight_.find(pk);
+    if (it != inflight_.end()) {
+      f = it->second;
+      inflight_.erase(it);
+    }
+  }
+  if (!fetched || (!write && (f.invalidated || f.recall))) {
+    // Not cacheable: the fetch failed, or the home has moved on since it answered.  A reader still gets the
+    // bytes that were fetched (valid as memory until the next acquire / release), but the next access asks again.
+    lk.unlock();
+    if (f.recall) send(f.recall_msg.sender, CoherenceOp::WRITEBACK_DATA, f.recall_msg.home, f.recall_msg.region, f.recall_msg.page, f.recall_msg.epoch);
+    MCCL_CHECK(fetched, "coherence: fetching the page data failed");
+    lk.lock();
+    retired_.push_back(std::move(cp.data));
+    return retired_.back().data();
+  }
+  cp.pinned = write;
+  cp.recall = f.recall;          // answered by write_page_done()
+  cp.recall_msg = f.recall_msg;
+  auto& slot = cache_[pk];
   slot = std::move(cp);
   return slot.data.data();
 }
 
+void CoherenceProtocol::give_back(const PageKey& k, CachedPage& cp, const CoherenceMessage& recall_msg) {
+  const uint32_t region = static_cast<uint32_t>(k.second >> 32);
+  const uint64_t page = k.second & 0xffffffffu;
+  if (cp.state == PageState::EXCLUSIVE && cp.dirty) {
+    uint64_t wr = dmem_->put(GlobalAddress(k.first, region, page * COHERENCE_PAGE_SIZE), cp.data.data(), cp.data.size());
+    if (wr) dmem_->poll_completion(wr, timeout_ms_);
+    std::lock_guard<std::mutex> lk(mu_);
+    ++stats_.writebacks;
+  }
+  send(recall_msg.sender, CoherenceOp::WRITEBACK_DATA, recall_msg.home, recall_msg.region, recall_msg.page, recall_msg.epoch);
+}
+
 void CoherenceProtocol::write_page_done(const GlobalAddress& g) {
   if (g.node_id == node_) return;  // the home writes in place
-  std::lock_guard<std::mutex> lk(mu_);
-  auto it = cache_.find({g.node_id, CoherenceDirectory::key(g.region_id, page_index(g.offset))});
-  MCCL_CHECK(it != cache_.end() && it->second.state == PageState::EXCLUSIVE,
-             "coherence: write_page_done on a page this node does not hold exclusively");
-  it->second.dirty = true;
+  const PageKey pk{g.node_id, CoherenceDirectory::key(g.region_id, page_index(g.offset))};
+  CachedPage taken;
+  bool recalled = false;
+  {
+    std::lock_guard<std::mutex> lk(mu_);
+    auto it = cache_.find(pk);
+    MCCL_CHECK(it != cache_.end() && it->second.state == PageState::EXCLUSIVE,
+               "coherence: write_page_done on a page this node does not hold exclusively");
+    it->second.dirty = true;
+    it->second.pinned = false;
+    if (it->second.recall) {
+      // the home asked for the page while it was being written: hand it back now
+      recalled = true;
+      taken = std::move(it->second);
+      cache_.erase(it);
+    }
+  }
+  if (recalled) give_back(pk, taken, taken.recall_msg);
 }
 
 PageState CoherenceProtocol::local_state(const GlobalAddress& g) const {
@@ -186,13 +250,18 @@ CoherenceStats CoherenceProtocol::stats() const {
 void CoherenceProtocol::acquire() {
   dmem_->drain_pending();
   epoch_.fetch_add(1);
+  std::lock_guard<std::mutex> lk(mu_);
+  retired_.clear();
 }
 
 void CoherenceProtocol::release() {
-  std::map<std::pair<uint16_t, uint64_t>, CachedPage> pages;
+  std::map<PageKey, CachedPage> pages;
   {
     std::lock_guard<std::mutex> lk(mu_);
     pages.swap(cache_);
+    // a recall that arrives for one of these pages while it is on its way home is answered by the
+    // WRITEBACK_DATA below, not by the service thread (which no longer finds the page)
+    for (auto& kv : pages) releasing_.insert(kv.first);
   }
   for (auto& kv : pages) {
     const uint16_t home = kv.first.first;
@@ -208,8 +277,12 @@ void CoherenceProtocol::release() {
       }
       send(home, CoherenceOp::WRITEBACK_DATA, home, region, page, epoch_.load());
     }
+    std::lock_guard<std::mutex> lk(mu_);
+    releasing_.erase(kv.first);
   }
   dmem_->drain_pending();
+  std::lock_guard<std::mutex> lk(mu_);
+  retired_.clear();
 }
 
 void CoherenceProtocol::fence() {
@@ -331,6 +404,9 @@ void CoherenceProtocol::handle_message(const CoherenceMessage& m) {
     }
     case CoherenceOp::WRITEBACK_DATA: {
       DirectoryEntry& e = dir_.entry(m.region, m.page);
+      // Only the current exclusive owner can give the page back.  (A node whose release() crossed a recall
+      // answers twice; by the time the second answer arrives the page may belong to somebody else.)
+      if (e.state != PageState::EXCLUSIVE || e.exclusive_owner != m.sender) break;
       e.state = PageState::UNCACHED;
       e.sharers = 0;
       e.exclusive_owner = 0xff;
@@ -344,22 +420,39 @@ void CoherenceProtocol::handle_message(const CoherenceMessage& m) {
       break;
     }
     case CoherenceOp::INVALIDATE: {
-      cache_.erase({m.home, key});
+      const PageKey pk{m.home, key};
+      auto it = cache_.find(pk);
+      if (it != cache_.end()) {
+        retired_.push_back(std::move(it->second.data));   // a reader may still be looking at it
+        cache_.erase(it);
+      }
+      auto fi = inflight_.find(pk);
+      if (fi != inflight_.end()) fi->second.invalidated = true;
       send(m.sender, CoherenceOp::INVALIDATE_ACK, m.home, m.region, m.page, m.epoch);
       break;
     }
     case CoherenceOp::WRITEBACK_REQ: {
-      auto it = cache_.find({m.home, key});
+      const PageKey pk{m.home, key};
+      if (releasing_.count(pk)) break;   // release() is writing it home and will say so itself
+      auto it = cache_.find(pk);
       if (it != cache_.end()) {
+        if (it->second.pinned) {         // being written right now: answered by write_page_done()
+          it->second.recall = true;
+          it->second.recall_msg = m;
+          break;
+        }
         CachedPage cp = std::move(it->second);
         cache_.erase(it);
-        if (cp.state == PageState::EXCLUSIVE && cp.dirty) {
-          lk.unlock();
-          uint64_t wr = dmem_->put(GlobalAddress(m.home, m.region, m.page * COHERENCE_PAGE_SIZE), cp.data.data(), cp.data.size());
-          if (wr) dmem_->poll_completion(wr, timeout_ms_);
-          lk.lock();
-          ++stats_.writebacks;
-        }
+        lk.unlock();
+        give_back(pk, cp, m);
+        lk.lock();
+        break;
+      }
+      auto fi = inflight_.find(pk);
+      if (fi != inflight_.end()) {       // granted, data not installed yet: answered once it is
+        fi->second.recall = true;
+        fi->second.recall_msg = m;
+        break;
       }
       send(m.sender, CoherenceOp::WRITEBACK_DATA, m.home, m.region, m.page, m.epoch);
       break;

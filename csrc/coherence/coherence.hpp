@@ -26,6 +26,7 @@
 #include <deque>
 #include <functional>
 #include <map>
+#include <set>
 #include <memory>
 #include <mutex>
 #include <thread>
@@ -135,10 +136,14 @@ class CoherenceProtocol {
   void barrier_all();                  // centralised at node 0
 
   // Makes the page containing g readable (write=false) or writable (write=true) on this node.
-  // Returns a pointer to the page's bytes: the home's own memory on the home node, else a local cached copy.
-  // Throws TimeoutError when the home does not answer within the protocol timeout.
+  // Returns a pointer to the start of the page's bytes: the home's own memory on the home node, else a local
+  // cached copy.  Throws TimeoutError when the home does not answer within the protocol timeout.
+  // A page obtained for writing is pinned: a recall from the home (another node wants the page) is held back
+  // until write_page_done(), so a write between the two calls can neither be lost nor touch freed memory.
+  // A copy obtained for reading stays valid as memory until the next acquire() or release(), even when the
+  // home invalidates it in between (it may then be stale, which release consistency allows).
   void* read_page(const GlobalAddress& g, bool write);
-  void write_page_done(const GlobalAddress& g);   // marks the cached page dirty
+  void write_page_done(const GlobalAddress& g);   // marks the cached page dirty, unpins it and answers a held-back recall
   PageState local_state(const GlobalAddress& g) const;
   bool directory_lookup(uint32_t region, uint64_t page, DirectoryEntry* out) const;  // home side
   uint64_t global_epoch() const { return epoch_.load(); }
@@ -147,10 +152,19 @@ class CoherenceProtocol {
   void handle_message(const CoherenceMessage& m);   // public for tests; normally called by the service thread
 
  private:
+  using PageKey = std::pair<uint16_t, uint64_t>;   // (home, directory key)
   struct CachedPage {
     PageState state = PageState::UNCACHED;
     bool dirty = false;
+    bool pinned = false;           // handed out for writing, write_page_done() not called yet
+    bool recall = false;           // the home asked for the page back while it was pinned
+    CoherenceMessage recall_msg;
     std::vector<uint8_t> data;
+  };
+  struct Inflight {                // a request of this node whose data has not been installed yet
+    bool invalidated = false;      // an INVALIDATE arrived meanwhile: do not cache what is being fetched
+    bool recall = false;           // a WRITEBACK_REQ arrived meanwhile: answer it once the page is installed and unpinned
+    CoherenceMessage recall_msg;
   };
   struct PendingTxn {         // one outstanding directory transaction per page at the home
     uint8_t requester = 0;
@@ -167,6 +181,8 @@ class CoherenceProtocol {
   int invalidate_sharers(uint32_t region, uint64_t page, uint8_t except);
   bool wait_reply(uint64_t seq, CoherenceOp* got);
   uint64_t page_bytes(const GlobalAddress& page_start);
+  // Writes the page home when dirty and tells the home it is back; called without mu_ held.
+  void give_back(const PageKey& k, CachedPage& cp, const CoherenceMessage& recall_msg);
 
   const int node_;
   std::shared_ptr<CoherenceBus> bus_;
@@ -179,7 +195,10 @@ class CoherenceProtocol {
   CoherenceDirectory dir_;                                  // pages this node is home of
   std::map<uint64_t, PendingTxn> pending_;                  // by directory key
   std::map<uint64_t, std::deque<CoherenceMessage>> waiting_;  // requests queued behind a pending transaction
-  std::map<std::pair<uint16_t, uint64_t>, CachedPage> cache_;  // (home, directory key) → local copy
+  std::map<PageKey, CachedPage> cache_;                     // local copies
+  std::map<PageKey, Inflight> inflight_;                    // requests sent, data not installed yet
+  std::set<PageKey> releasing_;                             // pages release() is writing home right now
+  std::vector<std::vector<uint8_t>> retired_;               // invalidated copies a reader may still hold a pointer to
   std::map<uint64_t, CoherenceOp> replies_;                 // sender_seq → reply opcode
   std::atomic<uint64_t> next_seq_{1};
   std::atomic<uint64_t> epoch_{0};

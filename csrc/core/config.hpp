@@ -100,10 +100,10 @@ struct EnvConfig {
   int64_t device_timeout_cap_ms = 0;        // upper bound of the derived value
   int nvls = -1;                            // -1 auto, 0 off, 1 required
   bool blocking_wait = false;               // Work::wait blocks the host
-  bool debug_bounds = false;                // kernels check peer pointers
+  bool debug_bounds = false;                // kernels check their arena extent; poison fill and canaries (MCCL_DEBUG_BOUNDS)
   int max_queue_depth = 1024;               // bounded progress queue
   std::string symm_mode;                    // "auto" | "vmm" | "ipc"
-  std::string fault_inject;                 // host-side fault injection spec
+  std::string fault_inject;                 // host-made faults: "rank=R,skip_signals=N,after=K,delay_ms=M" (MCCL_FAULT_INJECT)
   std::string trace_path;                   // JSON-lines trace file, empty = off
   int max_ctas = 0;                         // cap on CTAs per collective, 0 = default
 

@@ -1,0 +1,65 @@
+#include "launch.hpp"
+
+#include <atomic>
+#include <mutex>
+
+#include "log.hpp"
+
+namespace mccl {
+
+namespace {
+std::mutex g_mu;
+std::map<std::string, uint64_t> g_counts;
+std::atomic<uint64_t> g_total{0};
+thread_local cudaError_t t_first_error = cudaSuccess;
+
+// "(gemm_persistent_kernel<BN, STAGES, kAMn, kBMn>)" -> "gemm_persistent_kernel"
+std::string short_name(const char* kernel) {
+  std::string s(kernel);
+  size_t b = 0;
+  while (b < s.size() && (s[b] == '(' || s[b] == ' ')) ++b;
+  size_t e = b;
+  while (e < s.size() && s[e] != '<' && s[e] != ')' && s[e] != ' ') ++e;
+  return s.substr(b, e - b);
+}
+}  // namespace
+
+cudaError_t launch_record(const char* kernel, const char* file, int line, dim3 grid, dim3 block, size_t smem, cudaStream_t stream) {
+  const cudaError_t rc = cudaGetLastError();
+  g_total.fetch_add(1, std::memory_order_relaxed);
+  {
+    std::lock_guard<std::mutex> g(g_mu);
+    ++g_counts[short_name(kernel)];
+  }
+  if (rc != cudaSuccess) {
+    if (t_first_error == cudaSuccess) t_first_error = rc;
+    MCCL_ERROR("launch of " << kernel << " at " << file << ":" << line << " failed: " << cudaGetErrorString(rc) << " (grid " << grid.x
+                            << "x" << grid.y << "x" << grid.z << ", block " << block.x << ", smem " << smem << ")");
+  } else if (log_level() <= LogLevel::TRACE) {
+    const char* base = file;
+    for (const char* p = file; *p; ++p)
+      if (*p == '/') base = p + 1;
+    MCCL_TRACE("launch " << short_name(kernel) << " @" << base << ":" << line << " grid " << grid.x << "x" << grid.y << " block "
+                         << block.x << " smem " << smem << " stream " << static_cast<const void*>(stream));
+  }
+  return rc;
+}
+
+cudaError_t launch_status() {
+  const cudaError_t rc = t_first_error;
+  t_first_error = cudaSuccess;
+  return rc;
+}
+
+std::map<std::string, uint64_t> launch_counts() {
+  std::lock_guard<std::mutex> g(g_mu);
+  return g_counts;
+}
+void launch_counts_reset() {
+  std::lock_guard<std::mutex> g(g_mu);
+  g_counts.clear();
+  g_total.store(0);
+}
+uint64_t launch_total() { return g_total.load(); }
+
+}  // namespace mccl

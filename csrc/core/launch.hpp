@@ -1,0 +1,37 @@
+// One door for every kernel launch.
+//
+//   MCCL_LAUNCH(kernel, grid, block, smem, stream, args...)
+//
+// launches `kernel`, reads the launch status (cudaGetLastError, so a bad configuration is reported at
+// the site that caused it and a stale error of an unrelated call is not carried along), counts the
+// launch under the kernel's name, and at log level TRACE prints site, grid, block, shared memory and
+// stream.  The expression's value is the cudaError_t of the launch.  A kernel name that contains commas
+// (template arguments) goes in parentheses: MCCL_LAUNCH((gemm<BN, ST>), ...).
+//
+// The reference wraps every Metal command-buffer commit the same way (MCCL_COMMIT(site, ...):
+// csrc/metal/CommitTrace.hpp:15-26) so that a stalled or failed commit names its call site.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <map>
+#include <string>
+
+namespace mccl {
+
+// Status of the launch just made (clears the error state) plus bookkeeping; see MCCL_LAUNCH.
+cudaError_t launch_record(const char* kernel, const char* file, int line, dim3 grid, dim3 block, size_t smem, cudaStream_t stream);
+// First failure among the launches this thread made through MCCL_LAUNCH since the last call (cudaSuccess when
+// none); clears it.  Launchers that enqueue several kernels end with `return launch_status();`.
+cudaError_t launch_status();
+// Launches per kernel name since the process started (or since launch_counts_reset()).
+std::map<std::string, uint64_t> launch_counts();
+void launch_counts_reset();
+uint64_t launch_total();
+
+}  // namespace mccl
+
+#define MCCL_LAUNCH(kernel, grid, block, smem, stream, ...)                                                     \
+  ((kernel)<<<(grid), (block), (smem), (stream)>>>(__VA_ARGS__),                                               \
+   ::mccl::launch_record(#kernel, __FILE__, __LINE__, dim3(grid), dim3(block), static_cast<size_t>(smem), (stream)))

@@ -2,6 +2,7 @@
 // from peer memory (what host-side put / get use when the caller wants the SMs
 // rather than a copy engine to move the data), the stream-ordered acquire /
 // release pair of the coherence layer, and a small self-test of the atomics.
+#include "../core/launch.hpp"
 #include "dmem_kernels.hpp"
 
 #include "device/dmem.cuh"
@@ -65,31 +66,31 @@ cudaError_t launch_dmem_copy(void* dst, const void* src, size_t n, cudaStream_t 
   if (n == 0) return cudaSuccess;
   size_t want = (n + (64u << 10) - 1) / (64u << 10);
   int ctas = static_cast<int>(want < 1 ? 1 : (want > 64 ? 64 : want));
-  dmem_copy_kernel<<<ctas, 512, 0, stream>>>(static_cast<char*>(dst), static_cast<const char*>(src), n);
-  return cudaGetLastError();
+  MCCL_LAUNCH(dmem_copy_kernel, ctas, 512, 0, stream, static_cast<char*>(dst), static_cast<const char*>(src), n);
+  return ::mccl::launch_status();
 }
 
 cudaError_t launch_dmem_post_imm(ImmWire* slot, const ImmWire& rec, cudaStream_t stream) {
-  dmem_post_imm_kernel<<<1, 1, 0, stream>>>(slot, rec);
-  return cudaGetLastError();
+  MCCL_LAUNCH(dmem_post_imm_kernel, 1, 1, 0, stream, slot, rec);
+  return ::mccl::launch_status();
 }
 
 cudaError_t launch_coherence_release(unsigned int* const* peer_flags_dev, int world, int rank, unsigned int epoch,
                                      cudaStream_t stream) {
-  coherence_release_kernel<<<1, 32, 0, stream>>>(peer_flags_dev, world, rank, epoch);
-  return cudaGetLastError();
+  MCCL_LAUNCH(coherence_release_kernel, 1, 32, 0, stream, peer_flags_dev, world, rank, epoch);
+  return ::mccl::launch_status();
 }
 
 cudaError_t launch_coherence_acquire(const unsigned int* my_flags, int world, int rank, unsigned int epoch,
                                      unsigned long long timeout_ns, int* status_dev, cudaStream_t stream) {
-  coherence_acquire_kernel<<<1, 32, 0, stream>>>(my_flags, world, rank, epoch, timeout_ns, status_dev);
-  return cudaGetLastError();
+  MCCL_LAUNCH(coherence_acquire_kernel, 1, 32, 0, stream, my_flags, world, rank, epoch, timeout_ns, status_dev);
+  return ::mccl::launch_status();
 }
 
 cudaError_t launch_dmem_atomic_selftest(unsigned int* counter, unsigned long long* slot, float* sum, int adds,
                                         cudaStream_t stream) {
-  dmem_atomic_selftest_kernel<<<1, 256, 0, stream>>>(counter, slot, sum, adds);
-  return cudaGetLastError();
+  MCCL_LAUNCH(dmem_atomic_selftest_kernel, 1, 256, 0, stream, counter, slot, sum, adds);
+  return ::mccl::launch_status();
 }
 
 }  // namespace mccl

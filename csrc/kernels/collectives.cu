@@ -22,6 +22,7 @@
 #include <cstdio>
 #include <type_traits>
 
+#include "../core/launch.hpp"
 #include "comm_device.cuh"
 
 namespace mccl {
@@ -97,6 +98,10 @@ __global__ void __launch_bounds__(kThreads) twoshot_kernel(DevComm c, CollArgs a
   const size_t slot_bytes = static_cast<size_t>(per) * sizeof(W);
   const size_t recv_off = static_cast<size_t>(s.half) * c.half_bytes;
   const size_t red_off = recv_off + static_cast<size_t>(N) * slot_bytes;
+  if (bounds_violation(c, vr, red_off + slot_bytes)) {
+    cta_end(c, vr, s, TL_ALLREDUCE);
+    return;
+  }
   long long pb, pe;
   cta_span(per / E, pb, pe);
   auto chunk_limit = [&](int p) -> long long {  // one past the last valid element of chunk p
@@ -230,6 +235,10 @@ __global__ void __launch_bounds__(kThreads) oneshot_kernel(DevComm c, CollArgs a
   const long long padded = (a.numel + 15) / 16 * 16;
   const size_t slot_bytes = static_cast<size_t>(padded) * sizeof(W);
   const size_t base = static_cast<size_t>(s.half) * c.half_bytes;
+  if (bounds_violation(c, vr, base + static_cast<size_t>(N) * slot_bytes)) {
+    cta_end(c, vr, s, TL_ALLREDUCE);
+    return;
+  }
   long long pb, pe;
   cta_span(padded / E, pb, pe);
   const bool al_in = aligned16(in), al_out = aligned16(out);
@@ -308,6 +317,10 @@ __global__ void __launch_bounds__(kThreads) ring_kernel(DevComm c, CollArgs a) {
   auto rs_buf = [&](int r, int k) { return reinterpret_cast<W*>(c.arena[r] + base + static_cast<size_t>(k) * slot_bytes); };
   auto ag_buf = [&](int r, int k) { return reinterpret_cast<W*>(c.arena[r] + base + static_cast<size_t>(N - 1 + k) * slot_bytes); };
   const int next = (rank + 1) % N, prev = (rank + N - 1) % N;
+  if (bounds_violation(c, vr, base + static_cast<size_t>(2 * (N - 1)) * slot_bytes)) {
+    cta_end(c, vr, s, TL_ALLREDUCE);
+    return;
+  }
   long long pb, pe;
   cta_span(per / E, pb, pe);
   auto chunk_limit = [&](int p) -> long long {
@@ -394,6 +407,10 @@ __global__ void __launch_bounds__(kThreads) tree_kernel(DevComm c, CollArgs a) {
   while ((1 << R) < N) ++R;
   auto tbuf = [&](int r, int j) { return reinterpret_cast<W*>(c.arena[r] + base + static_cast<size_t>(j) * slot_bytes); };
   auto bbuf = [&](int r) { return reinterpret_cast<W*>(c.arena[r] + base + static_cast<size_t>(R) * slot_bytes); };
+  if (bounds_violation(c, vr, base + static_cast<size_t>(R + 1) * slot_bytes)) {
+    cta_end(c, vr, s, TL_ALLREDUCE);
+    return;
+  }
   long long pb, pe;
   cta_span(padded / E, pb, pe);
   const bool al_in = aligned16(in), al_out = aligned16(out);
@@ -542,6 +559,10 @@ __global__ void __launch_bounds__(kThreads) nvls_kernel(DevComm c, CollArgs a, c
   if constexpr (kStage) {
     const size_t base = static_cast<size_t>(s.half) * c.half_bytes;
     const size_t region = static_cast<size_t>(N) * per * sizeof(W);
+    if (bounds_violation(c, 0, base + 2 * region)) {
+      cta_end(c, 0, s, TL_ALLREDUCE);
+      return;
+    }
     stage_local = c.arena[rank] + base;
     stage_mc = c.mc_arena + base;
     result_local = stage_local + region;
@@ -691,6 +712,10 @@ __global__ void __launch_bounds__(kThreads) allgather_kernel(DevComm c, CollArgs
   const char* in = static_cast<const char*>(a.in[vr]);
   char* out = static_cast<char*>(a.out[vr]);
   const size_t base = static_cast<size_t>(s.half) * c.half_bytes;
+  if (bounds_violation(c, vr, base + nbytes)) {
+    cta_end(c, vr, s);
+    return;
+  }
   unsigned long long b0, b1;
   cta_byte_span(nbytes, b0, b1);
   cta_copy_bytes(c.arena[rank] + base + b0, in + b0, b1 - b0);
@@ -724,6 +749,10 @@ __global__ void __launch_bounds__(kThreads) broadcast_kernel(DevComm c, CollArgs
     unsigned long long hi = lo + slice16;
     return (hi < nbytes ? hi : nbytes) - lo;
   };
+  if (bounds_violation(c, vr, base + slice16)) {
+    cta_end(c, vr, s);
+    return;
+  }
   if (rank == root) {
     for (int k = 0; k < N; ++k) {
       const int p = (rank + k) % N;
@@ -757,6 +786,15 @@ __global__ void __launch_bounds__(kThreads) alltoall_kernel(DevComm c, A2AArgs a
   const char* in = static_cast<const char*>(a.in[vr]);
   char* out = static_cast<char*>(a.out[vr]);
   const size_t base = static_cast<size_t>(s.half) * c.half_bytes;
+  {
+    unsigned long long longest = 0;
+    for (int q = 0; q < N; ++q) longest = a.in_len[vr][q] > longest ? a.in_len[vr][q] : longest;
+    if (longest > a.slot_bytes || bounds_violation(c, vr, base + static_cast<size_t>(N) * a.slot_bytes)) {
+      if (longest > a.slot_bytes && threadIdx.x == 0) report_timeout(c, vr, PH_BOUNDS, rank);
+      cta_end(c, vr, s);
+      return;
+    }
+  }
   for (int k = 0; k < N; ++k) {
     const int q = (rank + k) % N;
     unsigned long long b0, b1;
@@ -864,7 +902,7 @@ __global__ void __launch_bounds__(32) barrier_kernel(DevComm c) {
 namespace {
 
 template <typename... KArgs, typename... Args>
-cudaError_t launch(void (*kernel)(KArgs...), const LaunchCfg& cfg, int threads, Args... args) {
+cudaError_t launch(const char* name, void (*kernel)(KArgs...), const LaunchCfg& cfg, int threads, Args... args) {
   // Threads per CTA: cfg.threads when the caller chose (128..512), else MCCL_COMM_THREADS, else 256.  A
   // 256-thread collective CTA needs half a register file, so it can share an SM with a persistent GEMM CTA; a
   // 512-thread CTA needs a whole one and therefore only lands on an SM no GEMM CTA occupies, which is what a
@@ -881,10 +919,12 @@ cudaError_t launch(void (*kernel)(KArgs...), const LaunchCfg& cfg, int threads, 
   dim3 grid(cfg.ctas, cfg.nlocal > 1 ? cfg.nlocal : 1);
   if (cfg.nlocal > 1) {
     void* params[] = {static_cast<void*>(&args)...};
-    return cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(kernel), grid, dim3(threads), params, 0, cfg.stream);
+    cudaError_t rc = cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(kernel), grid, dim3(threads), params, 0, cfg.stream);
+    const cudaError_t seen = launch_record(name, __FILE__, __LINE__, grid, dim3(threads), 0, cfg.stream);
+    return rc != cudaSuccess ? rc : seen;
   }
-  kernel<<<grid, threads, 0, cfg.stream>>>(args...);
-  return cudaGetLastError();
+  kernel<<<grid, threads, 0, cfg.stream>>>(args...);   // the one launch statement of this file: every collective goes through here
+  return launch_record(name, __FILE__, __LINE__, grid, dim3(threads), 0, cfg.stream);
 }
 
 enum class Sched { TWOSHOT, SCATTER, ONESHOT, RING, TREE };
@@ -892,11 +932,11 @@ enum class Sched { TWOSHOT, SCATTER, ONESHOT, RING, TREE };
 template <typename T, typename W>
 cudaError_t launch_typed(Sched k, const DevComm& c, const CollArgs& a, const LaunchCfg& cfg) {
   switch (k) {
-    case Sched::TWOSHOT: return launch(twoshot_kernel<T, W, false>, cfg, kThreads, c, a);
-    case Sched::SCATTER: return launch(twoshot_kernel<T, W, true>, cfg, kThreads, c, a);
-    case Sched::ONESHOT: return launch(oneshot_kernel<T, W>, cfg, kThreads, c, a);
-    case Sched::RING: return launch(ring_kernel<T, W>, cfg, kThreads, c, a);
-    case Sched::TREE: return launch(tree_kernel<T, W>, cfg, kThreads, c, a);
+    case Sched::TWOSHOT: return launch("twoshot_kernel", twoshot_kernel<T, W, false>, cfg, kThreads, c, a);
+    case Sched::SCATTER: return launch("twoshot_kernel", twoshot_kernel<T, W, true>, cfg, kThreads, c, a);
+    case Sched::ONESHOT: return launch("oneshot_kernel", oneshot_kernel<T, W>, cfg, kThreads, c, a);
+    case Sched::RING: return launch("ring_kernel", ring_kernel<T, W>, cfg, kThreads, c, a);
+    case Sched::TREE: return launch("tree_kernel", tree_kernel<T, W>, cfg, kThreads, c, a);
   }
   return cudaErrorInvalidValue;
 }
@@ -936,8 +976,8 @@ cudaError_t launch_allreduce_nvls(ElemType t, bool bf16_wire, bool staged, const
                                   char* local_sym, char* mc_sym, const LaunchCfg& cfg) {
   if (cfg.nlocal > 1) return cudaErrorNotSupported;  // no multicast object inside one GPU
 #define MCCL_NVLS(T, W)                                                                       \
-  (staged ? launch(nvls_kernel<T, W, true>, cfg, kThreads, c, a, local_sym, mc_sym)           \
-          : launch(nvls_kernel<T, W, false>, cfg, kThreads, c, a, local_sym, mc_sym))
+  (staged ? launch("nvls_kernel", nvls_kernel<T, W, true>, cfg, kThreads, c, a, local_sym, mc_sym)           \
+          : launch("nvls_kernel", nvls_kernel<T, W, false>, cfg, kThreads, c, a, local_sym, mc_sym))
   switch (t) {
     case ElemType::F32: return bf16_wire ? MCCL_NVLS(float, __nv_bfloat16) : MCCL_NVLS(float, float);
     case ElemType::F16: return MCCL_NVLS(__half, __half);
@@ -949,32 +989,32 @@ cudaError_t launch_allreduce_nvls(ElemType t, bool bf16_wire, bool staged, const
 
 cudaError_t launch_allreduce_symm(ElemType t, const DevComm& c, const CollArgs& a, const LaunchCfg& cfg) {
   switch (t) {
-    case ElemType::F32: return launch(symm_allreduce_kernel<float>, cfg, kThreads, c, a);
-    case ElemType::F16: return launch(symm_allreduce_kernel<__half>, cfg, kThreads, c, a);
-    case ElemType::BF16: return launch(symm_allreduce_kernel<__nv_bfloat16>, cfg, kThreads, c, a);
-    case ElemType::F64: return launch(symm_allreduce_kernel<double>, cfg, kThreads, c, a);
-    case ElemType::I32: return launch(symm_allreduce_kernel<int32_t>, cfg, kThreads, c, a);
-    case ElemType::I64: return launch(symm_allreduce_kernel<int64_t>, cfg, kThreads, c, a);
+    case ElemType::F32: return launch("symm_allreduce_kernel", symm_allreduce_kernel<float>, cfg, kThreads, c, a);
+    case ElemType::F16: return launch("symm_allreduce_kernel", symm_allreduce_kernel<__half>, cfg, kThreads, c, a);
+    case ElemType::BF16: return launch("symm_allreduce_kernel", symm_allreduce_kernel<__nv_bfloat16>, cfg, kThreads, c, a);
+    case ElemType::F64: return launch("symm_allreduce_kernel", symm_allreduce_kernel<double>, cfg, kThreads, c, a);
+    case ElemType::I32: return launch("symm_allreduce_kernel", symm_allreduce_kernel<int32_t>, cfg, kThreads, c, a);
+    case ElemType::I64: return launch("symm_allreduce_kernel", symm_allreduce_kernel<int64_t>, cfg, kThreads, c, a);
   }
   return cudaErrorInvalidValue;
 }
 
 cudaError_t launch_allgather(const DevComm& c, const CollArgs& a, const LaunchCfg& cfg) {
-  return launch(allgather_kernel, cfg, kThreads, c, a);
+  return launch("allgather_kernel", allgather_kernel, cfg, kThreads, c, a);
 }
 cudaError_t launch_broadcast(const DevComm& c, const CollArgs& a, const LaunchCfg& cfg) {
-  return launch(broadcast_kernel, cfg, kThreads, c, a);
+  return launch("broadcast_kernel", broadcast_kernel, cfg, kThreads, c, a);
 }
 cudaError_t launch_alltoall(const DevComm& c, const A2AArgs& a, const LaunchCfg& cfg) {
-  return launch(alltoall_kernel, cfg, kThreads, c, a);
+  return launch("alltoall_kernel", alltoall_kernel, cfg, kThreads, c, a);
 }
 cudaError_t launch_p2p(const P2PComm& c, const P2PArgs& a, const LaunchCfg& cfg) {
-  return launch(p2p_kernel, cfg, kThreads, c, a);
+  return launch("p2p_kernel", p2p_kernel, cfg, kThreads, c, a);
 }
 cudaError_t launch_barrier(const DevComm& c, const LaunchCfg& cfg) {
   LaunchCfg one = cfg;
   one.ctas = 1;
-  return launch(barrier_kernel, one, 32, c);
+  return launch("barrier_kernel", barrier_kernel, one, 32, c);
 }
 
 }  // namespace dev

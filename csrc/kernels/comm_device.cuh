@@ -52,6 +52,7 @@ struct DevComm {
   unsigned long long half_bytes; // size of one arena half
   unsigned long long timeout_ns;
   TimelineBuf* tl;               // device timeline, or nullptr (off)
+  unsigned long long arena_limit; // MCCL_DEBUG_BOUNDS: usable bytes of an arena (canaries start here); 0 = checks off
 };
 
 // ---- point-to-point (send / recv) ----
@@ -80,7 +81,7 @@ struct P2PComm {
 };
 constexpr int kP2PMaxCtas = 16;
 
-enum Phase : int { PH_BARRIER = 1, PH_PUSH = 2, PH_REDUCE = 3, PH_GATHER = 4, PH_RING = 5, PH_TREE = 6, PH_NVLS = 7, PH_SEND = 8, PH_RECV = 9 };
+enum Phase : int { PH_BARRIER = 1, PH_PUSH = 2, PH_REDUCE = 3, PH_GATHER = 4, PH_RING = 5, PH_TREE = 6, PH_NVLS = 7, PH_SEND = 8, PH_RECV = 9, PH_BOUNDS = 10 };
 
 __host__ __device__ inline int encode_status(int phase, int peer) { return (1 << 30) | (phase << 8) | (peer & 0xff); }
 
@@ -147,6 +148,19 @@ __device__ __forceinline__ void report_timeout(const DevComm& c, int vr, int pha
   volatile int* s = c.status[vr];
   if (*s == 0) *s = encode_status(phase, peer);
   __threadfence_system();
+}
+
+// MCCL_DEBUG_BOUNDS: every kernel states, before its first access, the last arena byte (exclusive) it will
+// touch on any rank.  When that lies beyond the arena the kernel records a violation in the status word
+// (phase "bounds", peer field = this rank) and returns without dereferencing anything, instead of writing
+// into whatever follows the arena in the peers' address spaces.
+__device__ __forceinline__ bool bounds_violation(const DevComm& c, int vr, unsigned long long arena_end) {
+  if (c.arena_limit == 0) return false;
+  // the launch works inside one half: [half * half_bytes, (half + 1) * half_bytes)
+  const unsigned long long half_begin = (c.state[vr]->seq & 1u) * c.half_bytes;
+  if (arena_end <= half_begin + c.half_bytes && arena_end <= c.arena_limit) return false;
+  if (threadIdx.x == 0) report_timeout(c, vr, PH_BOUNDS, c.rank_base + vr);
+  return true;
 }
 
 // Signals `peer` (its flag for this CTA and this source rank becomes `value`).

@@ -8,6 +8,7 @@
 // that reduce two local buffers.  Grid-stride over 16-byte packs with a scalar
 // path for unaligned pointers and the tail, mirroring the reference's
 // vector / scalar split (shaders.metal:159-187).
+#include "../core/launch.hpp"
 #include "collectives.hpp"
 #include "comm_device.cuh"
 
@@ -104,22 +105,22 @@ int grid_for(long long n, int elems_per_pack) {
 
 cudaError_t launch_reduce2(ElemType t, int op, void* dst, const void* src, long long n, cudaStream_t stream) {
   if (n <= 0) return cudaSuccess;
-  MCCL_EW_DISPATCH(t, (reduce2_kernel<T><<<grid_for(n, 16 / sizeof(T)), kEwThreads, 0, stream>>>(
+  MCCL_EW_DISPATCH(t, (MCCL_LAUNCH(reduce2_kernel<T>, grid_for(n, 16 / sizeof(T)), kEwThreads, 0, stream, 
                           static_cast<T*>(dst), static_cast<const T*>(src), n, op)));
-  return cudaGetLastError();
+  return ::mccl::launch_status();
 }
 
 cudaError_t launch_scale(ElemType t, void* buf, long long n, float scale, cudaStream_t stream) {
   if (n <= 0) return cudaSuccess;
-  MCCL_EW_DISPATCH(t, (scale_kernel<T><<<grid_for(n, 16 / sizeof(T)), kEwThreads, 0, stream>>>(static_cast<T*>(buf), n, scale)));
-  return cudaGetLastError();
+  MCCL_EW_DISPATCH(t, (MCCL_LAUNCH(scale_kernel<T>, grid_for(n, 16 / sizeof(T)), kEwThreads, 0, stream, static_cast<T*>(buf), n, scale)));
+  return ::mccl::launch_status();
 }
 
 cudaError_t launch_reduce2_scale(ElemType t, void* dst, const void* src, long long n, float scale, cudaStream_t stream) {
   if (n <= 0) return cudaSuccess;
-  MCCL_EW_DISPATCH(t, (reduce2_scale_kernel<T><<<grid_for(n, 16 / sizeof(T)), kEwThreads, 0, stream>>>(
+  MCCL_EW_DISPATCH(t, (MCCL_LAUNCH(reduce2_scale_kernel<T>, grid_for(n, 16 / sizeof(T)), kEwThreads, 0, stream, 
                           static_cast<T*>(dst), static_cast<const T*>(src), n, scale)));
-  return cudaGetLastError();
+  return ::mccl::launch_status();
 }
 
 }  // namespace dev

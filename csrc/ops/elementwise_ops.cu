@@ -2,6 +2,7 @@
 // AdamW, softmax cross entropy (forward + backward in one pass), transpose,
 // casts and the GELU derivative.  Every kernel moves 16 bytes per access and
 // reads each operand once from HBM (re-reads of a row hit L1/L2).
+#include "../core/launch.hpp"
 #include <atomic>
 
 #include "ops.hpp"
@@ -235,10 +236,10 @@ cudaError_t norm_fwd(const __nv_bfloat16* x, const float* w, const float* b, __n
                      int rows, int dim, float eps, cudaStream_t stream) {
   if (dim % 8 != 0) return cudaErrorNotSupported;
   const int blocks = (rows + 7) / 8;
-  if (b) norm_fwd_kernel<true><<<blocks, 256, 0, stream>>>(x, w, b, y, mean, rstd, rows, dim, eps);
-  else norm_fwd_kernel<false><<<blocks, 256, 0, stream>>>(x, w, b, y, mean, rstd, rows, dim, eps);
+  if (b) MCCL_LAUNCH(norm_fwd_kernel<true>, blocks, 256, 0, stream, x, w, b, y, mean, rstd, rows, dim, eps);
+  else MCCL_LAUNCH(norm_fwd_kernel<false>, blocks, 256, 0, stream, x, w, b, y, mean, rstd, rows, dim, eps);
   count_launch();
-  return cudaGetLastError();
+  return ::mccl::launch_status();
 }
 
 cudaError_t norm_bwd(const __nv_bfloat16* dy, const __nv_bfloat16* x, const float* w, const float* mean, const float* rstd,
@@ -246,22 +247,22 @@ cudaError_t norm_bwd(const __nv_bfloat16* dy, const __nv_bfloat16* x, const floa
                      cudaStream_t stream, const __nv_bfloat16* dx_add) {
   if (dim % 8 != 0) return cudaErrorNotSupported;
   const int blocks = (rows + 7) / 8;
-  if (layernorm) norm_bwd_dx_kernel<true><<<blocks, 256, 0, stream>>>(dy, x, w, mean, rstd, dx, dx_add, rows, dim);
-  else norm_bwd_dx_kernel<false><<<blocks, 256, 0, stream>>>(dy, x, w, mean, rstd, dx, dx_add, rows, dim);
+  if (layernorm) MCCL_LAUNCH(norm_bwd_dx_kernel<true>, blocks, 256, 0, stream, dy, x, w, mean, rstd, dx, dx_add, rows, dim);
+  else MCCL_LAUNCH(norm_bwd_dx_kernel<false>, blocks, 256, 0, stream, dy, x, w, mean, rstd, dx, dx_add, rows, dim);
   const int slabs = colsum_slabs(rows);
   dim3 grid((dim + 255) / 256, slabs);
   if (!scratch) {
     // no scratch: dw / db accumulate the slab sums atomically (they must hold the value to add to)
-    colsum_partial_kernel<true><<<grid, 256, 0, stream>>>(dy, x, mean, rstd, dw, layernorm ? db : nullptr, rows, dim, 1);
+    MCCL_LAUNCH(colsum_partial_kernel<true>, grid, 256, 0, stream, dy, x, mean, rstd, dw, layernorm ? db : nullptr, rows, dim, 1);
     count_launch(2);
-    return cudaGetLastError();
+    return ::mccl::launch_status();
   }
   float* part_w = scratch;
   float* part_b = layernorm ? scratch + static_cast<size_t>(slabs) * dim : nullptr;
-  colsum_partial_kernel<true><<<grid, 256, 0, stream>>>(dy, x, mean, rstd, part_w, part_b, rows, dim, 0);
-  colsum_final_kernel<<<(dim + 31) / 32, 256, 0, stream>>>(part_w, part_b, dw, layernorm ? db : nullptr, slabs, dim);
+  MCCL_LAUNCH(colsum_partial_kernel<true>, grid, 256, 0, stream, dy, x, mean, rstd, part_w, part_b, rows, dim, 0);
+  MCCL_LAUNCH(colsum_final_kernel, (dim + 31) / 32, 256, 0, stream, part_w, part_b, dw, layernorm ? db : nullptr, slabs, dim);
   count_launch(3);
-  return cudaGetLastError();
+  return ::mccl::launch_status();
 }
 
 cudaError_t colsum_bf16(const __nv_bfloat16* in, float* out, float* scratch, int rows, int dim, cudaStream_t stream) {
@@ -269,14 +270,14 @@ cudaError_t colsum_bf16(const __nv_bfloat16* in, float* out, float* scratch, int
   const int slabs = colsum_slabs(rows);
   dim3 grid((dim + 255) / 256, slabs);
   if (!scratch) {
-    colsum_partial_kernel<false><<<grid, 256, 0, stream>>>(in, nullptr, nullptr, nullptr, nullptr, out, rows, dim, 1);
+    MCCL_LAUNCH(colsum_partial_kernel<false>, grid, 256, 0, stream, in, nullptr, nullptr, nullptr, nullptr, out, rows, dim, 1);
     count_launch();
-    return cudaGetLastError();
+    return ::mccl::launch_status();
   }
-  colsum_partial_kernel<false><<<grid, 256, 0, stream>>>(in, nullptr, nullptr, nullptr, nullptr, scratch, rows, dim, 0);
-  colsum_final_kernel<<<(dim + 31) / 32, 256, 0, stream>>>(nullptr, scratch, nullptr, out, slabs, dim);
+  MCCL_LAUNCH(colsum_partial_kernel<false>, grid, 256, 0, stream, in, nullptr, nullptr, nullptr, nullptr, scratch, rows, dim, 0);
+  MCCL_LAUNCH(colsum_final_kernel, (dim + 31) / 32, 256, 0, stream, nullptr, scratch, nullptr, out, slabs, dim);
   count_launch(2);
-  return cudaGetLastError();
+  return ::mccl::launch_status();
 }
 
 // ------------------------------------------------------------------ AdamW --
@@ -337,10 +338,10 @@ cudaError_t adamw_flat(float* p, float* g, float* m, float* v, __nv_bfloat16* p1
   long long blocks = (n4 + 255) / 256;
   if (blocks > 148 * 8) blocks = 148 * 8;
   if (blocks < 1) blocks = 1;
-  adamw_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(p, g, m, v, p16, n4, n, lr, beta1, beta2, eps, wd, step, grad_scale,
-                                                             zero_grad ? 1 : 0);
+  MCCL_LAUNCH(adamw_kernel, static_cast<int>(blocks), 256, 0, stream, p, g, m, v, p16, n4, n, lr, beta1, beta2, eps, wd, step, grad_scale,
+              zero_grad ? 1 : 0);
   count_launch();
-  return cudaGetLastError();
+  return ::mccl::launch_status();
 }
 
 // ---------------------------------------------------------- cross entropy --
@@ -413,9 +414,9 @@ __global__ void __launch_bounds__(512) ce_kernel(__nv_bfloat16* __restrict__ log
 cudaError_t cross_entropy_fwd_bwd(__nv_bfloat16* logits, const long long* targets, float* loss_rows, int rows, int vocab,
                                   float grad_scale, cudaStream_t stream) {
   if (vocab % 8 != 0 || (reinterpret_cast<uintptr_t>(logits) & 15u)) return cudaErrorNotSupported;
-  ce_kernel<<<rows, 512, 0, stream>>>(logits, targets, loss_rows, vocab, grad_scale);
+  MCCL_LAUNCH(ce_kernel, rows, 512, 0, stream, logits, targets, loss_rows, vocab, grad_scale);
   count_launch();
-  return cudaGetLastError();
+  return ::mccl::launch_status();
 }
 
 // -------------------------------------------------------------- transpose --
@@ -445,9 +446,9 @@ __global__ void __launch_bounds__(256) transpose_kernel(const __nv_bfloat16* __r
 
 cudaError_t transpose_bf16(const __nv_bfloat16* in, __nv_bfloat16* out, int rows, int cols, cudaStream_t stream) {
   dim3 grid((cols + 63) / 64, (rows + 63) / 64);
-  transpose_kernel<<<grid, 256, 0, stream>>>(in, out, rows, cols);
+  MCCL_LAUNCH(transpose_kernel, grid, 256, 0, stream, in, out, rows, cols);
   count_launch();
-  return cudaGetLastError();
+  return ::mccl::launch_status();
 }
 
 // ------------------------------------------------------------------ casts --
@@ -472,9 +473,9 @@ cudaError_t cast_f32_bf16(const float* in, __nv_bfloat16* out, long long n, cuda
   long long blocks = (n / 4 + 255) / 256;
   if (blocks > 148 * 8) blocks = 148 * 8;
   if (blocks < 1) blocks = 1;
-  cast_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(in, out, n);
+  MCCL_LAUNCH(cast_kernel, static_cast<int>(blocks), 256, 0, stream, in, out, n);
   count_launch();
-  return cudaGetLastError();
+  return ::mccl::launch_status();
 }
 
 // ------------------------------------------------------------- GELU bwd ---
@@ -501,9 +502,9 @@ cudaError_t gelu_bwd(const __nv_bfloat16* dy, const __nv_bfloat16* z, __nv_bfloa
   long long blocks = (n / 8 + 255) / 256;
   if (blocks > 148 * 8) blocks = 148 * 8;
   if (blocks < 1) blocks = 1;
-  gelu_bwd_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(dy, z, dz, n / 8);
+  MCCL_LAUNCH(gelu_bwd_kernel, static_cast<int>(blocks), 256, 0, stream, dy, z, dz, n / 8);
   count_launch();
-  return cudaGetLastError();
+  return ::mccl::launch_status();
 }
 
 // ------------------------------------------------------------ embedding ---
@@ -564,18 +565,18 @@ cudaError_t embed_fwd(const long long* ids, const float* tok, const float* pos, 
                       int vocab, cudaStream_t stream) {
   if (dim % 8 != 0 || tokens <= 0 || seq <= 0) return cudaErrorNotSupported;
   const long long n8 = static_cast<long long>(tokens) * (dim / 8);
-  embed_fwd_kernel<<<embed_blocks(n8), 256, 0, stream>>>(ids, tok, pos, y, n8, seq, dim / 8, vocab);
+  MCCL_LAUNCH(embed_fwd_kernel, embed_blocks(n8), 256, 0, stream, ids, tok, pos, y, n8, seq, dim / 8, vocab);
   count_launch();
-  return cudaGetLastError();
+  return ::mccl::launch_status();
 }
 
 cudaError_t embed_bwd(const long long* ids, const __nv_bfloat16* dy, float* dtok, float* dpos, int tokens, int seq, int dim,
                       int vocab, cudaStream_t stream) {
   if (dim % 8 != 0 || tokens <= 0 || seq <= 0) return cudaErrorNotSupported;
   const long long n8 = static_cast<long long>(tokens) * (dim / 8);
-  embed_bwd_kernel<<<embed_blocks(n8), 256, 0, stream>>>(ids, dy, dtok, dpos, n8, seq, dim / 8, vocab);
+  MCCL_LAUNCH(embed_bwd_kernel, embed_blocks(n8), 256, 0, stream, ids, dy, dtok, dpos, n8, seq, dim / 8, vocab);
   count_launch();
-  return cudaGetLastError();
+  return ::mccl::launch_status();
 }
 
 }  // namespace ops
@@ -596,7 +597,9 @@ namespace {
 static __device__ __align__(256) float g_noalloc_scratch[MCCL_NOALLOC_SCRATCH_FLOATS];
 
 constexpr int kNoallocMaxDevices = 64;
-float* g_noalloc_scratch_ptr[kNoallocMaxDevices] = {};
+// Filled once per device; an atomic pointer because two threads may make their first call at the same time
+// (both would store the same address, but an unsynchronised store is still a data race).
+std::atomic<float*> g_noalloc_scratch_ptr[kNoallocMaxDevices];
 thread_local char t_noalloc_error[256] = "";
 
 // Device address of the scratch array on the current device (looked up on first use).
@@ -608,17 +611,28 @@ float* noalloc_scratch_for_current_device() {
                   rc == cudaSuccess ? "index out of range" : cudaGetErrorString(rc));
     return nullptr;
   }
-  if (!g_noalloc_scratch_ptr[device]) {
-    float* ptr = nullptr;
+  float* ptr = g_noalloc_scratch_ptr[device].load(std::memory_order_acquire);
+  if (!ptr) {
     rc = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_noalloc_scratch);
     if (rc != cudaSuccess || !ptr) {
       std::snprintf(t_noalloc_error, sizeof(t_noalloc_error), "cudaGetSymbolAddress failed on device %d: %s", device,
                     cudaGetErrorString(rc));
       return nullptr;
     }
-    g_noalloc_scratch_ptr[device] = ptr;
+    g_noalloc_scratch_ptr[device].store(ptr, std::memory_order_release);
   }
-  return g_noalloc_scratch_ptr[device];
+  return ptr;
+}
+
+// True when `p` is device memory of `device` (or memory CUDA cannot classify, which is let through).
+bool noalloc_on_device(const void* p, int device) {
+  cudaPointerAttributes attr;
+  if (cudaPointerGetAttributes(&attr, p) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return true;
+  }
+  if (attr.type == cudaMemoryTypeDevice) return attr.device == device;
+  return attr.type != cudaMemoryTypeHost;   // pinned host memory is not what the kernels expect
 }
 
 }  // namespace
@@ -632,15 +646,31 @@ extern "C" int mccl_colsum_bf16_noalloc(const void* in_bf16, float* out, int row
                   "bad argument: need non-null pointers, rows > 0, dim a positive multiple of 8 and a 16-byte aligned input");
     return MCCL_NOALLOC_BAD_ARGUMENT;
   }
-  const long long need = static_cast<long long>(mccl::ops::colsum_slabs(rows)) * dim;
+  const long long slabs = mccl::ops::colsum_slabs(rows);
+  const long long need = slabs * dim;
   if (need > MCCL_NOALLOC_SCRATCH_FLOATS) {
     std::snprintf(t_noalloc_error, sizeof(t_noalloc_error),
                   "problem too large for the fixed scratch array: ceil(rows/64)*dim = %lld floats, limit %d", need,
                   MCCL_NOALLOC_SCRATCH_FLOATS);
     return MCCL_NOALLOC_TOO_LARGE;
   }
+  if (slabs > MCCL_NOALLOC_MAX_SLABS) {
+    // many rows of a narrow matrix: the partial sums would fit, but one grid dimension of the first stage is the
+    // number of slabs, and that dimension is limited to 65535
+    std::snprintf(t_noalloc_error, sizeof(t_noalloc_error),
+                  "problem too large: ceil(rows/64) = %lld row slabs, limit %d (rows <= %d)", slabs, MCCL_NOALLOC_MAX_SLABS,
+                  MCCL_NOALLOC_MAX_SLABS * 64);
+    return MCCL_NOALLOC_TOO_LARGE;
+  }
   float* scratch = noalloc_scratch_for_current_device();
   if (!scratch) return MCCL_NOALLOC_CUDA_ERROR;
+  int device = -1;
+  cudaGetDevice(&device);
+  if (!noalloc_on_device(in_bf16, device) || !noalloc_on_device(out, device)) {
+    std::snprintf(t_noalloc_error, sizeof(t_noalloc_error),
+                  "bad argument: in and out must be device memory of the current device (%d); the scratch array used is that device's", device);
+    return MCCL_NOALLOC_BAD_ARGUMENT;
+  }
   cudaError_t rc = mccl::ops::colsum_bf16(static_cast<const __nv_bfloat16*>(in_bf16), out, scratch, rows, dim,
                                           static_cast<cudaStream_t>(stream));
   if (rc != cudaSuccess) {

@@ -15,6 +15,7 @@
 //                       epilogue stores each tile into its owner's staging slot
 // Tiles are visited chunk by chunk starting with this rank's own chunk, so
 // compute on data that is already local overlaps the NVLink transfers.
+#include "../core/launch.hpp"
 #include "gemm_common.cuh"
 #include "gemm_persistent.cuh"
 
@@ -747,9 +748,9 @@ no_split:
   int gemm_ctas = ctas - f.copy_ctas;
   if (gemm_ctas < 1) return cudaErrorInvalidValue;
   if (tiles < gemm_ctas) gemm_ctas = tiles;
-  gemm_persistent_kernel<BN, STAGES, kAMn, kBMn><<<gemm_ctas + f.copy_ctas, 192, L::kTotal, stream>>>(ma, mb, g, f);
+  MCCL_LAUNCH((gemm_persistent_kernel<BN, STAGES, kAMn, kBMn>), gemm_ctas + f.copy_ctas, 192, L::kTotal, stream, ma, mb, g, f);
   count_launch();
-  return cudaGetLastError();
+  return ::mccl::launch_status();
 }
 
 }  // namespace
@@ -759,8 +760,8 @@ int gemm_cta_limit() { return g_gemm_cta_limit.load(std::memory_order_relaxed); 
 int gemm_sm_count() { return sm_count(); }
 
 cudaError_t launch_bump_epoch(uint32_t* epoch, uint32_t* zeroed, cudaStream_t stream) {
-  bump_epoch_kernel<<<1, 1, 0, stream>>>(epoch, zeroed);
-  return cudaGetLastError();
+  MCCL_LAUNCH(bump_epoch_kernel, 1, 1, 0, stream, epoch, zeroed);
+  return ::mccl::launch_status();
 }
 
 cudaError_t launch_gemm_persistent(const GemmArgs& a, const FusedDev& f, int max_ctas, cudaStream_t stream) {

@@ -15,6 +15,7 @@
 // The reference has no GEMM of its own (no tensor-core code at all); this
 // kernel exists for the model operators and as the core the fused
 // all-gather→GEMM / GEMM→reduce-scatter tensor-parallel kernels build on.
+#include "../core/launch.hpp"
 #include "gemm_common.cuh"
 #include "gemm_persistent.cuh"
 
@@ -193,9 +194,9 @@ cudaError_t launch_cfg(const GemmArgs& a, cudaStream_t stream) {
   if (!g.err) return unsupported("no device error word");
   g.tl = nullptr;
   dim3 grid((a.n + BN - 1) / BN, (a.m + BM - 1) / BM);
-  gemm_bf16_kernel<BN, STAGES, kAMn, kBMn><<<grid, 192, L::kTotal, stream>>>(ma, mb, g);
+  MCCL_LAUNCH((gemm_bf16_kernel<BN, STAGES, kAMn, kBMn>), grid, 192, L::kTotal, stream, ma, mb, g);
   count_launch();
-  return cudaGetLastError();
+  return ::mccl::launch_status();
 }
 
 }  // namespace

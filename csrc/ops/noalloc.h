@@ -20,8 +20,15 @@
  * Rules for callers
  *  - `in` (bf16, 16-byte aligned) and `out` (fp32) are device pointers the
  *    caller owns; dim must be a multiple of 8.
- *  - ceil(rows / 64) * dim must not exceed MCCL_NOALLOC_SCRATCH_FLOATS; larger
- *    problems are refused with MCCL_NOALLOC_TOO_LARGE and nothing is launched.
+ *  - ceil(rows / 64) * dim must not exceed MCCL_NOALLOC_SCRATCH_FLOATS and
+ *    ceil(rows / 64) must not exceed MCCL_NOALLOC_MAX_SLABS (a grid-dimension
+ *    limit that very long, narrow matrices reach first); larger problems are
+ *    refused with MCCL_NOALLOC_TOO_LARGE and nothing is launched.
+ *  - `in`, `out` and `stream` must belong to the device that is current when
+ *    the call is made: the scratch array used is the current device's copy,
+ *    and a kernel given another device's pointers would read or write the
+ *    wrong memory.  Pointers that CUDA reports as another device's (or as
+ *    host memory) are refused with MCCL_NOALLOC_BAD_ARGUMENT.
  *  - The first call on a device looks up the device address of the array (no
  *    allocation, but a runtime query): make that first call before any stream
  *    capture begins on that device.
@@ -40,10 +47,11 @@ extern "C" {
 #endif
 
 #define MCCL_NOALLOC_SCRATCH_FLOATS (1 << 20)
+#define MCCL_NOALLOC_MAX_SLABS 65535
 
 enum {
   MCCL_NOALLOC_OK = 0,
-  MCCL_NOALLOC_BAD_ARGUMENT = -1,  /* null pointer, dim not a multiple of 8, misaligned input */
+  MCCL_NOALLOC_BAD_ARGUMENT = -1,  /* null pointer, dim not a multiple of 8, misaligned input, memory of another device */
   MCCL_NOALLOC_TOO_LARGE = -2,     /* partial sums would not fit the fixed array */
   MCCL_NOALLOC_CUDA_ERROR = -3     /* a CUDA call failed; see mccl_noalloc_last_error() */
 };

@@ -4,7 +4,10 @@
 
 #include <algorithm>
 #include <cstring>
+#include <chrono>
 #include <mutex>
+#include <thread>
+#include <vector>
 
 #include "../core/errors.hpp"
 #include "../core/log.hpp"
@@ -47,8 +50,34 @@ int to_dev_op(RedOp op, DType t) {
   return 0;
 }
 
+constexpr size_t kCanaryBytes = 512;
+
+// "rank=1,skip_signals=1,after=2,delay_ms=50": comma-separated key=value pairs, unknown keys are an error.
+void parse_fault_spec(const std::string& spec, int* rank, int* skip, long long* after, int* delay_ms) {
+  size_t b = 0;
+  while (b < spec.size()) {
+    size_t e = spec.find(',', b);
+    if (e == std::string::npos) e = spec.size();
+    const std::string kv = spec.substr(b, e - b);
+    b = e + 1;
+    if (kv.empty()) continue;
+    const size_t eq = kv.find('=');
+    MCCL_CHECK(eq != std::string::npos, "MCCL_FAULT_INJECT: expected key=value, got '" << kv << "'");
+    const std::string k = kv.substr(0, eq);
+    const long long v = std::atoll(kv.c_str() + eq + 1);
+    if (k == "rank") *rank = static_cast<int>(v);
+    else if (k == "skip_signals") *skip = static_cast<int>(v);
+    else if (k == "after") *after = v;
+    else if (k == "delay_ms") *delay_ms = static_cast<int>(v);
+    else MCCL_CHECK(false, "MCCL_FAULT_INJECT: unknown key '" << k << "' (rank, skip_signals, after, delay_ms)");
+  }
+}
+
 const char* phase_name(int ph) {
   switch (ph) {
+    case dev::PH_SEND: return "send";
+    case dev::PH_RECV: return "recv";
+    case dev::PH_BOUNDS: return "bounds";
     case dev::PH_BARRIER: return "barrier";
     case dev::PH_PUSH: return "push";
     case dev::PH_REDUCE: return "reduce";
@@ -74,6 +103,8 @@ struct DeviceComm::Impl {
   size_t half_bytes = 0;
   unsigned long long timeout_ns = 0;
   int max_ctas = 64;
+  bool debug_bounds = false;  // MCCL_DEBUG_BOUNDS: kernels check their arena extent, canaries behind the arena
+  unsigned long long debug_limit = 0;  // tests: pretend the arena ends here, so that the device-side check trips
   int threads = 0;         // threads per collective CTA, 0 = kernel default
   int64_t nvls_above = 0;  // AUTO uses staged NVLS at or above this many wire bytes (0 = never)
   // Launch ordering across streams: the arena halves, flags and epochs are shared by every launch of this
@@ -106,10 +137,34 @@ struct DeviceComm::Impl {
     last_stream = s;
     have_last = true;
   }
+  // Host-made faults (MCCL_FAULT_INJECT, see parse_fault_spec): applied on the rank they name, at the
+  // collective they name, from the host side of the launch.  Nothing here makes a GPU fault or hang: a
+  // skipped signal makes the peers' bounded waits run out, a delay makes a rank late.
+  struct FaultSpec {
+    int rank = -1;            // rank the fault applies to (-1: no fault configured)
+    int skip_signals = 0;     // withhold the signals of this many collectives ...
+    long long after = 0;      // ... starting with collective number `after` (0-based) of this communicator
+    int delay_ms = 0;         // sleep this long on the host before every launch from `after` on
+    bool armed = false;
+  } fault;
+  long long collectives = 0;
+  DeviceComm* owner = nullptr;
+  void apply_fault(cudaStream_t s) {
+    const long long n = collectives++;
+    if (fault.rank < 0 || owner == nullptr || owner->rank() != fault.rank || n < fault.after || capturing(s)) return;
+    if (fault.delay_ms > 0) std::this_thread::sleep_for(std::chrono::milliseconds(fault.delay_ms));
+    if (fault.skip_signals > 0 && !fault.armed) {
+      fault.armed = true;
+      owner->inject_skip_signals(fault.skip_signals);
+    }
+  }
   struct Ordered {   // scope of one public collective call
     Impl* impl;
     cudaStream_t s;
-    Ordered(Impl* i, void* stream) : impl(i), s(static_cast<cudaStream_t>(stream)) { impl->order_before(s); }
+    Ordered(Impl* i, void* stream) : impl(i), s(static_cast<cudaStream_t>(stream)) {
+      impl->apply_fault(s);
+      impl->order_before(s);
+    }
     ~Ordered() { impl->order_after(s); }
   };
 
@@ -129,6 +184,7 @@ struct DeviceComm::Impl {
     c.half_bytes = half_bytes;
     c.timeout_ns = timeout_ns;
     c.tl = timeline_device_ptr();
+    c.arena_limit = debug_bounds ? (debug_limit ? debug_limit : 2ull * half_bytes) : 0ull;
     return c;
   }
 };
@@ -148,10 +204,27 @@ DeviceComm::DeviceComm(int world, int device, const EnvConfig& cfg)
 
 void DeviceComm::init_common() {
   impl_.reset(new Impl());
+  impl_->owner = this;
+  if (!cfg_.fault_inject.empty())
+    parse_fault_spec(cfg_.fault_inject, &impl_->fault.rank, &impl_->fault.skip_signals, &impl_->fault.after, &impl_->fault.delay_ms);
   MCCL_CUDA_CHECK(cudaSetDevice(device_));
   size_t arena = static_cast<size_t>(std::max<int64_t>(cfg_.arena_bytes, 2 << 20));
   impl_->arena = mesh_->alloc(arena, /*want_multicast=*/true);
+  impl_->debug_bounds = cfg_.debug_bounds;
   impl_->half_bytes = (impl_->arena->bytes / 2) / 256 * 256;
+  if (impl_->debug_bounds) {
+    // Debug layout: both halves are poisoned (0xFF bytes read as NaN in every float type, so a kernel that
+    // consumes staging nobody wrote shows up in the results) and the last kCanaryBytes of the allocation hold
+    // a pattern that check_status() verifies: a write past the second half lands there first.
+    impl_->half_bytes = ((impl_->arena->bytes - kCanaryBytes) / 2) / 256 * 256;
+    MCCL_CUDA_CHECK(cudaMemset(impl_->arena->ptrs[rank_], 0xFF, 2 * impl_->half_bytes));
+    MCCL_CUDA_CHECK(cudaMemset(static_cast<char*>(impl_->arena->ptrs[rank_]) + 2 * impl_->half_bytes, 0xA5, kCanaryBytes));
+    if (nlocal_ > 1)
+      for (int v = 1; v < nlocal_; ++v) {
+        MCCL_CUDA_CHECK(cudaMemset(impl_->arena->ptrs[v], 0xFF, 2 * impl_->half_bytes));
+        MCCL_CUDA_CHECK(cudaMemset(static_cast<char*>(impl_->arena->ptrs[v]) + 2 * impl_->half_bytes, 0xA5, kCanaryBytes));
+      }
+  }
   impl_->pads = mesh_->alloc(static_cast<size_t>(dev::kChannels) * dev::kFlagWordsPerChannel * sizeof(uint32_t), false);
   impl_->p2p_slot = static_cast<size_t>(std::max<int64_t>(env::i64("MCCL_P2P_SLOT_MB", 4), 1)) << 20;
   if (nlocal_ > 1) impl_->p2p_slot = std::min<size_t>(impl_->p2p_slot, 1u << 20);
@@ -200,12 +273,37 @@ int DeviceComm::status() const {
 
 void DeviceComm::check_status() const {
   int s = status();
+  if (!s && impl_->debug_bounds) check_canaries();
   if (!s) return;
   int phase = (s >> 8) & 0xff, peer = s & 0xff;
+  MCCL_CHECK_T(phase != dev::PH_BOUNDS, ProtocolError,
+               "MCCL_DEBUG_BOUNDS: a collective kernel on rank " << peer << " was given arguments whose staging extent exceeds "
+                                                                 << "its arena half of " << impl_->half_bytes
+                                                                 << " bytes; it returned without touching memory");
   MCCL_CHECK_T(false, TimeoutError,
                "device wait timed out: rank " << rank_ << " waited for rank " << peer << " in phase '"
                                               << phase_name(phase) << "' longer than "
                                               << impl_->timeout_ns / 1000000ull << " ms; the group must be rebuilt");
+}
+
+void DeviceComm::check_canaries() const {
+  if (!impl_->debug_bounds) return;
+  MCCL_CUDA_CHECK(cudaSetDevice(device_));
+  MCCL_CUDA_CHECK(cudaDeviceSynchronize());
+  std::vector<unsigned char> host(kCanaryBytes);
+  for (int v = 0; v < nlocal_; ++v) {
+    const char* base = static_cast<const char*>(impl_->arena->ptrs[nlocal_ > 1 ? v : rank_]);
+    MCCL_CUDA_CHECK(cudaMemcpy(host.data(), base + 2 * impl_->half_bytes, kCanaryBytes, cudaMemcpyDeviceToHost));
+    for (size_t i = 0; i < kCanaryBytes; ++i)
+      MCCL_CHECK_T(host[i] == 0xA5, ProtocolError,
+                   "MCCL_DEBUG_BOUNDS: the canary behind the staging arena of rank " << (rank_ + v) << " was overwritten at byte "
+                                                                                   << i << " (a kernel wrote past its arena half)");
+  }
+}
+
+void DeviceComm::set_debug_arena_limit(size_t bytes) {
+  MCCL_CHECK(impl_->debug_bounds, "set_debug_arena_limit needs MCCL_DEBUG_BOUNDS=1");
+  impl_->debug_limit = bytes;
 }
 
 void DeviceComm::clear_status() { std::memset(impl_->status_host, 0, sizeof(int) * dev::kMaxRanks); }

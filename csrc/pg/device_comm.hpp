@@ -133,6 +133,12 @@ class DeviceComm {
   int status() const;
   // Throws TimeoutError with peer / phase decoded from the status word.
   void check_status() const;
+  // MCCL_DEBUG_BOUNDS=1 only: synchronises the device and verifies the pattern behind the staging arena.
+  void check_canaries() const;
+  bool debug_bounds() const { return cfg_.debug_bounds; }
+  // MCCL_DEBUG_BOUNDS=1 only, for tests: the kernels are told the arena ends after `bytes` (0 = its real end),
+  // which makes their extent check refuse launches the host-side checks let through.
+  void set_debug_arena_limit(size_t bytes);
   void clear_status();
   // Host-made fault for tests: this rank withholds its signals during the
   // next `count` collectives, so the peers' bounded waits run out.

@@ -3,6 +3,7 @@
 #include <cstdio>
 #include <exception>
 #include <functional>
+#include <stdexcept>
 #include <string>
 #include <vector>
 

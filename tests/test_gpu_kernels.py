@@ -286,3 +286,41 @@ def test_bounded_wait_reports_timeout_and_context_survives():
     # the context still works
     x = torch.ones(10, device="cuda")
     assert (x + x).sum().item() == 20
+
+
+def test_debug_bounds_poison_canaries_and_refusal(monkeypatch):
+    """MCCL_DEBUG_BOUNDS=1: the staging arena starts out poisoned and ends in a canary, results are unchanged,
+    and a kernel whose staging extent would leave its arena half records a violation and touches nothing."""
+    monkeypatch.setenv("MCCL_DEBUG_BOUNDS", "1")
+    C = _C()
+    c = C.DeviceComm(4, 0)
+    assert c.debug_bounds
+    for algo in ("oneshot", "twoshot", "ring", "tree"):
+        for n in (5, 4097, 1 << 18):
+            ins = _inputs(4, n, torch.float32, seed=n)
+            outs = [torch.empty_like(t) for t in ins]
+            c.allreduce(ins, outs, algo=algo)
+            torch.cuda.synchronize()
+            gold = _gold(ins, "sum")
+            assert not torch.isnan(outs[0]).any(), (algo, n)      # no poisoned staging was consumed
+            assert ((outs[0].double().cpu() - gold).abs().max() / gold.abs().max()).item() < 1e-5, (algo, n)
+    outs2 = [torch.empty(4 * 1000, device="cuda") for _ in range(4)]
+    c.allgather([torch.full((1000,), float(v), device="cuda") for v in range(4)], outs2)
+    torch.cuda.synchronize()
+    c.check_status()          # also verifies the canary behind the arena
+    c.check_canaries()
+    # pretend the arena is 64 KiB long: a 1 MiB two-shot needs more, so the kernel must refuse
+    c.set_debug_arena_limit(64 << 10)
+    ins = _inputs(4, 1 << 18, torch.float32, seed=3)
+    outs = [torch.full_like(t, -7.0) for t in ins]
+    c.allreduce(ins, outs, algo="twoshot")
+    torch.cuda.synchronize()
+    assert c.status() != 0
+    assert all((o == -7.0).all() for o in outs), "a refused kernel must not write its outputs"
+    with pytest.raises(Exception, match="MCCL_DEBUG_BOUNDS"):
+        c.check_status()
+    c.clear_status()
+    c.set_debug_arena_limit(0)
+    c.allreduce(ins, outs, algo="twoshot")
+    torch.cuda.synchronize()
+    c.check_status()

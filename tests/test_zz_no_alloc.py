@@ -39,11 +39,15 @@ def test_noalloc_colsum_matches_regular_entry_point_twice():
         torch.manual_seed(seed)
         x = torch.randn(rows, dim, device="cuda").bfloat16()
         out = torch.full((dim,), float("nan"), device="cuda")
+        torch.cuda.synchronize()
         before = torch.cuda.memory_allocated()
+        free_before, _ = torch.cuda.mem_get_info()      # the driver's own count: sees a cudaMalloc made inside the library too
         rc = lib.mccl_colsum_bf16_noalloc(x.data_ptr(), out.data_ptr(), rows, dim, stream)
         assert rc == 0, lib.mccl_noalloc_last_error()
         torch.cuda.synchronize()
         assert torch.cuda.memory_allocated() == before
+        free_after, _ = torch.cuda.mem_get_info()
+        assert free_after >= free_before, (free_before, free_after)   # nothing was taken from the device
         ref = C.colsum_bf16(x)
         torch.cuda.synchronize()
         err = ((out - ref).abs().max() / ref.abs().max().clamp_min(1e-6)).item()
@@ -60,6 +64,14 @@ def test_noalloc_colsum_refuses_what_does_not_fit():
     # ceil(rows / 64) * dim = 2^21 floats > 2^20: refused from the sizes alone, nothing is launched
     rc = lib.mccl_colsum_bf16_noalloc(x.data_ptr(), out.data_ptr(), 64 * 1024, 2048, None)
     assert rc == -2 and b"too large" in lib.mccl_noalloc_last_error()
+    # many rows of a narrow matrix: the partial sums would fit (78125 * 8 floats) but the slab count exceeds the
+    # grid-dimension limit; this, too, is refused up front with TOO_LARGE instead of failing at launch
+    rc = lib.mccl_colsum_bf16_noalloc(x.data_ptr(), out.data_ptr(), 5_000_000, 8, None)
+    assert rc == -2 and b"too large" in lib.mccl_noalloc_last_error()
     rc = lib.mccl_colsum_bf16_noalloc(x.data_ptr(), out.data_ptr(), 8, 12, None)
     assert rc == -1
+    # pinned host memory is not device memory of the current device
+    host = torch.zeros(8, 8, dtype=torch.bfloat16).pin_memory()
+    rc = lib.mccl_colsum_bf16_noalloc(host.data_ptr(), out.data_ptr(), 8, 8, None)
+    assert rc == -1 and b"current device" in lib.mccl_noalloc_last_error()
     torch.cuda.synchronize()
