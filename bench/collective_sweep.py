@@ -58,7 +58,10 @@ def main() -> None:
     ap.add_argument("--max-mb", type=float, default=1024.0)
     ap.add_argument("--min-kb", type=float, default=1.0)
     ap.add_argument("--ops", default="allreduce,allgather,reduce_scatter,alltoall")
-    ap.add_argument("--algos", default="oneshot,twoshot,ring,tree,nvls,symm,auto")
+    ap.add_argument("--algos", default="oneshot,twoshot,twoshot_push,ring,tree,nvls,symm,auto")
+    ap.add_argument("--size-step", type=int, default=2, help="ratio between consecutive message sizes")
+    ap.add_argument("--ctas", type=int, default=0, help="cap on CTAs per collective kernel (0 = default)")
+    ap.add_argument("--threads", type=int, default=0, help="threads per collective CTA (0 = default)")
     ap.add_argument("--dtypes", default="fp32,fp32+bf16wire,bf16")
     ap.add_argument("--out", default="")
     args = ap.parse_args()
@@ -71,6 +74,8 @@ def main() -> None:
     dist.init_process_group("mccl", rank=rank, world_size=world)
     nccl = dist.new_group(backend="nccl")
     comm = mccl_b200.get_backend().device_comm(local)
+    if args.ctas or args.threads:
+        comm.set_launch_shape(args.ctas, args.threads)
     warm = torch.ones(1024, device=device)
     dist.all_reduce(warm, group=nccl)
 
@@ -78,7 +83,7 @@ def main() -> None:
     s = int(args.min_kb * 1024)
     while s <= int(args.max_mb * (1 << 20)):
         sizes.append(s)
-        s *= 2
+        s *= max(args.size_step, 2)
     rows = []
     symm_cache = {}
     ops = args.ops.split(",")
@@ -133,8 +138,6 @@ def main() -> None:
                     variants.append(("mccl", lambda: comm.reduce_scatter([nxt()], [outs[0]], op="sum", wire=wire)))
                     variants.append(("nccl", lambda: dist.reduce_scatter_tensor(outs[0], nxt(), group=nccl)))
                 elif op == "alltoall":
-                    if nbytes // world > (comm.arena_bytes // 2 // world):
-                        continue
                     outs = [torch.empty(numel, dtype=dtype, device=device)]
                     sp = [[numel // world] * world]
                     variants.append(("mccl", lambda: comm.alltoallv([nxt()], [outs[0]], sp, sp)))
@@ -146,7 +149,8 @@ def main() -> None:
                     msg = numel * es * (world if op == "allgather" else 1)
                     busbw = msg / (us * 1e-6) / 1e9 * bus_factor(op, world)
                     row = {"op": op, "dtype": dt_name, "bytes": msg, "impl": name, "us": round(us, 2),
-                           "busbw_gbs": round(busbw, 2), "frac_of_900": round(busbw / NVLINK_GBS, 3), "world": world}
+                           "busbw_gbs": round(busbw, 2), "frac_of_900": round(busbw / NVLINK_GBS, 3), "world": world,
+                           "ctas": comm.max_ctas, "threads": comm.launch_threads}
                     rows.append(row)
                     if rank == 0:
                         print(json.dumps(row), flush=True)

@@ -51,6 +51,7 @@ def main() -> None:
     ap.add_argument("--configs", default="inline,shared256,sm8,sm16,sm24,sm16nvls")
     ap.add_argument("--out", default="")
     ap.add_argument("--no-timeline", action="store_true")
+    ap.add_argument("--gemm-shapes", action="store_true", help="also list the in-step time of every GEMM shape")
     args = ap.parse_args()
 
     import torch
@@ -116,7 +117,7 @@ def main() -> None:
             trainer.step(toks[0], tgts[0])
             torch.cuda.synchronize(device)
             recs = timeline.drain(local_rank)
-            summary = timeline.summarize(recs)
+            summary = timeline.summarize(recs, shapes=args.gemm_shapes)
         if rank == 0:
             head = {"config": name, "n_gpus": world, "model": args.model, "ms_per_step": round(best, 4),
                     "overlap": overlap, "comm_sms": comm_sms, "comm_threads": comm_threads, "wire": wire,

@@ -74,6 +74,7 @@ Algo parse_algo(const std::string& s) {
   if (s == "butterfly" || s == "twoshot") return Algo::BUTTERFLY;
   if (s == "oneshot") return Algo::ONESHOT;
   if (s == "nvls") return Algo::NVLS;
+  if (s == "twoshot_push" || s == "butterfly_push") return Algo::BUTTERFLY_PUSH;
   MCCL_CHECK(false, "unknown allreduce algorithm '" << s << "'");
   return Algo::AUTO;
 }
@@ -154,7 +155,10 @@ void bind_comm(py::module_& m) {
             return at::from_blob(static_cast<char*>(a->ptrs[r]) + byte_offset, shape, [a](void*) {}, opts);
           },
           py::arg("rank"), py::arg("byte_offset"), py::arg("shape"), py::arg("dtype"), py::arg("device"),
-          "View of rank `rank`'s block (as mapped in this process) as a tensor; the view keeps the allocation alive.");
+          "View of rank `rank`'s block (as mapped in this process) as a tensor; the view keeps the allocation alive.  For "
+          "rank != this rank the tensor aliases another GPU's memory: use it only with plain elementwise copies or this "
+          "package's own kernels, never as an operand of a library kernel (matmul, attention, ...), which may issue "
+          "cluster-multicast bulk loads that must not read a peer's memory.");
 
   py::class_<DeviceComm, std::shared_ptr<DeviceComm>>(m, "DeviceComm")
       .def(py::init([](int world, int device) { return std::make_shared<DeviceComm>(world, device, EnvConfig::from_env()); }),

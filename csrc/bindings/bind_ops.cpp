@@ -91,7 +91,7 @@ void bind_ops(py::module_& m) {
       "gemm_bf16",
       [](const at::Tensor& a, const at::Tensor& b, const c10::optional<at::Tensor>& bias, const std::string& epilogue,
          bool out_fp32, const c10::optional<at::Tensor>& out, bool accumulate, bool a_t, bool b_t,
-         const c10::optional<at::Tensor>& residual) {
+         const c10::optional<at::Tensor>& residual, const c10::optional<at::Tensor>& dgelu_z) {
         need_cuda(a, "gemm(a)");
         need_cuda(b, "gemm(b)");
         MCCL_CHECK_TENSOR(a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16, "gemm: operands must be bf16");
@@ -143,6 +143,12 @@ void bind_ops(py::module_& m) {
           MCCL_CHECK_TENSOR(residual->numel() == M * N && d.is_contiguous(), "gemm: residual must be a contiguous [M, N] tensor");
           g.residual = bf(*residual);
         }
+        if (dgelu_z.has_value() && dgelu_z->defined()) {
+          need(*dgelu_z, at::kBFloat16, "gemm(dgelu_z)");
+          MCCL_CHECK_TENSOR(dgelu_z->numel() == M * N && d.is_contiguous() && !out_fp32,
+                            "gemm: dgelu_z must be a contiguous [M, N] bf16 tensor and the output bf16");
+          g.dgelu_z = bf(*dgelu_z);
+        }
         cudaError_t rc = ops::gemm_bf16_tn(g, stream_of(a));
         MCCL_CHECK_T(rc == cudaSuccess, CudaError,
                      "gemm_bf16 [" << M << "x" << N << "x" << K << ", lda " << g.lda << ", ldb " << g.ldb << ", ldd " << g.ldd
@@ -151,7 +157,7 @@ void bind_ops(py::module_& m) {
       },
       py::arg("a"), py::arg("b"), py::arg("bias") = py::none(), py::arg("epilogue") = "none", py::arg("out_fp32") = false,
       py::arg("out") = py::none(), py::arg("accumulate") = false, py::arg("a_t") = false, py::arg("b_t") = false,
-      py::arg("residual") = py::none());
+      py::arg("residual") = py::none(), py::arg("dgelu_z") = py::none());
 
   m.def(
       "norm_fwd",

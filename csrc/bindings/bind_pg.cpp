@@ -61,6 +61,7 @@ void bind_pg(py::module_& m) {
               if (s == "butterfly" || s == "twoshot") return Algo::BUTTERFLY;
               if (s == "oneshot") return Algo::ONESHOT;
               if (s == "nvls") return Algo::NVLS;
+              if (s == "twoshot_push" || s == "butterfly_push") return Algo::BUTTERFLY_PUSH;
               MCCL_CHECK(false, "allreduce_with: unknown algorithm '" << s << "'");
               return Algo::AUTO;
             };

@@ -16,7 +16,7 @@
 
 namespace mccl {
 
-enum class Algo : int { AUTO = 0, RING, TREE, BUTTERFLY /* = two-shot */, ONESHOT, NVLS };
+enum class Algo : int { AUTO = 0, RING, TREE, BUTTERFLY /* = two-shot */, ONESHOT, NVLS, BUTTERFLY_PUSH /* two-shot, gather half pushed */ };
 enum class WireDtype : int { NATIVE = 0, BF16 };
 
 inline const char* algo_name(Algo a) {
@@ -27,6 +27,7 @@ inline const char* algo_name(Algo a) {
     case Algo::BUTTERFLY: return "butterfly";
     case Algo::ONESHOT: return "oneshot";
     case Algo::NVLS: return "nvls";
+    case Algo::BUTTERFLY_PUSH: return "twoshot_push";
   }
   return "?";
 }
@@ -76,6 +77,7 @@ inline Algo requested_algo() {
   if (s == "butterfly" || s == "twoshot") return Algo::BUTTERFLY;
   if (s == "oneshot") return Algo::ONESHOT;
   if (s == "nvls") return Algo::NVLS;
+  if (s == "twoshot_push" || s == "butterfly_push") return Algo::BUTTERFLY_PUSH;
   return Algo::TREE;
 }
 

@@ -1,6 +1,7 @@
 #include "launch.hpp"
 
 #include <atomic>
+#include <cstdlib>
 #include <mutex>
 
 #include "log.hpp"
@@ -43,6 +44,14 @@ cudaError_t launch_record(const char* kernel, const char* file, int line, dim3 g
                          << block.x << " smem " << smem << " stream " << static_cast<const void*>(stream));
   }
   return rc;
+}
+
+bool pdl_enabled() {
+  static const bool on = [] {
+    const char* v = std::getenv("MCCL_PDL");
+    return !(v && v[0] == '0');
+  }();
+  return on;
 }
 
 cudaError_t launch_status() {

@@ -30,7 +30,38 @@ std::map<std::string, uint64_t> launch_counts();
 void launch_counts_reset();
 uint64_t launch_total();
 
+// Programmatic dependent launch (sm_90+).  A kernel launched with MCCL_LAUNCH_PDL may begin while the kernel before
+// it in the stream is still draining: its CTAs become resident, do their set-up (barrier init, tensor-memory
+// allocation, descriptor prefetch, index arithmetic) and then block in pdl_wait() until every earlier kernel of the
+// stream has finished and its memory is visible.  Such a kernel must call pdl_wait() before its first access to
+// global memory, read or write.  pdl_trigger() tells the hardware that the kernels after this one may start their
+// set-up; kernels that never call it release their dependents when they exit.  MCCL_PDL=0 turns the launch attribute
+// off (the device calls are then no-ops), which is the switch for A/B timing.
+bool pdl_enabled();
+template <typename... KArgs, typename... Args>
+cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+#if defined(__CUDACC__)
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+#endif
+
 }  // namespace mccl
+
+#define MCCL_LAUNCH_PDL(kernel, grid, block, smem, stream, ...)                                                 \
+  (::mccl::launch_pdl((kernel), dim3(grid), dim3(block), static_cast<size_t>(smem), (stream), __VA_ARGS__),     \
+   ::mccl::launch_record(#kernel, __FILE__, __LINE__, dim3(grid), dim3(block), static_cast<size_t>(smem), (stream)))
 
 #define MCCL_LAUNCH(kernel, grid, block, smem, stream, ...)                                                     \
   ((kernel)<<<(grid), (block), (smem), (stream)>>>(__VA_ARGS__),                                               \

@@ -57,6 +57,9 @@ inline long long chunk_elems(long long numel, int world) {
 inline size_t twoshot_bytes(long long numel, int world, size_t wire_es) {
   return static_cast<size_t>(chunk_elems(numel, world)) * wire_es * static_cast<size_t>(world + 1);
 }
+inline size_t twoshot_push_bytes(long long numel, int world, size_t wire_es) {
+  return static_cast<size_t>(chunk_elems(numel, world)) * wire_es * static_cast<size_t>(2 * world);
+}
 inline size_t oneshot_bytes(long long numel, int world, size_t wire_es) {
   return static_cast<size_t>((numel + 15) / 16 * 16) * wire_es * static_cast<size_t>(world);
 }

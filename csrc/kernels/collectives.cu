@@ -68,6 +68,37 @@ __device__ __forceinline__ void cta_copy_bytes(char* dst, const char* src, unsig
   }
 }
 
+// Copies n bytes from src to up to kMaxRanks destinations (peers' memory): every 16-byte unit is loaded once and
+// stored to each destination, several units in flight per thread.  Stores to peers are posted, so this is the fast
+// direction over NVLink.  Destinations must be 16-byte aligned; an unaligned source takes the per-destination path.
+__device__ __forceinline__ void cta_push_bytes(char* const* dsts, int ndst, const char* src, unsigned long long n) {
+  if (n == 0 || ndst == 0) return;
+  if (!aligned16(src)) {
+    for (int d = 0; d < ndst; ++d) cta_copy_bytes(dsts[d], src, n);
+    return;
+  }
+  const unsigned long long vecs = n / 16;
+  constexpr int U = 4;
+  for (unsigned long long i0 = threadIdx.x; i0 < vecs; i0 += static_cast<unsigned long long>(blockDim.x) * U) {
+    uint4 v[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const unsigned long long i = i0 + static_cast<unsigned long long>(u) * blockDim.x;
+      if (i < vecs) v[u] = reinterpret_cast<const uint4*>(src)[i];
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const unsigned long long i = i0 + static_cast<unsigned long long>(u) * blockDim.x;
+      if (i >= vecs) continue;
+      for (int d = 0; d < ndst; ++d) reinterpret_cast<uint4*>(dsts[d])[i] = v[u];
+    }
+  }
+  for (unsigned long long b = vecs * 16 + threadIdx.x; b < n; b += blockDim.x) {
+    const char c = src[b];
+    for (int d = 0; d < ndst; ++d) dsts[d][b] = c;
+  }
+}
+
 // Byte range [begin, end) of an n-byte segment owned by this CTA, in 16-byte units.
 __device__ __forceinline__ void cta_byte_span(unsigned long long n, unsigned long long& begin, unsigned long long& end) {
   unsigned long long units = (n + 15) / 16;
@@ -220,6 +251,136 @@ __global__ void __launch_bounds__(kThreads) twoshot_kernel(DevComm c, CollArgs a
     else pull(std::integral_constant<int, 1>{}, std::integral_constant<int, kMaxRanks - 1>{});
     cta_end(c, vr, s, TL_ALLREDUCE);
   }
+}
+
+// ======================================================== two-shot, pushed ==
+// Same reduce-scatter as above, but the all-gather half is pushed too: the owner of a chunk stores the reduced
+// (wire-typed) chunk into every peer's arena and each rank then unpacks from its own arena.  Nothing is ever
+// loaded from a peer, and loads are the slow direction over NVLink (a load's round trip bounds how much a
+// thread can keep in flight, a store is posted).  Costs one more local pass and N instead of one result slots.
+template <typename T, typename W>
+__global__ void __launch_bounds__(kThreads) twoshot_push_kernel(DevComm c, CollArgs a) {
+  using PK = Pack<T, W>;
+  constexpr int E = PK::kElems;
+  using Acc = typename PK::Acc;
+  const int vr = blockIdx.y, rank = c.rank_base + vr, N = c.world;
+  CtaSync s = cta_begin(c, vr);
+  const T* in = static_cast<const T*>(a.in[vr]);
+  T* out = static_cast<T*>(a.out[vr]);
+  const long long per = a.per;
+  const long long total = a.numel;
+  const size_t slot_bytes = static_cast<size_t>(per) * sizeof(W);
+  const size_t recv_off = static_cast<size_t>(s.half) * c.half_bytes;
+  const size_t gath_off = recv_off + static_cast<size_t>(N) * slot_bytes;
+  if (bounds_violation(c, vr, gath_off + static_cast<size_t>(N) * slot_bytes)) {
+    cta_end(c, vr, s, TL_ALLREDUCE);
+    return;
+  }
+  long long pb, pe;
+  cta_span(per / E, pb, pe);
+  auto chunk_limit = [&](int p) -> long long {
+    long long lim = static_cast<long long>(p + 1) * per;
+    return lim < total ? lim : total;
+  };
+  // Phase 1: push my copy of chunk p to rank p.
+  constexpr int U = 4;
+  for (long long i0 = pb + threadIdx.x; i0 < pe; i0 += static_cast<long long>(blockDim.x) * U) {
+#pragma unroll 1
+    for (int k = 1; k < N; ++k) {
+      const int p = (rank + k) % N;
+      Acc v[U][E];
+      int nv[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long i = i0 + static_cast<long long>(u) * blockDim.x;
+        const long long e0 = static_cast<long long>(p) * per + i * E;
+        nv[u] = i < pe ? valid_in_pack(e0, chunk_limit(p), E) : 0;
+        if (nv[u] > 0) load_pack<T, E, Acc>(in + e0, v[u], nv[u], aligned16(in + e0));
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (nv[u] <= 0) continue;
+        const long long i = i0 + static_cast<long long>(u) * blockDim.x;
+        W* dst = reinterpret_cast<W*>(c.arena[p] + recv_off + static_cast<size_t>(rank) * slot_bytes) + i * E;
+        store_pack<W, E, Acc>(dst, v[u], E, true);
+      }
+    }
+  }
+  if (barrier_all(c, vr, rank, s, PH_PUSH)) {
+    cta_end(c, vr, s, TL_ALLREDUCE);
+    return;
+  }
+  // Phase 2: reduce chunk `rank`, keep it, and push the wire-typed result to every peer.
+  for (long long i = pb + threadIdx.x; i < pe; i += blockDim.x) {
+    const long long e0 = static_cast<long long>(rank) * per + i * E;
+    const int nv = valid_in_pack(e0, chunk_limit(rank), E);
+    if (nv <= 0) continue;
+    Acc acc[E];
+    load_pack<T, E, Acc>(in + e0, acc, nv, aligned16(in + e0));
+    uint4 slots[kMaxRanks];
+#pragma unroll
+    for (int src = 0; src < kMaxRanks; ++src)
+      if (src < N && src != rank)
+        slots[src] = ld16(c.arena[rank] + recv_off + static_cast<size_t>(src) * slot_bytes + static_cast<size_t>(i) * 16);
+#pragma unroll
+    for (int src = 0; src < kMaxRanks; ++src) {
+      if (src < N && src != rank) {
+        const W* w = reinterpret_cast<const W*>(&slots[src]);
+#pragma unroll
+        for (int e = 0; e < E; ++e) acc[e] = apply_op<Acc>(a.op, acc[e], static_cast<Acc>(Elem<W>::up(w[e])));
+      }
+    }
+    if (a.op == OP_AVG) {
+#pragma unroll
+      for (int e = 0; e < E; ++e) acc[e] = finish_avg<Acc>(acc[e], N, a.inv_world);
+    }
+    round_through_wire<T, W, E, Acc>(acc);
+    uint4 raw;
+    {
+      W* w = reinterpret_cast<W*>(&raw);
+#pragma unroll
+      for (int e = 0; e < E; ++e) w[e] = Elem<W>::down(static_cast<typename Elem<W>::Acc>(acc[e]));
+    }
+#pragma unroll
+    for (int k = 1; k < kMaxRanks; ++k) {
+      if (k < N) {
+        const int p = (rank + k) % N;
+        st16(c.arena[p] + gath_off + static_cast<size_t>(rank) * slot_bytes + static_cast<size_t>(i) * 16, raw);
+      }
+    }
+    store_pack<T, E, Acc>(out + e0, acc, nv, aligned16(out + e0));
+  }
+  if (barrier_all(c, vr, rank, s, PH_REDUCE)) {
+    cta_end(c, vr, s, TL_ALLREDUCE);
+    return;
+  }
+  // Phase 3: unpack the other ranks' chunks from my own arena.
+  for (int k = 1; k < N; ++k) {
+    const int p = (rank + k) % N;
+    const char* src = c.arena[rank] + gath_off + static_cast<size_t>(p) * slot_bytes;
+    for (long long i0 = pb + threadIdx.x; i0 < pe; i0 += static_cast<long long>(blockDim.x) * U) {
+      uint4 raw[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long i = i0 + static_cast<long long>(u) * blockDim.x;
+        if (i < pe) raw[u] = ld16(src + static_cast<size_t>(i) * 16);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long i = i0 + static_cast<long long>(u) * blockDim.x;
+        if (i >= pe) continue;
+        const long long e0 = static_cast<long long>(p) * per + i * E;
+        const int nv = valid_in_pack(e0, chunk_limit(p), E);
+        if (nv <= 0) continue;
+        Acc v[E];
+        const W* w = reinterpret_cast<const W*>(&raw[u]);
+#pragma unroll
+        for (int e = 0; e < E; ++e) v[e] = static_cast<Acc>(Elem<W>::up(w[e]));
+        store_pack<T, E, Acc>(out + e0, v, nv, aligned16(out + e0));
+      }
+    }
+  }
+  cta_end(c, vr, s, TL_ALLREDUCE);
 }
 
 // =============================================================== one-shot ==
@@ -703,22 +864,59 @@ __global__ void __launch_bounds__(kThreads) symm_allreduce_kernel(DevComm c, Col
 }
 
 // ============================================================== allgather ==
-// Bytes, any alignment.  Stage my block in my arena, meet, pull the others.
+// Bytes, any alignment.  Every rank pushes its block into slot `rank` of every peer's arena (posted stores to
+// all peers at once), the ranks meet, and each one unpacks the N - 1 foreign slots from its own arena.
 __global__ void __launch_bounds__(kThreads) allgather_kernel(DevComm c, CollArgs a) {
   const int vr = blockIdx.y, rank = c.rank_base + vr, N = c.world;
   CtaSync s = cta_begin(c, vr);
   const unsigned long long nbytes = static_cast<unsigned long long>(a.numel);
   const unsigned long long stride = static_cast<unsigned long long>(a.stride);
+  const unsigned long long slot = (nbytes + 15) / 16 * 16;
   const char* in = static_cast<const char*>(a.in[vr]);
   char* out = static_cast<char*>(a.out[vr]);
   const size_t base = static_cast<size_t>(s.half) * c.half_bytes;
-  if (bounds_violation(c, vr, base + nbytes)) {
+  if (bounds_violation(c, vr, base + static_cast<size_t>(N) * slot)) {
     cta_end(c, vr, s);
     return;
   }
   unsigned long long b0, b1;
   cta_byte_span(nbytes, b0, b1);
-  cta_copy_bytes(c.arena[rank] + base + b0, in + b0, b1 - b0);
+  if (a.reserved != 0 && c.mc_arena != nullptr && aligned16(in)) {
+    // In-switch replication: one store through the multicast mapping lands in slot `rank` of every arena, so this
+    // GPU's links carry the block once instead of N - 1 times.
+    char* mc = c.mc_arena + base + static_cast<size_t>(rank) * slot;
+    const unsigned long long v0 = b0 / 16, v1 = (b1 - b0) / 16 + v0;
+    constexpr int U = 4;
+    for (unsigned long long i0 = v0 + threadIdx.x; i0 < v1; i0 += static_cast<unsigned long long>(blockDim.x) * U) {
+      uint4 v[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const unsigned long long i = i0 + static_cast<unsigned long long>(u) * blockDim.x;
+        if (i < v1) v[u] = reinterpret_cast<const uint4*>(in)[i];
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const unsigned long long i = i0 + static_cast<unsigned long long>(u) * blockDim.x;
+        if (i < v1) multimem_st16(mc + i * 16, v[u]);
+      }
+    }
+    // ragged tail of the block (fewer than 16 bytes): plain stores to every peer
+    const unsigned long long tail0 = v1 * 16;
+    if (tail0 < b1) {
+      for (int k = 1; k < N; ++k) {
+        const int p = (rank + k) % N;
+        cta_copy_bytes(c.arena[p] + base + static_cast<size_t>(rank) * slot + tail0, in + tail0, b1 - tail0);
+      }
+    }
+  } else {
+    char* dsts[kMaxRanks];
+    int nd = 0;
+    for (int k = 1; k < N; ++k) {
+      const int p = (rank + k) % N;
+      dsts[nd++] = c.arena[p] + base + static_cast<size_t>(rank) * slot + b0;
+    }
+    cta_push_bytes(dsts, nd, in + b0, b1 - b0);
+  }
   if (out + static_cast<size_t>(rank) * stride != in) cta_copy_bytes(out + static_cast<size_t>(rank) * stride + b0, in + b0, b1 - b0);
   if (barrier_all(c, vr, rank, s, PH_GATHER)) {
     cta_end(c, vr, s);
@@ -726,7 +924,7 @@ __global__ void __launch_bounds__(kThreads) allgather_kernel(DevComm c, CollArgs
   }
   for (int k = 1; k < N; ++k) {
     const int p = (rank + k) % N;
-    cta_copy_bytes(out + static_cast<size_t>(p) * stride + b0, c.arena[p] + base + b0, b1 - b0);
+    cta_copy_bytes(out + static_cast<size_t>(p) * stride + b0, c.arena[rank] + base + static_cast<size_t>(p) * slot + b0, b1 - b0);
   }
   cta_end(c, vr, s);
 }
@@ -777,42 +975,62 @@ __global__ void __launch_bounds__(kThreads) broadcast_kernel(DevComm c, CollArgs
 }
 
 // =============================================================== alltoall ==
-// P2P dispatch: rank r stages the segment meant for rank q in slot q of its
-// own arena; after the meeting, rank q pulls slot q of every rank straight
-// into its output at that peer's offset.  Segment sizes may differ per pair.
+// P2P dispatch: rank r pushes the segment meant for rank q straight into slot r of q's arena (posted stores); after
+// the meeting every rank unpacks its N - 1 slots into its output at the senders' offsets.  Segment sizes may differ
+// per pair, and a rank only knows its own, so the number of rounds (a round moves at most slot_bytes per pair) is
+// agreed on the device: every CTA first tells every peer its rank's longest segment through a word behind the
+// slots, and all take the largest.  Segments of any length therefore go through one launch.
 __global__ void __launch_bounds__(kThreads) alltoall_kernel(DevComm c, A2AArgs a) {
   const int vr = blockIdx.y, rank = c.rank_base + vr, N = c.world;
   CtaSync s = cta_begin(c, vr);
   const char* in = static_cast<const char*>(a.in[vr]);
   char* out = static_cast<char*>(a.out[vr]);
   const size_t base = static_cast<size_t>(s.half) * c.half_bytes;
-  {
-    unsigned long long longest = 0;
-    for (int q = 0; q < N; ++q) longest = a.in_len[vr][q] > longest ? a.in_len[vr][q] : longest;
-    if (longest > a.slot_bytes || bounds_violation(c, vr, base + static_cast<size_t>(N) * a.slot_bytes)) {
-      if (longest > a.slot_bytes && threadIdx.x == 0) report_timeout(c, vr, PH_BOUNDS, rank);
-      cta_end(c, vr, s);
-      return;
-    }
+  const unsigned long long slot = a.slot_bytes;
+  // control words: [cta][source rank] behind the N data slots of this half
+  const size_t ctl_off = base + static_cast<size_t>(N) * slot;
+  if (bounds_violation(c, vr, ctl_off + static_cast<size_t>(gridDim.x) * kMaxRanks * sizeof(unsigned long long))) {
+    cta_end(c, vr, s);
+    return;
   }
-  for (int k = 0; k < N; ++k) {
-    const int q = (rank + k) % N;
-    unsigned long long b0, b1;
-    cta_byte_span(a.in_len[vr][q], b0, b1);
-    if (q == rank)
-      cta_copy_bytes(out + a.out_off[vr][q] + b0, in + a.in_off[vr][q] + b0, b1 - b0);
-    else
-      cta_copy_bytes(c.arena[rank] + base + q * a.slot_bytes + b0, in + a.in_off[vr][q] + b0, b1 - b0);
+  unsigned long long longest = 0;
+  for (int q = 0; q < N; ++q) {
+    longest = a.in_len[vr][q] > longest ? a.in_len[vr][q] : longest;
+    longest = a.out_len[vr][q] > longest ? a.out_len[vr][q] : longest;
   }
+  if (threadIdx.x < N)
+    reinterpret_cast<unsigned long long*>(c.arena[threadIdx.x] + ctl_off)[blockIdx.x * kMaxRanks + rank] = longest;
   if (barrier_all(c, vr, rank, s, PH_GATHER)) {
     cta_end(c, vr, s);
     return;
   }
-  for (int k = 1; k < N; ++k) {
-    const int p = (rank + k) % N;
-    unsigned long long b0, b1;
-    cta_byte_span(a.out_len[vr][p], b0, b1);
-    cta_copy_bytes(out + a.out_off[vr][p] + b0, c.arena[p] + base + rank * a.slot_bytes + b0, b1 - b0);
+  for (int q = 0; q < N; ++q) {
+    const unsigned long long v = reinterpret_cast<const unsigned long long*>(c.arena[rank] + ctl_off)[blockIdx.x * kMaxRanks + q];
+    longest = v > longest ? v : longest;
+  }
+  const unsigned long long rounds = longest == 0 ? 0 : (longest + slot - 1) / slot;
+  for (unsigned long long r = 0; r < rounds; ++r) {
+    const unsigned long long lo = r * slot;
+    for (int k = 0; k < N; ++k) {
+      const int q = (rank + k) % N;
+      const unsigned long long len = a.in_len[vr][q] > lo ? (a.in_len[vr][q] - lo < slot ? a.in_len[vr][q] - lo : slot) : 0;
+      unsigned long long b0, b1;
+      cta_byte_span(len, b0, b1);
+      if (q == rank)
+        cta_copy_bytes(out + a.out_off[vr][q] + lo + b0, in + a.in_off[vr][q] + lo + b0, b1 - b0);
+      else
+        cta_copy_bytes(c.arena[q] + base + static_cast<size_t>(rank) * slot + b0, in + a.in_off[vr][q] + lo + b0, b1 - b0);
+    }
+    if (barrier_all(c, vr, rank, s, PH_GATHER)) break;
+    for (int k = 1; k < N; ++k) {
+      const int p = (rank + k) % N;
+      const unsigned long long len = a.out_len[vr][p] > lo ? (a.out_len[vr][p] - lo < slot ? a.out_len[vr][p] - lo : slot) : 0;
+      unsigned long long b0, b1;
+      cta_byte_span(len, b0, b1);
+      cta_copy_bytes(out + a.out_off[vr][p] + lo + b0, c.arena[rank] + base + static_cast<size_t>(p) * slot + b0, b1 - b0);
+    }
+    // the slots are overwritten in the next round: everybody must have unpacked first
+    if (r + 1 < rounds && barrier_all(c, vr, rank, s, PH_GATHER)) break;
   }
   cta_end(c, vr, s);
 }
@@ -927,12 +1145,13 @@ cudaError_t launch(const char* name, void (*kernel)(KArgs...), const LaunchCfg& 
   return launch_record(name, __FILE__, __LINE__, grid, dim3(threads), 0, cfg.stream);
 }
 
-enum class Sched { TWOSHOT, SCATTER, ONESHOT, RING, TREE };
+enum class Sched { TWOSHOT, TWOSHOT_PUSH, SCATTER, ONESHOT, RING, TREE };
 
 template <typename T, typename W>
 cudaError_t launch_typed(Sched k, const DevComm& c, const CollArgs& a, const LaunchCfg& cfg) {
   switch (k) {
     case Sched::TWOSHOT: return launch("twoshot_kernel", twoshot_kernel<T, W, false>, cfg, kThreads, c, a);
+    case Sched::TWOSHOT_PUSH: return launch("twoshot_push_kernel", twoshot_push_kernel<T, W>, cfg, kThreads, c, a);
     case Sched::SCATTER: return launch("twoshot_kernel", twoshot_kernel<T, W, true>, cfg, kThreads, c, a);
     case Sched::ONESHOT: return launch("oneshot_kernel", oneshot_kernel<T, W>, cfg, kThreads, c, a);
     case Sched::RING: return launch("ring_kernel", ring_kernel<T, W>, cfg, kThreads, c, a);
@@ -958,6 +1177,9 @@ cudaError_t dispatch(Sched k, ElemType t, bool bf16_wire, const DevComm& c, cons
 
 cudaError_t launch_allreduce_twoshot(ElemType t, bool bf16_wire, const DevComm& c, const CollArgs& a, const LaunchCfg& cfg) {
   return dispatch(Sched::TWOSHOT, t, bf16_wire, c, a, cfg);
+}
+cudaError_t launch_allreduce_twoshot_push(ElemType t, bool bf16_wire, const DevComm& c, const CollArgs& a, const LaunchCfg& cfg) {
+  return dispatch(Sched::TWOSHOT_PUSH, t, bf16_wire, c, a, cfg);
 }
 cudaError_t launch_reduce_scatter(ElemType t, bool bf16_wire, const DevComm& c, const CollArgs& a, const LaunchCfg& cfg) {
   return dispatch(Sched::SCATTER, t, bf16_wire, c, a, cfg);

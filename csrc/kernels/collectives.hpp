@@ -24,6 +24,8 @@ struct LaunchCfg {
 };
 
 cudaError_t launch_allreduce_twoshot(ElemType t, bool bf16_wire, const DevComm& c, const CollArgs& a, const LaunchCfg& cfg);
+// two-shot whose all-gather half is pushed as well (no loads from peers); needs twoshot_push_bytes of arena
+cudaError_t launch_allreduce_twoshot_push(ElemType t, bool bf16_wire, const DevComm& c, const CollArgs& a, const LaunchCfg& cfg);
 cudaError_t launch_allreduce_oneshot(ElemType t, bool bf16_wire, const DevComm& c, const CollArgs& a, const LaunchCfg& cfg);
 cudaError_t launch_allreduce_ring(ElemType t, bool bf16_wire, const DevComm& c, const CollArgs& a, const LaunchCfg& cfg);
 cudaError_t launch_allreduce_tree(ElemType t, bool bf16_wire, const DevComm& c, const CollArgs& a, const LaunchCfg& cfg);

@@ -51,6 +51,9 @@ __global__ void __launch_bounds__(256) norm_fwd_kernel(const __nv_bfloat16* __re
                                                        const float* __restrict__ b, __nv_bfloat16* __restrict__ y,
                                                        float* __restrict__ mean_out, float* __restrict__ rstd_out, int rows,
                                                        int dim, float eps) {
+  // dependent launch: the CTA may be resident before the previous kernel of the stream has finished
+  ::mccl::pdl_trigger();
+  ::mccl::pdl_wait();
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (warp >= rows) return;
   const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<size_t>(warp) * dim);
@@ -97,6 +100,9 @@ __global__ void __launch_bounds__(256) norm_bwd_dx_kernel(const __nv_bfloat16* _
                                                           const float* __restrict__ w, const float* __restrict__ mean,
                                                           const float* __restrict__ rstd, __nv_bfloat16* __restrict__ dx,
                                                           const __nv_bfloat16* __restrict__ dx_add, int rows, int dim) {
+  // dependent launch: the CTA may be resident before the previous kernel of the stream has finished
+  ::mccl::pdl_trigger();
+  ::mccl::pdl_wait();
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (warp >= rows) return;
   const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<size_t>(warp) * dim);
@@ -153,6 +159,9 @@ __global__ void __launch_bounds__(256) colsum_partial_kernel(const __nv_bfloat16
                                                              const float* __restrict__ mean, const float* __restrict__ rstd,
                                                              float* __restrict__ part_w, float* __restrict__ part_b, int rows,
                                                              int dim, int atomic) {
+  // dependent launch: the CTA may be resident before the previous kernel of the stream has finished
+  ::mccl::pdl_trigger();
+  ::mccl::pdl_wait();
   __shared__ float sw[8][32][9], sb[8][32][9];
   const int cg = threadIdx.x & 31, ry = threadIdx.x >> 5;
   const int col = blockIdx.x * 256 + cg * 8;
@@ -205,6 +214,9 @@ __global__ void __launch_bounds__(256) colsum_partial_kernel(const __nv_bfloat16
 // then the 8 lanes are combined in a fixed order.
 __global__ void __launch_bounds__(256) colsum_final_kernel(const float* __restrict__ part_w, const float* __restrict__ part_b,
                                                            float* __restrict__ dw, float* __restrict__ db, int slabs, int dim) {
+  // dependent launch: the CTA may be resident before the previous kernel of the stream has finished
+  ::mccl::pdl_trigger();
+  ::mccl::pdl_wait();
   __shared__ float sw[8][33], sb[8][33];
   const int cx = threadIdx.x & 31, ly = threadIdx.x >> 5;
   const int c = blockIdx.x * 32 + cx;
@@ -236,8 +248,8 @@ cudaError_t norm_fwd(const __nv_bfloat16* x, const float* w, const float* b, __n
                      int rows, int dim, float eps, cudaStream_t stream) {
   if (dim % 8 != 0) return cudaErrorNotSupported;
   const int blocks = (rows + 7) / 8;
-  if (b) MCCL_LAUNCH(norm_fwd_kernel<true>, blocks, 256, 0, stream, x, w, b, y, mean, rstd, rows, dim, eps);
-  else MCCL_LAUNCH(norm_fwd_kernel<false>, blocks, 256, 0, stream, x, w, b, y, mean, rstd, rows, dim, eps);
+  if (b) MCCL_LAUNCH_PDL(norm_fwd_kernel<true>, blocks, 256, 0, stream, x, w, b, y, mean, rstd, rows, dim, eps);
+  else MCCL_LAUNCH_PDL(norm_fwd_kernel<false>, blocks, 256, 0, stream, x, w, b, y, mean, rstd, rows, dim, eps);
   count_launch();
   return ::mccl::launch_status();
 }
@@ -247,20 +259,20 @@ cudaError_t norm_bwd(const __nv_bfloat16* dy, const __nv_bfloat16* x, const floa
                      cudaStream_t stream, const __nv_bfloat16* dx_add) {
   if (dim % 8 != 0) return cudaErrorNotSupported;
   const int blocks = (rows + 7) / 8;
-  if (layernorm) MCCL_LAUNCH(norm_bwd_dx_kernel<true>, blocks, 256, 0, stream, dy, x, w, mean, rstd, dx, dx_add, rows, dim);
-  else MCCL_LAUNCH(norm_bwd_dx_kernel<false>, blocks, 256, 0, stream, dy, x, w, mean, rstd, dx, dx_add, rows, dim);
+  if (layernorm) MCCL_LAUNCH_PDL(norm_bwd_dx_kernel<true>, blocks, 256, 0, stream, dy, x, w, mean, rstd, dx, dx_add, rows, dim);
+  else MCCL_LAUNCH_PDL(norm_bwd_dx_kernel<false>, blocks, 256, 0, stream, dy, x, w, mean, rstd, dx, dx_add, rows, dim);
   const int slabs = colsum_slabs(rows);
   dim3 grid((dim + 255) / 256, slabs);
   if (!scratch) {
     // no scratch: dw / db accumulate the slab sums atomically (they must hold the value to add to)
-    MCCL_LAUNCH(colsum_partial_kernel<true>, grid, 256, 0, stream, dy, x, mean, rstd, dw, layernorm ? db : nullptr, rows, dim, 1);
+    MCCL_LAUNCH_PDL(colsum_partial_kernel<true>, grid, 256, 0, stream, dy, x, mean, rstd, dw, layernorm ? db : nullptr, rows, dim, 1);
     count_launch(2);
     return ::mccl::launch_status();
   }
   float* part_w = scratch;
   float* part_b = layernorm ? scratch + static_cast<size_t>(slabs) * dim : nullptr;
-  MCCL_LAUNCH(colsum_partial_kernel<true>, grid, 256, 0, stream, dy, x, mean, rstd, part_w, part_b, rows, dim, 0);
-  MCCL_LAUNCH(colsum_final_kernel, (dim + 31) / 32, 256, 0, stream, part_w, part_b, dw, layernorm ? db : nullptr, slabs, dim);
+  MCCL_LAUNCH_PDL(colsum_partial_kernel<true>, grid, 256, 0, stream, dy, x, mean, rstd, part_w, part_b, rows, dim, 0);
+  MCCL_LAUNCH_PDL(colsum_final_kernel, (dim + 31) / 32, 256, 0, stream, part_w, part_b, dw, layernorm ? db : nullptr, slabs, dim);
   count_launch(3);
   return ::mccl::launch_status();
 }
@@ -270,12 +282,12 @@ cudaError_t colsum_bf16(const __nv_bfloat16* in, float* out, float* scratch, int
   const int slabs = colsum_slabs(rows);
   dim3 grid((dim + 255) / 256, slabs);
   if (!scratch) {
-    MCCL_LAUNCH(colsum_partial_kernel<false>, grid, 256, 0, stream, in, nullptr, nullptr, nullptr, nullptr, out, rows, dim, 1);
+    MCCL_LAUNCH_PDL(colsum_partial_kernel<false>, grid, 256, 0, stream, in, nullptr, nullptr, nullptr, nullptr, out, rows, dim, 1);
     count_launch();
     return ::mccl::launch_status();
   }
-  MCCL_LAUNCH(colsum_partial_kernel<false>, grid, 256, 0, stream, in, nullptr, nullptr, nullptr, nullptr, scratch, rows, dim, 0);
-  MCCL_LAUNCH(colsum_final_kernel, (dim + 31) / 32, 256, 0, stream, nullptr, scratch, nullptr, out, slabs, dim);
+  MCCL_LAUNCH_PDL(colsum_partial_kernel<false>, grid, 256, 0, stream, in, nullptr, nullptr, nullptr, nullptr, scratch, rows, dim, 0);
+  MCCL_LAUNCH_PDL(colsum_final_kernel, (dim + 31) / 32, 256, 0, stream, nullptr, scratch, nullptr, out, slabs, dim);
   count_launch(2);
   return ::mccl::launch_status();
 }
@@ -285,6 +297,9 @@ __global__ void __launch_bounds__(256) adamw_kernel(float* __restrict__ p, float
                                                     float* __restrict__ v, __nv_bfloat16* __restrict__ p16, long long n4, long long n,
                                                     float lr, float b1, float b2, float eps, float wd,
                                                     const float* __restrict__ step_ptr, float gscale, int zero_grad) {
+  // dependent launch: the CTA may be resident before the previous kernel of the stream has finished
+  ::mccl::pdl_trigger();
+  ::mccl::pdl_wait();
   const float step = *step_ptr;
   const float bc1 = 1.f - powf(b1, step), bc2 = 1.f - powf(b2, step);
   const float inv_bc1 = 1.f / bc1, inv_sqrt_bc2 = rsqrtf(bc2), decay = 1.f - lr * wd;
@@ -338,7 +353,7 @@ cudaError_t adamw_flat(float* p, float* g, float* m, float* v, __nv_bfloat16* p1
   long long blocks = (n4 + 255) / 256;
   if (blocks > 148 * 8) blocks = 148 * 8;
   if (blocks < 1) blocks = 1;
-  MCCL_LAUNCH(adamw_kernel, static_cast<int>(blocks), 256, 0, stream, p, g, m, v, p16, n4, n, lr, beta1, beta2, eps, wd, step, grad_scale,
+  MCCL_LAUNCH_PDL(adamw_kernel, static_cast<int>(blocks), 256, 0, stream, p, g, m, v, p16, n4, n, lr, beta1, beta2, eps, wd, step, grad_scale,
               zero_grad ? 1 : 0);
   count_launch();
   return ::mccl::launch_status();
@@ -349,6 +364,9 @@ cudaError_t adamw_flat(float* p, float* g, float* m, float* v, __nv_bfloat16* p1
 // Pass 2: overwrite the row with (softmax - onehot) * scale.
 __global__ void __launch_bounds__(512) ce_kernel(__nv_bfloat16* __restrict__ logits, const long long* __restrict__ targets,
                                                  float* __restrict__ loss_rows, int vocab, float scale) {
+  // dependent launch: the CTA may be resident before the previous kernel of the stream has finished
+  ::mccl::pdl_trigger();
+  ::mccl::pdl_wait();
   __shared__ float s_max[16], s_sum[16];
   const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
   __nv_bfloat16* lr = logits + static_cast<size_t>(row) * vocab;
@@ -414,7 +432,7 @@ __global__ void __launch_bounds__(512) ce_kernel(__nv_bfloat16* __restrict__ log
 cudaError_t cross_entropy_fwd_bwd(__nv_bfloat16* logits, const long long* targets, float* loss_rows, int rows, int vocab,
                                   float grad_scale, cudaStream_t stream) {
   if (vocab % 8 != 0 || (reinterpret_cast<uintptr_t>(logits) & 15u)) return cudaErrorNotSupported;
-  MCCL_LAUNCH(ce_kernel, rows, 512, 0, stream, logits, targets, loss_rows, vocab, grad_scale);
+  MCCL_LAUNCH_PDL(ce_kernel, rows, 512, 0, stream, logits, targets, loss_rows, vocab, grad_scale);
   count_launch();
   return ::mccl::launch_status();
 }
@@ -422,6 +440,9 @@ cudaError_t cross_entropy_fwd_bwd(__nv_bfloat16* logits, const long long* target
 // -------------------------------------------------------------- transpose --
 __global__ void __launch_bounds__(256) transpose_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out,
                                                         int rows, int cols) {
+  // dependent launch: the CTA may be resident before the previous kernel of the stream has finished
+  ::mccl::pdl_trigger();
+  ::mccl::pdl_wait();
   __shared__ __nv_bfloat16 tile[64][66];
   const int c0 = blockIdx.x * 64, r0 = blockIdx.y * 64;
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
@@ -446,13 +467,16 @@ __global__ void __launch_bounds__(256) transpose_kernel(const __nv_bfloat16* __r
 
 cudaError_t transpose_bf16(const __nv_bfloat16* in, __nv_bfloat16* out, int rows, int cols, cudaStream_t stream) {
   dim3 grid((cols + 63) / 64, (rows + 63) / 64);
-  MCCL_LAUNCH(transpose_kernel, grid, 256, 0, stream, in, out, rows, cols);
+  MCCL_LAUNCH_PDL(transpose_kernel, grid, 256, 0, stream, in, out, rows, cols);
   count_launch();
   return ::mccl::launch_status();
 }
 
 // ------------------------------------------------------------------ casts --
 __global__ void __launch_bounds__(256) cast_kernel(const float* __restrict__ in, __nv_bfloat16* __restrict__ out, long long n) {
+  // dependent launch: the CTA may be resident before the previous kernel of the stream has finished
+  ::mccl::pdl_trigger();
+  ::mccl::pdl_wait();
   const long long n4 = n / 4;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n4;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
@@ -473,7 +497,7 @@ cudaError_t cast_f32_bf16(const float* in, __nv_bfloat16* out, long long n, cuda
   long long blocks = (n / 4 + 255) / 256;
   if (blocks > 148 * 8) blocks = 148 * 8;
   if (blocks < 1) blocks = 1;
-  MCCL_LAUNCH(cast_kernel, static_cast<int>(blocks), 256, 0, stream, in, out, n);
+  MCCL_LAUNCH_PDL(cast_kernel, static_cast<int>(blocks), 256, 0, stream, in, out, n);
   count_launch();
   return ::mccl::launch_status();
 }
@@ -481,6 +505,9 @@ cudaError_t cast_f32_bf16(const float* in, __nv_bfloat16* out, long long n, cuda
 // ------------------------------------------------------------- GELU bwd ---
 __global__ void __launch_bounds__(256) gelu_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ z,
                                                        __nv_bfloat16* __restrict__ dz, long long n8) {
+  // dependent launch: the CTA may be resident before the previous kernel of the stream has finished
+  ::mccl::pdl_trigger();
+  ::mccl::pdl_wait();
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n8;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
     float g[8], zz[8], o[8];
@@ -502,7 +529,7 @@ cudaError_t gelu_bwd(const __nv_bfloat16* dy, const __nv_bfloat16* z, __nv_bfloa
   long long blocks = (n / 8 + 255) / 256;
   if (blocks > 148 * 8) blocks = 148 * 8;
   if (blocks < 1) blocks = 1;
-  MCCL_LAUNCH(gelu_bwd_kernel, static_cast<int>(blocks), 256, 0, stream, dy, z, dz, n / 8);
+  MCCL_LAUNCH_PDL(gelu_bwd_kernel, static_cast<int>(blocks), 256, 0, stream, dy, z, dz, n / 8);
   count_launch();
   return ::mccl::launch_status();
 }
@@ -512,6 +539,9 @@ cudaError_t gelu_bwd(const __nv_bfloat16* dy, const __nv_bfloat16* z, __nv_bfloa
 __global__ void __launch_bounds__(256) embed_fwd_kernel(const long long* __restrict__ ids, const float* __restrict__ tok,
                                                         const float* __restrict__ pos, __nv_bfloat16* __restrict__ y, long long n8,
                                                         int seq, int dim8, int vocab) {
+  // dependent launch: the CTA may be resident before the previous kernel of the stream has finished
+  ::mccl::pdl_trigger();
+  ::mccl::pdl_wait();
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n8;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
     const long long t = i / dim8;
@@ -534,6 +564,9 @@ __global__ void __launch_bounds__(256) embed_fwd_kernel(const long long* __restr
 __global__ void __launch_bounds__(256) embed_bwd_kernel(const long long* __restrict__ ids, const __nv_bfloat16* __restrict__ dy,
                                                         float* __restrict__ dtok, float* __restrict__ dpos, long long n8, int seq,
                                                         int dim8, int vocab) {
+  // dependent launch: the CTA may be resident before the previous kernel of the stream has finished
+  ::mccl::pdl_trigger();
+  ::mccl::pdl_wait();
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n8;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
     const long long t = i / dim8;
@@ -565,7 +598,7 @@ cudaError_t embed_fwd(const long long* ids, const float* tok, const float* pos, 
                       int vocab, cudaStream_t stream) {
   if (dim % 8 != 0 || tokens <= 0 || seq <= 0) return cudaErrorNotSupported;
   const long long n8 = static_cast<long long>(tokens) * (dim / 8);
-  MCCL_LAUNCH(embed_fwd_kernel, embed_blocks(n8), 256, 0, stream, ids, tok, pos, y, n8, seq, dim / 8, vocab);
+  MCCL_LAUNCH_PDL(embed_fwd_kernel, embed_blocks(n8), 256, 0, stream, ids, tok, pos, y, n8, seq, dim / 8, vocab);
   count_launch();
   return ::mccl::launch_status();
 }
@@ -574,7 +607,7 @@ cudaError_t embed_bwd(const long long* ids, const __nv_bfloat16* dy, float* dtok
                       int vocab, cudaStream_t stream) {
   if (dim % 8 != 0 || tokens <= 0 || seq <= 0) return cudaErrorNotSupported;
   const long long n8 = static_cast<long long>(tokens) * (dim / 8);
-  MCCL_LAUNCH(embed_bwd_kernel, embed_blocks(n8), 256, 0, stream, ids, dy, dtok, dpos, n8, seq, dim / 8, vocab);
+  MCCL_LAUNCH_PDL(embed_bwd_kernel, embed_blocks(n8), 256, 0, stream, ids, dy, dtok, dpos, n8, seq, dim / 8, vocab);
   count_launch();
   return ::mccl::launch_status();
 }

@@ -21,6 +21,7 @@ struct GemmDev {
   __nv_bfloat16* aux;
   const float* bias;
   const __nv_bfloat16* residual;
+  const __nv_bfloat16* dgelu_z;   // when set: D = acc * gelu'(z), the backward of a GELU fused into the producing GEMM
   int m, n, k;
   int ldd;
   int d_fp32;
@@ -63,6 +64,23 @@ __device__ __forceinline__ void epilogue_store(const GemmDev& g, int row, int co
     }
 #pragma unroll
     for (int j = 0; j < 32; ++j) v[j] = gelu_erf(v[j]);
+  }
+  if (g.dgelu_z) {
+    const __nv_bfloat16* zrow = g.dgelu_z + static_cast<size_t>(row) * g.ldd + col0;
+#pragma unroll
+    for (int j8 = 0; j8 < 4; ++j8) {
+      if (j8 * 8 < ncols) {
+        const uint4 pk = *reinterpret_cast<const uint4*>(zrow + j8 * 8);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&pk);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 t = __bfloat1622float2(h[i]);
+          const float x0 = t.x, x1 = t.y;
+          v[j8 * 8 + 2 * i] *= 0.5f * (1.f + erff(x0 * 0.70710678f)) + x0 * 0.39894228f * __expf(-0.5f * x0 * x0);
+          v[j8 * 8 + 2 * i + 1] *= 0.5f * (1.f + erff(x1 * 0.70710678f)) + x1 * 0.39894228f * __expf(-0.5f * x1 * x1);
+        }
+      }
+    }
   }
   if (g.residual) {
     const __nv_bfloat16* rrow = g.residual + static_cast<size_t>(row) * g.ldd + col0;

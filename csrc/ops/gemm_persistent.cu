@@ -373,13 +373,19 @@ __global__ void __launch_bounds__(192, 1) gemm_persistent_kernel(const __grid_co
   uint64_t* acc_empty = acc_full + 2;    // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  // Tile scheduler (plain GEMMs): the producer draws the next tile from a device-wide counter and
-  // publishes it to the MMA and epilogue warps through a ring of four entries, so a CTA that starts
-  // late or shares its SM with a collective kernel simply takes fewer tiles.
+  // Tile ring: the producer publishes the tiles of this CTA (static round-robin order) to the MMA and epilogue
+  // warps through a ring of four entries.  (A device-wide tile counter was tried in its place, so that a CTA
+  // sharing its SM with a collective kernel would take fewer tiles: neutral on one GPU, 0.1-0.3 ms slower per
+  // step on two, so it is gone; the collectives get SMs of their own instead.)
   uint64_t* sched_full = reinterpret_cast<uint64_t*>(smem + L::kTiles + L::kGemmBarriers + L::kReduceBarriers);
   uint64_t* sched_empty = sched_full + 4;
   volatile int* sched_tile = reinterpret_cast<volatile int*>(sched_empty + 4);
 
+  // Dependent launch: this CTA may be resident while the previous kernel of the stream is still draining.  Barrier
+  // init, tensor-memory allocation and descriptor prefetch below touch no global data; pdl_wait() comes before the
+  // first access that does (at once for the fused roles, which read their call number from global memory).
+  pdl_trigger();
+  if (f.mode != FUSE_NONE) pdl_wait();
   const unsigned long long tl_t0 = tl_begin(g.tl);
   const uint32_t epoch = f.mode != FUSE_NONE ? *f.epoch_ptr : 0u;
   if (f.mode != FUSE_NONE && static_cast<int>(blockIdx.x) < f.copy_ctas) {
@@ -424,6 +430,7 @@ __global__ void __launch_bounds__(192, 1) gemm_persistent_kernel(const __grid_co
   __syncthreads();
   tc::fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  if (f.mode == FUSE_NONE) pdl_wait();   // set-up done: from here on operands are read and outputs written
 
   // Reduce-scatter fusion: phase-major order; inside a phase the chunks of the other ranks come first
   // (rank + 1, rank + 2, ...) and this rank's own chunk last, so what peers wait for is ready earliest.
@@ -458,8 +465,7 @@ __global__ void __launch_bounds__(192, 1) gemm_persistent_kernel(const __grid_co
           ok = wait_or_abort(&sched_empty[slot], ((i >> 2) - 1) & 1, abort_flag, wait_ns);
           if (!ok) break;
         }
-        int t = (f.sched_counter == nullptr || i == 0) ? gcta + i * gctas
-                                                       : gctas + static_cast<int>(atomicAdd(f.sched_counter, 1u));
+        int t = gcta + i * gctas;   // static round-robin over the CTAs
         if (t >= total_tiles) t = -1;
         sched_tile[slot] = t;
         tc::mbar_arrive(&sched_full[slot]);
@@ -610,14 +616,6 @@ __global__ void __launch_bounds__(192, 1) gemm_persistent_kernel(const __grid_co
     tc::tmem_dealloc(tmem_base, 2 * BN);
   }
   tl_end(g.tl, tl_t0, TL_GEMM, (static_cast<uint32_t>(m_tiles) << 16) | static_cast<uint32_t>(n_tiles * splits));
-  if (f.sched_counter != nullptr && threadIdx.x == 0) {
-    // the CTA that leaves last rewinds the counters for the next launch that uses this slot
-    __threadfence();
-    if (atomicAdd(f.sched_counter + 1, 1u) + 1u == gridDim.x) {
-      atomicExch(f.sched_counter, 0u);
-      atomicExch(f.sched_counter + 1, 0u);
-    }
-  }
   // out of tiles: help with the reduction (the tile ring is idle now)
   if (f.mode == FUSE_REDUCE_SCATTER_D && *abort_flag == 0)
     reduce_scatter_role(f, g, epoch, smem, reinterpret_cast<ReduceShared*>(smem + L::kTiles + L::kGemmBarriers));
@@ -625,21 +623,6 @@ __global__ void __launch_bounds__(192, 1) gemm_persistent_kernel(const __grid_co
 
 // Process-wide cap on the CTAs of plain GEMM launches (0 = one per SM); see set_gemm_cta_limit().
 std::atomic<int> g_gemm_cta_limit{0};
-
-// Counter pairs {next tile, CTAs that have left} of the tile scheduler, one array per device.
-constexpr unsigned int kSchedSlots = 1024;
-__device__ unsigned int g_sched_counters[2 * kSchedSlots];
-unsigned int* sched_counters() {
-  static unsigned int* ptr[64] = {};
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
-  if (!ptr[dev]) {
-    void* p = nullptr;
-    if (cudaGetSymbolAddress(&p, g_sched_counters) != cudaSuccess) return nullptr;
-    ptr[dev] = static_cast<unsigned int*>(p);
-  }
-  return ptr[dev];
-}
 
 int sm_count() {
   static int n = 0;
@@ -695,6 +678,7 @@ cudaError_t launch_persistent_cfg(const GemmArgs& a, const FusedDev& f_in, int m
   g.aux = a.aux;
   g.bias = a.bias;
   g.residual = a.residual;
+  g.dgelu_z = a.dgelu_z;
   g.m = a.m;
   g.n = a.n;
   g.k = a.k;
@@ -712,7 +696,7 @@ cudaError_t launch_persistent_cfg(const GemmArgs& a, const FusedDev& f_in, int m
     const char* v = std::getenv("MCCL_GEMM_SPLITK");
     return !(v && v[0] == '0');
   }();
-  if (allow_split && a.d_fp32 && a.epilogue == EPI_NONE && !a.residual && f.mode == FUSE_NONE) {
+  if (allow_split && a.d_fp32 && a.epilogue == EPI_NONE && !a.residual && !a.dgelu_z && f.mode == FUSE_NONE) {
     const int splits = choose_splits(tiles, a.k / BK, sm_count());
     if (splits > 1) {
       if (!a.accumulate) {
@@ -726,21 +710,6 @@ cudaError_t launch_persistent_cfg(const GemmArgs& a, const FusedDev& f_in, int m
     }
   }
 no_split:
-  // Plain GEMMs draw tiles from a device-wide counter (one of a ring of slots per launch; the last CTA of a
-  // launch rewinds its slot, and launches that share a slot are far apart in stream order).
-  // Off by default: on the data-parallel step it measured neutral on one GPU and 0.1-0.3 ms slower on two
-  // (the extra scheduler hand-shake per tile costs more than the balancing gains); MCCL_GEMM_DYNAMIC=1 enables it.
-  static const bool dynamic_tiles = [] {
-    const char* v = std::getenv("MCCL_GEMM_DYNAMIC");
-    return v && v[0] == '1';
-  }();
-  if (dynamic_tiles && f.mode == FUSE_NONE) {
-    unsigned int* base = sched_counters();
-    if (base) {
-      static std::atomic<unsigned int> next_slot{0};
-      f.sched_counter = base + 2 * (next_slot.fetch_add(1) % kSchedSlots);
-    }
-  }
   int ctas = sm_count();
   if (max_ctas <= 0) max_ctas = g_gemm_cta_limit.load(std::memory_order_relaxed);
   if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
@@ -748,7 +717,7 @@ no_split:
   int gemm_ctas = ctas - f.copy_ctas;
   if (gemm_ctas < 1) return cudaErrorInvalidValue;
   if (tiles < gemm_ctas) gemm_ctas = tiles;
-  MCCL_LAUNCH((gemm_persistent_kernel<BN, STAGES, kAMn, kBMn>), gemm_ctas + f.copy_ctas, 192, L::kTotal, stream, ma, mb, g, f);
+  MCCL_LAUNCH_PDL((gemm_persistent_kernel<BN, STAGES, kAMn, kBMn>), gemm_ctas + f.copy_ctas, 192, L::kTotal, stream, ma, mb, g, f);
   count_launch();
   return ::mccl::launch_status();
 }

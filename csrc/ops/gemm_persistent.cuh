@@ -34,7 +34,6 @@ struct FusedDev {
   const uint32_t* epoch_ptr = nullptr;        // device word: number of this fused call (bumped before the launch)
   unsigned long long timeout_ns = 0;          // bound of every cross-GPU wait
   int* status = nullptr;                      // written (non-zero) when such a wait runs out
-  unsigned int* sched_counter = nullptr;      // plain GEMMs: {next tile, CTAs that have left}; null = static tile order
   uint32_t* sig[kFuseMaxRanks] = {};          // every rank's signal words for these fusions (peer-mapped)
   // all-gather → GEMM
   const void* a_peer[kFuseMaxRanks] = {};     // rank r's shard of A

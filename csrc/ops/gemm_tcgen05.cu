@@ -182,6 +182,7 @@ cudaError_t launch_cfg(const GemmArgs& a, cudaStream_t stream) {
   g.aux = a.aux;
   g.bias = a.bias;
   g.residual = a.residual;
+  g.dgelu_z = a.dgelu_z;
   g.m = a.m;
   g.n = a.n;
   g.k = a.k;
@@ -216,6 +217,7 @@ cudaError_t gemm_bf16_tn(const GemmArgs& a, cudaStream_t stream) {
   if ((a.epilogue == EPI_BIAS_GELU || a.epilogue == EPI_GELU) && (!a.aux || a.d_fp32)) return cudaErrorInvalidValue;
   if (a.accumulate && !a.d_fp32) return cudaErrorInvalidValue;
   if (a.residual && (reinterpret_cast<uintptr_t>(a.residual) & 15u)) return unsupported("residual pointer must be 16-byte aligned");
+  if (a.dgelu_z && ((reinterpret_cast<uintptr_t>(a.dgelu_z) & 15u) || a.d_fp32)) return unsupported("dgelu_z must be 16-byte aligned and the output bf16");
   if (a.a_mn_major && a.m % 8 != 0) return unsupported("an MN-major A needs M to be a multiple of 8");
   // Default: persistent kernel (one CTA per SM, double-buffered accumulator).
   // MCCL_GEMM_KERNEL=tile selects the one-tile-per-CTA kernel below.

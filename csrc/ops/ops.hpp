@@ -80,6 +80,7 @@ struct GemmArgs {
   __nv_bfloat16* aux = nullptr;      // [M, N] pre-activation (GELU epilogues)
   const float* bias = nullptr;       // [N]
   const __nv_bfloat16* residual = nullptr;  // [M, N] added after bias / activation, row stride ldd
+  const __nv_bfloat16* dgelu_z = nullptr;   // [M, N] pre-activation: D = acc * gelu'(z) (input gradient through a GELU), row stride ldd
   int m = 0, n = 0, k = 0;
   int lda = 0, ldb = 0, ldd = 0;
   bool d_fp32 = false;

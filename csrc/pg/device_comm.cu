@@ -107,6 +107,8 @@ struct DeviceComm::Impl {
   unsigned long long debug_limit = 0;  // tests: pretend the arena ends here, so that the device-side check trips
   int threads = 0;         // threads per collective CTA, 0 = kernel default
   int64_t nvls_above = 0;  // AUTO uses staged NVLS at or above this many wire bytes (0 = never)
+  int64_t push_above = 0;  // AUTO uses the fully pushed two-shot at or above this many wire bytes (0 = never)
+  bool ag_multicast = true;  // allgather stores through the multicast mapping when there is one (MCCL_AG_NVLS=0: plain pushes)
   // Launch ordering across streams: the arena halves, flags and epochs are shared by every launch of this
   // communicator, so two collectives must never overlap on the device.  Each launch records `last_done` on its
   // stream; a launch on another stream first waits for it.  (Skipped while a stream is being captured: a graph
@@ -246,6 +248,8 @@ void DeviceComm::init_common() {
   int cap = cfg_.max_ctas > 0 ? cfg_.max_ctas : 64;   // 64 CTAs of 256 threads
   impl_->max_ctas = std::min(cap, dev::kMaxCtas);
   impl_->nvls_above = env::i64("MCCL_NVLS_ABOVE", 0);
+  impl_->push_above = env::i64("MCCL_PUSH_ABOVE", 0);
+  impl_->ag_multicast = env::flag("MCCL_AG_NVLS", true);
   if (nlocal_ > 1) impl_->max_ctas = std::max(1, std::min(impl_->max_ctas, 96 / nlocal_));  // all virtual ranks co-resident
   if (mesh_->mode() != SymmMesh::Mode::LOCAL) mesh_->store_barrier("devcomm-ready");
 }
@@ -358,8 +362,9 @@ Algo DeviceComm::decide_allreduce(Algo requested, size_t numel, DType t, RedOp o
     // tuning table (MCCL_NVLS_ABOVE, wire bytes); buffers that already live in the
     // symmetric heap take the copy-free NVLS path through allreduce_symm instead.
     if (static_cast<int64_t>(wire_bytes) <= tree_below) a = Algo::ONESHOT;
-    else a = (nvls_ok && impl_->nvls_above > 0 && static_cast<int64_t>(wire_bytes) >= impl_->nvls_above) ? Algo::NVLS
-                                                                                                        : Algo::BUTTERFLY;
+    else if (nvls_ok && impl_->nvls_above > 0 && static_cast<int64_t>(wire_bytes) >= impl_->nvls_above) a = Algo::NVLS;
+    else if (impl_->push_above > 0 && static_cast<int64_t>(wire_bytes) >= impl_->push_above) a = Algo::BUTTERFLY_PUSH;
+    else a = Algo::BUTTERFLY;
   }
   if (a == Algo::NVLS && !nvls_ok) a = Algo::BUTTERFLY;
   if (a == Algo::RING && numel < static_cast<size_t>(world_)) a = Algo::TREE;
@@ -384,6 +389,7 @@ Algo DeviceComm::allreduce(const void* const* ins, void* const* outs, size_t num
       case Algo::RING: return dev::ring_bytes(n, world_, wes);
       case Algo::TREE: return dev::tree_bytes(n, world_, wes);
       case Algo::NVLS: return dev::nvls_bytes(n, world_, wes);
+      case Algo::BUTTERFLY_PUSH: return dev::twoshot_push_bytes(n, world_, wes);
       default: return dev::twoshot_bytes(n, world_, wes);
     }
   };
@@ -422,6 +428,7 @@ Algo DeviceComm::allreduce(const void* const* ins, void* const* outs, size_t num
       case Algo::RING: rc = dev::launch_allreduce_ring(et, bw, c, a, cfg); break;
       case Algo::TREE: rc = dev::launch_allreduce_tree(et, bw, c, a, cfg); break;
       case Algo::NVLS: rc = dev::launch_allreduce_nvls(et, bw, true, c, a, nullptr, nullptr, cfg); break;
+      case Algo::BUTTERFLY_PUSH: rc = dev::launch_allreduce_twoshot_push(et, bw, c, a, cfg); break;
       default: rc = dev::launch_allreduce_twoshot(et, bw, c, a, cfg); break;
     }
     MCCL_CHECK_T(rc == cudaSuccess, CudaError, "allreduce(" << algo_name(algo) << ") launch failed: " << cudaGetErrorString(rc));
@@ -508,7 +515,9 @@ void DeviceComm::allgather(const void* const* ins, void* const* outs, size_t nby
   if (nbytes == 0) return;
   Impl::Ordered ordered(impl_.get(), stream);
   const size_t half = impl_->half_bytes;
-  const size_t piece = std::min(nbytes, half / 16 * 16);
+  // every rank's piece has a slot of its own in each arena half
+  const size_t piece = std::min(nbytes, (half / static_cast<size_t>(world_)) / 16 * 16);
+  MCCL_CHECK(piece >= 16 || nbytes < 16, "arena too small for allgather; raise MCCL_ARENA_MB");
   for (size_t done = 0; done < nbytes; done += piece) {
     const size_t n = std::min(piece, nbytes - done);
     // Piece k of every rank's block lands at out + r*nbytes + done: express it
@@ -519,6 +528,7 @@ void DeviceComm::allgather(const void* const* ins, void* const* outs, size_t nby
       a.out[v] = static_cast<char*>(outs[v]) + done;
     }
     a.numel = static_cast<long long>(n);
+    a.reserved = (impl_->ag_multicast && nvls_available() && nlocal_ == 1) ? 1 : 0;   // replicate in the switch
     a.stride = static_cast<long long>(nbytes);  // distance between ranks' blocks in the output
     dev::LaunchCfg cfg;
     cfg.nlocal = nlocal_;
@@ -563,14 +573,14 @@ void DeviceComm::alltoallv(const void* const* ins, void* const* outs, const std:
                            const std::vector<std::vector<size_t>>& out_len, void* stream) {
   MCCL_CHECK(world_ >= 2, "device alltoall needs at least two ranks");
   Impl::Ordered ordered(impl_.get(), stream);
-  const size_t slot = (impl_->half_bytes / static_cast<size_t>(world_)) / 16 * 16;
+  // One slot per source rank in each arena half, plus the control words the kernel uses to agree on the number
+  // of rounds (segments longer than a slot go through in several rounds inside the one launch).
+  const size_t ctl = static_cast<size_t>(dev::kMaxCtas) * dev::kMaxRanks * sizeof(unsigned long long);
+  MCCL_CHECK(impl_->half_bytes > ctl + 16u * static_cast<size_t>(world_), "arena too small for alltoall; raise MCCL_ARENA_MB");
+  const size_t slot = ((impl_->half_bytes - ctl) / static_cast<size_t>(world_)) / 16 * 16;
   size_t longest = 0;
   for (int v = 0; v < nlocal_; ++v)
     for (int p = 0; p < world_; ++p) longest = std::max({longest, in_len[v][p], out_len[v][p]});
-  // Every rank must run the same number of launches.  A rank only knows its
-  // own segment sizes, so segments longer than a slot are not split silently.
-  MCCL_CHECK(longest <= slot, "alltoall segment of " << longest << " bytes exceeds the " << slot
-                                                     << "-byte arena slot; raise MCCL_ARENA_MB");
   dev::A2AArgs a{};
   for (int v = 0; v < nlocal_; ++v) {
     a.in[v] = ins[v];

@@ -127,7 +127,7 @@ def cmd_tune(args) -> int:
     with open(args.sweep) as f:
         rows = [r for r in json.load(f) if r["op"] == "allreduce" and r["dtype"] == "fp32" and r["impl"].startswith("mccl:")]
     table_rows = [{"bytes": r["bytes"], "algo": r["impl"].split(":", 1)[1], "us": r["us"]} for r in rows
-                  if r["impl"].split(":", 1)[1] in ("oneshot", "twoshot", "nvls")]
+                  if r["impl"].split(":", 1)[1] in ("oneshot", "twoshot", "twoshot_push", "nvls")]
     world = rows[0]["world"] if rows else 0
     path = save_tuning_table(table_rows, world, args.out or None)
     print(path)

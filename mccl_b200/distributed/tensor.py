@@ -57,7 +57,12 @@ class DistributedTensor:
         return self._symm is not None
 
     def peer_view(self, rank: int) -> torch.Tensor:
-        """This process's mapping of a peer's shard (symmetric heap only): a load / store over NVLink."""
+        """This process's mapping of a peer's shard (symmetric heap only): every access is a load / store over NVLink.
+
+        The returned tensor aliases ANOTHER GPU's memory.  Copy it with a plain elementwise copy
+        (``.clone()``, ``dst.copy_(view)``, ``view.copy_(src)``) or hand it to this package's own kernels;
+        never pass it to a library kernel (``matmul``, attention, convolutions, ...): such kernels may read
+        their operands with cluster-multicast bulk loads, which must not touch a peer's memory."""
         if self._symm is None:
             raise RuntimeError("peer views need a CUDA shard on a backend='mccl' group")
         n = self.local.numel()

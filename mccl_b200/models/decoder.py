@@ -158,6 +158,9 @@ class Block(nn.Module):
         if cfg.act == "swiglu":
             g, u = self.gate_up(h, native).chunk(2, dim=-1)
             h = F.silu(g) * u
+        elif native:
+            from .. import ops
+            return ops.mlp_gelu(h, self.up.weight, self.up.bias, self.down.weight, self.down.bias, residual=x)
         else:
             h = self.up(h, native, act="gelu")
         return self.down(h, native, residual=x)

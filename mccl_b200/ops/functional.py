@@ -52,6 +52,18 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias=None, act: str = "none", 
     return y if residual is None else y + residual
 
 
+def mlp_gelu(x: torch.Tensor, w1: torch.Tensor, b1, w2: torch.Tensor, b2, residual=None) -> torch.Tensor:
+    """gelu(x @ w1^T + b1) @ w2^T + b2 (+ residual).  On CUDA the whole block is one autograd node whose backward
+    fuses the GELU derivative into the input-gradient GEMM of the second layer."""
+    d_in, d_ff, d_out = w1.shape[1], w1.shape[0], w2.shape[0]
+    if (x.is_cuda and _HAS["gemm_bf16"] and d_in % 64 == 0 and d_ff % 64 == 0 and d_out % 8 == 0
+            and os.environ.get("MCCL_FUSE_MLP", "1") != "0"):
+        from .native import MlpGeluFn
+        return MlpGeluFn.apply(x, w1, b1, w2, b2, residual)
+    h = linear(x, w1, b1, "gelu")
+    return linear(h, w2, b2, "none", residual)
+
+
 def embedding(ids: torch.Tensor, tok: torch.Tensor, pos=None) -> torch.Tensor:
     """bf16(tok[ids] + pos[:seq]) for ids [..., seq]; tok / pos are fp32 tables."""
     seq = ids.shape[-1]

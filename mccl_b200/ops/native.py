@@ -110,6 +110,66 @@ class LinearFn(torch.autograd.Function):
         return dx, dw, db, None, dres
 
 
+class MlpGeluFn(torch.autograd.Function):
+    """y = gelu(x @ W1^T + b1) @ W2^T + b2 (+ residual) as one autograd node, so that backward can fuse across
+    the two layers: the input-gradient GEMM of the second layer multiplies by gelu'(z) in its epilogue and
+    writes dz directly (no separate GELU-backward pass over the [tokens, d_ff] tensor)."""
+
+    @staticmethod
+    def forward(ctx, x, w1, b1, w2, b2, residual=None):
+        D, FF = w1.shape[1], w1.shape[0]
+        x2 = x.reshape(-1, D)
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        w1_16, w2_16 = _bf16_weight(w1), _bf16_weight(w2)
+        h, z = _C.gemm_bf16(x2, w1_16, b1, "gelu")
+        res2 = None
+        if residual is not None:
+            res2 = residual.reshape(-1, w2.shape[0])
+            if not res2.is_contiguous():
+                res2 = res2.contiguous()
+        y, _ = _C.gemm_bf16(h, w2_16, b2, "none", False, None, False, False, False, res2)
+        ctx.save_for_backward(x2, w1_16, w2_16, z, h)
+        ctx.params = (w1, b1, w2, b2)
+        ctx.has_residual = residual is not None
+        return y.view(*x.shape[:-1], w2.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w1_16, w2_16, z, h = ctx.saved_tensors
+        w1, b1, w2, b2 = ctx.params
+        dy2 = dy.reshape(-1, w2_16.shape[0])
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        # second layer: dz = (dy . W2) * gelu'(z) in one kernel; dW2 = dy^T . h; db2 = column sums of dy
+        dz, _ = _C.gemm_bf16(dy2, w2_16, None, "none", False, None, False, False, True, None, z)
+        grads = {}
+        for name, (w, a_mat, b_mat) in (("w2", (w2, dy2, h)), ("w1", (w1, dz, x2))):
+            sink = _sink(w)
+            if sink is not None:
+                _C.gemm_bf16(a_mat, b_mat, None, "none", True, sink, True, True, True)
+                _notify(w)
+                grads[name] = None
+            else:
+                grads[name], _ = _C.gemm_bf16(a_mat, b_mat, None, "none", True, None, False, True, True)
+        for name, (b, src) in (("b2", (b2, dy2)), ("b1", (b1, dz))):
+            if b is None:
+                grads[name] = None
+                continue
+            bsink = _sink(b)
+            if bsink is not None:
+                _C.colsum_bf16(src, bsink, True)
+                _notify(b)
+                grads[name] = None
+            else:
+                grads[name] = _C.colsum_bf16(src)
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dx, _ = _C.gemm_bf16(dz, w1_16, None, "none", False, None, False, False, True)
+            dx = dx.view(*dy.shape[:-1], w1_16.shape[1])
+        return dx, grads["w1"], grads["b1"], grads["w2"], grads["b2"], (dy if ctx.has_residual else None)
+
+
 class NormFn(torch.autograd.Function):
     """LayerNorm (bias given) or RMSNorm (bias None) over the last dimension; fp32 weight / bias."""
 

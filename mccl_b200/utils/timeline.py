@@ -113,7 +113,27 @@ def analyze(recs: np.ndarray) -> Dict:
     }
 
 
-def summarize(recs: np.ndarray) -> str:
+def gemm_shapes(recs: np.ndarray) -> List[Dict]:
+    """Per GEMM launch shape (m tiles, n tiles x k splits): launches, CTAs, and time from the first CTA's start
+    to the last CTA's end, as the kernels themselves saw it inside the running step."""
+    gemm = recs[recs[:, 2] == KIND_GEMM]
+    if len(gemm) == 0:
+        return []
+    gemm = gemm[np.argsort(gemm[:, 0])]
+    by_shape: Dict[int, List] = {}
+    for k in _launches(gemm):
+        by_shape.setdefault(int(k[0, 3]), []).append((int(k[:, 1].max() - k[:, 0].min()), len(k),
+                                                       float((k[:, 1] - k[:, 0]).mean())))
+    rows = []
+    for tag, v in by_shape.items():
+        rows.append({"m_tiles": tag >> 16, "n_tiles_x_splits": tag & 0xffff, "launches": len(v),
+                     "ctas": v[0][1], "mean_us": sum(x[0] for x in v) / len(v) / 1e3,
+                     "total_us": sum(x[0] for x in v) / 1e3, "mean_cta_us": sum(x[2] for x in v) / len(v) / 1e3})
+    rows.sort(key=lambda r: -r["total_us"])
+    return rows
+
+
+def summarize(recs: np.ndarray, shapes: bool = False) -> str:
     a = analyze(recs)
     lines = [f"span {a['span_us']:.1f} us; GEMM busy {a['gemm_busy_us']:.1f} us in {a.get('gemm_launches', 0)} launches; "
              f"collectives busy {a.get('collective_busy_us', 0.0):.1f} us, of which {a.get('collective_not_under_gemm_us', 0.0):.1f} us "
@@ -122,4 +142,9 @@ def summarize(recs: np.ndarray) -> str:
     for r in a["collectives"]:
         lines.append(f"  {r['kind']:<10} {r['start_us']:9.1f} {r['dur_us']:8.1f} {r['ctas']:5d} {r['sms']:4d} "
                      f"{r['gemm_overlap']:12.2f} {r['ctas_sharing_sm_with_gemm']:16d}")
+    if shapes:
+        lines.append("  GEMM shapes: m_tiles  n_tiles*splits  launches  ctas  mean_us  mean_cta_us  total_us")
+        for r in gemm_shapes(recs):
+            lines.append(f"    {r['m_tiles']:6d} {r['n_tiles_x_splits']:8d} {r['launches']:9d} {r['ctas']:5d} {r['mean_us']:8.1f} "
+                         f"{r['mean_cta_us']:11.1f} {r['total_us']:9.1f}")
     return "\n".join(lines)

@@ -73,7 +73,7 @@ def _gold(inputs, op):
             "product": st.prod(0)}[op]
 
 
-@pytest.mark.parametrize("algo", ["oneshot", "twoshot", "ring", "tree"])
+@pytest.mark.parametrize("algo", ["oneshot", "twoshot", "twoshot_push", "ring", "tree"])
 @pytest.mark.parametrize("dtype,wire", [(torch.float32, "native"), (torch.float32, "bf16"), (torch.bfloat16, "native"),
                                         (torch.float16, "native"), (torch.float64, "native"), (torch.int32, "native"),
                                         (torch.int64, "native")])
@@ -125,7 +125,7 @@ def test_allreduce_larger_than_arena_piece(comm):
     n = min(n, 48 << 20)
     ins = _inputs(world, n, torch.float32, seed=3)
     outs = [torch.empty_like(t) for t in ins]
-    for algo in ("twoshot", "oneshot"):
+    for algo in ("twoshot", "twoshot_push", "oneshot"):
         comm.allreduce(ins, outs, op="sum", algo=algo)
         torch.cuda.synchronize()
         assert comm.status() == 0
@@ -180,8 +180,38 @@ def test_allgather_broadcast_alltoall_emulated(comm):
     for r in range(world):
         want = torch.cat([torch.full((p + r + 1,), float(p * 10 + r)) for p in range(world)]).cuda()
         assert torch.equal(outs[r], want), ("alltoall", r)
+    # segments longer than an arena slot: the kernel agrees on the number of rounds on the device.  Only rank 0
+    # sends long segments (so the other ranks learn the round count from it), of different lengths per peer.
+    slot = comm.arena_bytes // 2 // world
+    long_elems = (slot // 4) * 2 + 1001          # fp32: a little over two slots
+    ins, outs, isp, osp = [], [], [], []
+    for r in range(world):
+        isp.append([(long_elems + 7 * p) if r == 0 else 5 for p in range(world)])
+        osp.append([(long_elems + 7 * r) if p == 0 else 5 for p in range(world)])
+        ins.append(torch.cat([torch.arange(isp[-1][p], dtype=torch.float32) + 1000.0 * (r * world + p) for p in range(world)]).cuda())
+        outs.append(torch.zeros(sum(osp[-1]), device="cuda"))
+    comm.alltoallv(ins, outs, isp, osp)
+    torch.cuda.synchronize()
+    assert comm.status() == 0
+    for r in range(world):
+        want = torch.cat([torch.arange(osp[r][p], dtype=torch.float32) + 1000.0 * (p * world + r) for p in range(world)]).cuda()
+        assert torch.equal(outs[r], want), ("alltoall rounds", r)
     comm.barrier()
     torch.cuda.synchronize()
+    assert comm.status() == 0
+
+
+def test_allgather_larger_than_a_slot(comm):
+    """A block longer than its slot (arena half / world) goes in pieces."""
+    world = comm.world
+    n = (comm.arena_bytes // 2 // world) // 4 * 2 + 333    # fp32 elements: a little over two slots per rank
+    ins = [(torch.arange(n, dtype=torch.float32) * 0.5 + r).cuda() for r in range(world)]
+    outs = [torch.zeros(n * world, device="cuda") for _ in range(world)]
+    comm.allgather(ins, outs)
+    torch.cuda.synchronize()
+    want = torch.cat(ins)
+    for r in range(world):
+        assert torch.equal(outs[r], want), r
     assert comm.status() == 0
 
 

@@ -250,3 +250,37 @@ def test_norm_residual_function_matches_separate_add():
     out2 = (ops.norm(x, w, b, 1e-5) * 2).float().sum() + (x.float() * 3).sum()
     out2.backward()
     assert _rel(gx, x.grad) < 1e-2 and _rel(gw, w.grad) < 1e-4
+
+
+@pytest.mark.parametrize("with_residual", [True, False])
+def test_fused_mlp_matches_fp32_reference(with_residual):
+    """gelu(x W1^T + b1) W2^T + b2 (+ residual) as one autograd node: forward and every gradient against a plain
+    fp32 PyTorch computation of the same block (the input-gradient GEMM of the second layer multiplies by
+    gelu'(z) in its epilogue)."""
+    from mccl_b200 import ops
+    torch.manual_seed(3)
+    T, D, FF = 256, 128, 512
+    x = (torch.randn(T, D, device="cuda") * 0.5).bfloat16().requires_grad_(True)
+    res = (torch.randn(T, D, device="cuda") * 0.5).bfloat16().requires_grad_(True) if with_residual else None
+    w1 = (torch.randn(FF, D, device="cuda") * 0.05).requires_grad_(True)
+    b1 = (torch.randn(FF, device="cuda") * 0.1).requires_grad_(True)
+    w2 = (torch.randn(D, FF, device="cuda") * 0.05).requires_grad_(True)
+    b2 = (torch.randn(D, device="cuda") * 0.1).requires_grad_(True)
+    y = ops.mlp_gelu(x, w1, b1, w2, b2, residual=res)
+    dy = (torch.randn(T, D, device="cuda") * 0.1).bfloat16()
+    y.backward(dy)
+    got = [x.grad, w1.grad, b1.grad, w2.grad, b2.grad] + ([res.grad] if with_residual else [])
+    # fp32 reference on the bf16-rounded inputs and weights
+    xr = x.detach().float().requires_grad_(True)
+    rr = res.detach().float().requires_grad_(True) if with_residual else None
+    w1r, b1r = w1.detach().bfloat16().float().requires_grad_(True), b1.detach().clone().requires_grad_(True)
+    w2r, b2r = w2.detach().bfloat16().float().requires_grad_(True), b2.detach().clone().requires_grad_(True)
+    yr = F.gelu(xr @ w1r.t() + b1r) @ w2r.t() + b2r
+    if with_residual:
+        yr = yr + rr
+    yr.backward(dy.float())
+    assert _rel(y, yr) < 2e-2
+    want = [xr.grad, w1r.grad, b1r.grad, w2r.grad, b2r.grad] + ([rr.grad] if with_residual else [])
+    for g, w, name in zip(got, want, ["dx", "dw1", "db1", "dw2", "db2", "dres"]):
+        assert _rel(g, w) < 2e-2, (name, _rel(g, w))
+    assert _C().gemm_error_flag() == 0
