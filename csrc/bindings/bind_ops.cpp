@@ -39,6 +39,7 @@ __nv_bfloat16* bf(const at::Tensor& t) { return reinterpret_cast<__nv_bfloat16*>
 int parse_epilogue(const std::string& s, bool has_bias) {
   if (s == "none") return has_bias ? ops::EPI_BIAS : ops::EPI_NONE;
   if (s == "gelu") return has_bias ? ops::EPI_BIAS_GELU : ops::EPI_GELU;
+  if (s == "gelu_d") return has_bias ? ops::EPI_BIAS_GELU_D : ops::EPI_GELU_D;   // aux = gelu'(z) instead of z
   MCCL_CHECK(false, "unknown GEMM epilogue '" << s << "'");
   return 0;
 }
@@ -91,7 +92,7 @@ void bind_ops(py::module_& m) {
       "gemm_bf16",
       [](const at::Tensor& a, const at::Tensor& b, const c10::optional<at::Tensor>& bias, const std::string& epilogue,
          bool out_fp32, const c10::optional<at::Tensor>& out, bool accumulate, bool a_t, bool b_t,
-         const c10::optional<at::Tensor>& residual, const c10::optional<at::Tensor>& dgelu_z) {
+         const c10::optional<at::Tensor>& residual, const c10::optional<at::Tensor>& mul) {
         need_cuda(a, "gemm(a)");
         need_cuda(b, "gemm(b)");
         MCCL_CHECK_TENSOR(a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16, "gemm: operands must be bf16");
@@ -133,7 +134,8 @@ void bind_ops(py::module_& m) {
         }
         g.epilogue = parse_epilogue(epilogue, g.bias != nullptr);
         at::Tensor aux;
-        if (g.epilogue == ops::EPI_BIAS_GELU || g.epilogue == ops::EPI_GELU) {
+        if (g.epilogue == ops::EPI_BIAS_GELU || g.epilogue == ops::EPI_GELU || g.epilogue == ops::EPI_BIAS_GELU_D ||
+            g.epilogue == ops::EPI_GELU_D) {
           MCCL_CHECK_TENSOR(d.is_contiguous(), "gemm: GELU epilogue needs a contiguous output");
           aux = at::empty({M, N}, a.options());
           g.aux = bf(aux);
@@ -143,11 +145,11 @@ void bind_ops(py::module_& m) {
           MCCL_CHECK_TENSOR(residual->numel() == M * N && d.is_contiguous(), "gemm: residual must be a contiguous [M, N] tensor");
           g.residual = bf(*residual);
         }
-        if (dgelu_z.has_value() && dgelu_z->defined()) {
-          need(*dgelu_z, at::kBFloat16, "gemm(dgelu_z)");
-          MCCL_CHECK_TENSOR(dgelu_z->numel() == M * N && d.is_contiguous() && !out_fp32,
-                            "gemm: dgelu_z must be a contiguous [M, N] bf16 tensor and the output bf16");
-          g.dgelu_z = bf(*dgelu_z);
+        if (mul.has_value() && mul->defined()) {
+          need(*mul, at::kBFloat16, "gemm(mul)");
+          MCCL_CHECK_TENSOR(mul->numel() == M * N && d.is_contiguous() && !out_fp32,
+                            "gemm: mul must be a contiguous [M, N] bf16 tensor and the output bf16");
+          g.mul = bf(*mul);
         }
         cudaError_t rc = ops::gemm_bf16_tn(g, stream_of(a));
         MCCL_CHECK_T(rc == cudaSuccess, CudaError,
@@ -157,7 +159,7 @@ void bind_ops(py::module_& m) {
       },
       py::arg("a"), py::arg("b"), py::arg("bias") = py::none(), py::arg("epilogue") = "none", py::arg("out_fp32") = false,
       py::arg("out") = py::none(), py::arg("accumulate") = false, py::arg("a_t") = false, py::arg("b_t") = false,
-      py::arg("residual") = py::none(), py::arg("dgelu_z") = py::none());
+      py::arg("residual") = py::none(), py::arg("mul") = py::none());
 
   m.def(
       "norm_fwd",
@@ -267,6 +269,45 @@ void bind_ops(py::module_& m) {
       },
       py::arg("logits"), py::arg("targets"), py::arg("grad_scale") = 1.0,
       "Returns per-row losses; overwrites logits with (softmax - onehot) * grad_scale.");
+
+  // ---- causal self-attention (head dimension 64) on the fused QKV projection ----
+  m.def(
+      "attn_fwd",
+      [](const at::Tensor& qkv, double scale) {
+        need(qkv, at::kBFloat16, "attention(qkv)");
+        MCCL_CHECK_TENSOR(qkv.dim() == 5 && qkv.size(2) == 3 && qkv.size(4) == 64, "attention: qkv must be [B, S, 3, H, 64]");
+        const int64_t B = qkv.size(0), S = qkv.size(1), H = qkv.size(3);
+        c10::cuda::CUDAGuard guard(qkv.device());
+        at::Tensor o = at::empty({B, S, H * 64}, qkv.options());
+        at::Tensor lse = at::empty({B, H, S}, qkv.options().dtype(at::kFloat));
+        cudaError_t rc = ops::attention_fwd(bf(qkv), bf(o), lse.data_ptr<float>(), static_cast<int>(B), static_cast<int>(S),
+                                            static_cast<int>(H), static_cast<float>(scale), stream_of(qkv));
+        MCCL_CHECK_T(rc == cudaSuccess, CudaError, "attention forward [B " << B << ", S " << S << ", H " << H << "] failed: "
+                                                                           << cudaGetErrorString(rc));
+        return std::make_pair(o, lse);
+      },
+      py::arg("qkv"), py::arg("scale"), "Causal attention; returns (o [B, S, H*64] bf16, lse [B, H, S] fp32, log2 domain).  S % 128 == 0.");
+  m.def(
+      "attn_bwd",
+      [](const at::Tensor& qkv, const at::Tensor& o, const at::Tensor& d_o, const at::Tensor& lse, double scale) {
+        need(qkv, at::kBFloat16, "attention_bwd(qkv)");
+        need(o, at::kBFloat16, "attention_bwd(o)");
+        need(d_o, at::kBFloat16, "attention_bwd(d_o)");
+        need(lse, at::kFloat, "attention_bwd(lse)");
+        MCCL_CHECK_TENSOR(qkv.dim() == 5 && qkv.size(2) == 3 && qkv.size(4) == 64, "attention_bwd: qkv must be [B, S, 3, H, 64]");
+        const int64_t B = qkv.size(0), S = qkv.size(1), H = qkv.size(3);
+        MCCL_CHECK_TENSOR(o.numel() == B * S * H * 64 && d_o.numel() == o.numel() && lse.numel() == B * H * S,
+                          "attention_bwd: operand sizes do not match qkv");
+        c10::cuda::CUDAGuard guard(qkv.device());
+        at::Tensor dqkv = at::empty_like(qkv);
+        cudaError_t rc = ops::attention_bwd(bf(qkv), bf(o), bf(d_o), lse.data_ptr<float>(), bf(dqkv), static_cast<int>(B),
+                                            static_cast<int>(S), static_cast<int>(H), static_cast<float>(scale), stream_of(qkv));
+        MCCL_CHECK_T(rc == cudaSuccess, CudaError, "attention backward [B " << B << ", S " << S << ", H " << H << "] failed: "
+                                                                            << cudaGetErrorString(rc));
+        return dqkv;
+      },
+      py::arg("qkv"), py::arg("o"), py::arg("d_o"), py::arg("lse"), py::arg("scale"),
+      "Gradient of the whole qkv tensor.  S must be 128 or 256.");
 
   // ---- tensor-parallel GEMMs fused with their collective ----
   py::class_<ops::TpGemm>(m, "TpGemm")

@@ -48,8 +48,10 @@ cudaError_t launch_record(const char* kernel, const char* file, int line, dim3 g
 
 bool pdl_enabled() {
   static const bool on = [] {
+    // Off unless MCCL_PDL=1: on the 70M training step (one CUDA graph of ~500 kernels) the programmatic edges
+    // measured 0.2 ms per step slower than plain stream order (7.08 against 6.88 ms on one B200).
     const char* v = std::getenv("MCCL_PDL");
-    return !(v && v[0] == '0');
+    return v && v[0] == '1';
   }();
   return on;
 }

@@ -35,8 +35,9 @@ uint64_t launch_total();
 // allocation, descriptor prefetch, index arithmetic) and then block in pdl_wait() until every earlier kernel of the
 // stream has finished and its memory is visible.  Such a kernel must call pdl_wait() before its first access to
 // global memory, read or write.  pdl_trigger() tells the hardware that the kernels after this one may start their
-// set-up; kernels that never call it release their dependents when they exit.  MCCL_PDL=0 turns the launch attribute
-// off (the device calls are then no-ops), which is the switch for A/B timing.
+// set-up; kernels that never call it release their dependents when they exit.  The launch attribute is only set with
+// MCCL_PDL=1 (without it the device calls are no-ops and the stream serialises as usual): measured on the training
+// step it did not pay, so it is an option, not the default.
 bool pdl_enabled();
 template <typename... KArgs, typename... Args>
 cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {

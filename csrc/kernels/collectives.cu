@@ -68,6 +68,36 @@ __device__ __forceinline__ void cta_copy_bytes(char* dst, const char* src, unsig
   }
 }
 
+// Same copy, for sources that a peer rewrites while this kernel runs (staging slots that are reused round after
+// round inside one launch): the loads go to L2 (ld.global.cg), so a line that this SM cached in an earlier round
+// cannot be served again from L1.
+__device__ __forceinline__ void cta_copy_bytes_uncached(char* dst, const char* src, unsigned long long n) {
+  if (n == 0) return;
+  if (aligned16(dst) && aligned16(src)) {
+    unsigned long long vecs = n / 16;
+    unsigned long long i = threadIdx.x;
+    for (; i + 3ull * blockDim.x < vecs; i += 4ull * blockDim.x) {
+      uint4 a = __ldcg(reinterpret_cast<const uint4*>(src) + i);
+      uint4 b = __ldcg(reinterpret_cast<const uint4*>(src) + i + blockDim.x);
+      uint4 c = __ldcg(reinterpret_cast<const uint4*>(src) + i + 2ull * blockDim.x);
+      uint4 d = __ldcg(reinterpret_cast<const uint4*>(src) + i + 3ull * blockDim.x);
+      reinterpret_cast<uint4*>(dst)[i] = a;
+      reinterpret_cast<uint4*>(dst)[i + blockDim.x] = b;
+      reinterpret_cast<uint4*>(dst)[i + 2ull * blockDim.x] = c;
+      reinterpret_cast<uint4*>(dst)[i + 3ull * blockDim.x] = d;
+    }
+    for (; i < vecs; i += blockDim.x) reinterpret_cast<uint4*>(dst)[i] = __ldcg(reinterpret_cast<const uint4*>(src) + i);
+    for (unsigned long long b = vecs * 16 + threadIdx.x; b < n; b += blockDim.x) dst[b] = __ldcg(src + b);
+  } else if (((reinterpret_cast<uintptr_t>(dst) | reinterpret_cast<uintptr_t>(src)) & 3u) == 0) {
+    unsigned long long words = n / 4;
+    for (unsigned long long i = threadIdx.x; i < words; i += blockDim.x)
+      reinterpret_cast<uint32_t*>(dst)[i] = __ldcg(reinterpret_cast<const uint32_t*>(src) + i);
+    for (unsigned long long b = words * 4 + threadIdx.x; b < n; b += blockDim.x) dst[b] = __ldcg(src + b);
+  } else {
+    for (unsigned long long b = threadIdx.x; b < n; b += blockDim.x) dst[b] = __ldcg(src + b);
+  }
+}
+
 // Copies n bytes from src to up to kMaxRanks destinations (peers' memory): every 16-byte unit is loaded once and
 // stored to each destination, several units in flight per thread.  Stores to peers are posted, so this is the fast
 // direction over NVLink.  Destinations must be 16-byte aligned; an unaligned source takes the per-destination path.
@@ -1014,8 +1044,12 @@ __global__ void __launch_bounds__(kThreads) alltoall_kernel(DevComm c, A2AArgs a
     for (int k = 0; k < N; ++k) {
       const int q = (rank + k) % N;
       const unsigned long long len = a.in_len[vr][q] > lo ? (a.in_len[vr][q] - lo < slot ? a.in_len[vr][q] - lo : slot) : 0;
+      // The slot is cut among the CTAs once, whatever the round's length: a byte of the slot then belongs to the same
+      // CTA index in every round, and the per-CTA meetings below are all the ordering a slot byte needs.
       unsigned long long b0, b1;
-      cta_byte_span(len, b0, b1);
+      cta_byte_span(slot, b0, b1);
+      b0 = b0 < len ? b0 : len;
+      b1 = b1 < len ? b1 : len;
       if (q == rank)
         cta_copy_bytes(out + a.out_off[vr][q] + lo + b0, in + a.in_off[vr][q] + lo + b0, b1 - b0);
       else
@@ -1026,8 +1060,10 @@ __global__ void __launch_bounds__(kThreads) alltoall_kernel(DevComm c, A2AArgs a
       const int p = (rank + k) % N;
       const unsigned long long len = a.out_len[vr][p] > lo ? (a.out_len[vr][p] - lo < slot ? a.out_len[vr][p] - lo : slot) : 0;
       unsigned long long b0, b1;
-      cta_byte_span(len, b0, b1);
-      cta_copy_bytes(out + a.out_off[vr][p] + lo + b0, c.arena[rank] + base + static_cast<size_t>(p) * slot + b0, b1 - b0);
+      cta_byte_span(slot, b0, b1);
+      b0 = b0 < len ? b0 : len;
+      b1 = b1 < len ? b1 : len;
+      cta_copy_bytes_uncached(out + a.out_off[vr][p] + lo + b0, c.arena[rank] + base + static_cast<size_t>(p) * slot + b0, b1 - b0);
     }
     // the slots are overwritten in the next round: everybody must have unpacked first
     if (r + 1 < rounds && barrier_all(c, vr, rank, s, PH_GATHER)) break;
@@ -1071,8 +1107,11 @@ __global__ void __launch_bounds__(kThreads) p2p_kernel(P2PComm c, P2PArgs a) {
     const uint32_t seq = base + static_cast<uint32_t>(k) + 1u;
     const unsigned long long off = k * slot;
     const unsigned long long len = a.nbytes - off < slot ? a.nbytes - off : slot;
+    // fixed partition of the slot among the CTAs (clipped to this chunk): a slot byte has one owner in every chunk
     unsigned long long b0, b1;
-    cta_byte_span(len, b0, b1);
+    cta_byte_span(slot, b0, b1);
+    b0 = b0 < len ? b0 : len;
+    b1 = b1 < len ? b1 : len;
     if (sending) {
       // buffer seq & 1 last held chunk seq - 2: the receiver must have copied that one out
       failed = wait_flag(c.free_[rank] + blockIdx.x * kMaxRanks + peer, seq - 2u, PH_SEND);
@@ -1088,7 +1127,7 @@ __global__ void __launch_bounds__(kThreads) p2p_kernel(P2PComm c, P2PArgs a) {
       failed = wait_flag(c.ready[rank] + blockIdx.x * kMaxRanks + peer, seq, PH_RECV);
       if (failed) break;
       const char* src = c.region[rank] + (static_cast<size_t>(peer) * 2 + (seq & 1u)) * slot;
-      cta_copy_bytes(user + off + b0, src + b0, b1 - b0);
+      cta_copy_bytes_uncached(user + off + b0, src + b0, b1 - b0);   // the two buffers are reused chunk after chunk
       __syncthreads();
       if (threadIdx.x == 0) st_release_sys(c.free_[peer] + blockIdx.x * kMaxRanks + rank, seq);
     }

@@ -21,7 +21,7 @@ struct GemmDev {
   __nv_bfloat16* aux;
   const float* bias;
   const __nv_bfloat16* residual;
-  const __nv_bfloat16* dgelu_z;   // when set: D = acc * gelu'(z), the backward of a GELU fused into the producing GEMM
+  const __nv_bfloat16* mul;       // when set: D = acc * mul, e.g. the backward of a GELU (mul = saved gelu'(z)) fused into the producing GEMM
   int m, n, k;
   int ldd;
   int d_fp32;
@@ -45,10 +45,32 @@ __device__ __forceinline__ void epilogue_store(const GemmDev& g, int row, int co
 #pragma unroll
   for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
   const int ncols = (g.n - col0) < 32 ? (g.n - col0) : 32;  // multiple of 8
-  if (g.epilogue == EPI_BIAS || g.epilogue == EPI_BIAS_GELU) {
+  if (g.epilogue == EPI_BIAS || g.epilogue == EPI_BIAS_GELU || g.epilogue == EPI_BIAS_GELU_D) {
 #pragma unroll
     for (int j = 0; j < 32; ++j)
       if (j < ncols) v[j] += __ldg(g.bias + col0 + j);
+  }
+  if (g.epilogue == EPI_BIAS_GELU_D || g.epilogue == EPI_GELU_D) {
+    // value and derivative share the erf; the derivative is what backward needs, so it is saved instead of z
+    float dv[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      const float x = v[j];
+      const float cdf = 0.5f * (1.f + erff(x * 0.70710678f));
+      dv[j] = cdf + x * 0.39894228f * __expf(-0.5f * x * x);
+      v[j] = x * cdf;
+    }
+    __nv_bfloat16* arow = g.aux + static_cast<size_t>(row) * g.ldd + col0;
+#pragma unroll
+    for (int j8 = 0; j8 < 4; ++j8) {
+      if (j8 * 8 < ncols) {
+        uint4 pk;
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(dv[j8 * 8 + 2 * i], dv[j8 * 8 + 2 * i + 1]);
+        *reinterpret_cast<uint4*>(arow + j8 * 8) = pk;
+      }
+    }
   }
   if (g.epilogue == EPI_BIAS_GELU || g.epilogue == EPI_GELU) {
     __nv_bfloat16* zrow = g.aux + static_cast<size_t>(row) * g.ldd + col0;
@@ -65,19 +87,18 @@ __device__ __forceinline__ void epilogue_store(const GemmDev& g, int row, int co
 #pragma unroll
     for (int j = 0; j < 32; ++j) v[j] = gelu_erf(v[j]);
   }
-  if (g.dgelu_z) {
-    const __nv_bfloat16* zrow = g.dgelu_z + static_cast<size_t>(row) * g.ldd + col0;
+  if (g.mul) {
+    const __nv_bfloat16* mrow = g.mul + static_cast<size_t>(row) * g.ldd + col0;
 #pragma unroll
     for (int j8 = 0; j8 < 4; ++j8) {
       if (j8 * 8 < ncols) {
-        const uint4 pk = *reinterpret_cast<const uint4*>(zrow + j8 * 8);
+        const uint4 pk = *reinterpret_cast<const uint4*>(mrow + j8 * 8);
         const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&pk);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const float2 t = __bfloat1622float2(h[i]);
-          const float x0 = t.x, x1 = t.y;
-          v[j8 * 8 + 2 * i] *= 0.5f * (1.f + erff(x0 * 0.70710678f)) + x0 * 0.39894228f * __expf(-0.5f * x0 * x0);
-          v[j8 * 8 + 2 * i + 1] *= 0.5f * (1.f + erff(x1 * 0.70710678f)) + x1 * 0.39894228f * __expf(-0.5f * x1 * x1);
+          v[j8 * 8 + 2 * i] *= t.x;
+          v[j8 * 8 + 2 * i + 1] *= t.y;
         }
       }
     }

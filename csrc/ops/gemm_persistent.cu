@@ -678,7 +678,7 @@ cudaError_t launch_persistent_cfg(const GemmArgs& a, const FusedDev& f_in, int m
   g.aux = a.aux;
   g.bias = a.bias;
   g.residual = a.residual;
-  g.dgelu_z = a.dgelu_z;
+  g.mul = a.mul;
   g.m = a.m;
   g.n = a.n;
   g.k = a.k;
@@ -696,7 +696,7 @@ cudaError_t launch_persistent_cfg(const GemmArgs& a, const FusedDev& f_in, int m
     const char* v = std::getenv("MCCL_GEMM_SPLITK");
     return !(v && v[0] == '0');
   }();
-  if (allow_split && a.d_fp32 && a.epilogue == EPI_NONE && !a.residual && !a.dgelu_z && f.mode == FUSE_NONE) {
+  if (allow_split && a.d_fp32 && a.epilogue == EPI_NONE && !a.residual && !a.mul && f.mode == FUSE_NONE) {
     const int splits = choose_splits(tiles, a.k / BK, sm_count());
     if (splits > 1) {
       if (!a.accumulate) {

@@ -182,7 +182,7 @@ cudaError_t launch_cfg(const GemmArgs& a, cudaStream_t stream) {
   g.aux = a.aux;
   g.bias = a.bias;
   g.residual = a.residual;
-  g.dgelu_z = a.dgelu_z;
+  g.mul = a.mul;
   g.m = a.m;
   g.n = a.n;
   g.k = a.k;
@@ -213,11 +213,13 @@ cudaError_t gemm_bf16_tn(const GemmArgs& a, cudaStream_t stream) {
   if ((reinterpret_cast<uintptr_t>(a.a) | reinterpret_cast<uintptr_t>(a.b) | reinterpret_cast<uintptr_t>(a.d)) & 15u)
     return unsupported("operand pointers must be 16-byte aligned");
   if (a.aux && (reinterpret_cast<uintptr_t>(a.aux) & 15u)) return unsupported("aux pointer must be 16-byte aligned");
-  if ((a.epilogue == EPI_BIAS || a.epilogue == EPI_BIAS_GELU) && !a.bias) return cudaErrorInvalidValue;
-  if ((a.epilogue == EPI_BIAS_GELU || a.epilogue == EPI_GELU) && (!a.aux || a.d_fp32)) return cudaErrorInvalidValue;
+  if ((a.epilogue == EPI_BIAS || a.epilogue == EPI_BIAS_GELU || a.epilogue == EPI_BIAS_GELU_D) && !a.bias) return cudaErrorInvalidValue;
+  if ((a.epilogue == EPI_BIAS_GELU || a.epilogue == EPI_GELU || a.epilogue == EPI_BIAS_GELU_D || a.epilogue == EPI_GELU_D) &&
+      (!a.aux || a.d_fp32))
+    return cudaErrorInvalidValue;
   if (a.accumulate && !a.d_fp32) return cudaErrorInvalidValue;
   if (a.residual && (reinterpret_cast<uintptr_t>(a.residual) & 15u)) return unsupported("residual pointer must be 16-byte aligned");
-  if (a.dgelu_z && ((reinterpret_cast<uintptr_t>(a.dgelu_z) & 15u) || a.d_fp32)) return unsupported("dgelu_z must be 16-byte aligned and the output bf16");
+  if (a.mul && ((reinterpret_cast<uintptr_t>(a.mul) & 15u) || a.d_fp32)) return unsupported("mul must be 16-byte aligned and the output bf16");
   if (a.a_mn_major && a.m % 8 != 0) return unsupported("an MN-major A needs M to be a multiple of 8");
   // Default: persistent kernel (one CTA per SM, double-buffered accumulator).
   // MCCL_GEMM_KERNEL=tile selects the one-tile-per-CTA kernel below.

@@ -64,12 +64,23 @@ cudaError_t embed_fwd(const long long* ids, const float* tok, const float* pos, 
 cudaError_t embed_bwd(const long long* ids, const __nv_bfloat16* dy, float* dtok, float* dpos, int tokens, int seq, int dim,
                       int vocab, cudaStream_t stream);
 
+// ---- causal self-attention, head dimension 64, straight from the fused QKV projection.
+// qkv: [B, S, 3, H, 64] bf16; o: [B, S, H, 64] bf16; lse: [B, H, S] fp32 (log2 domain, saved for backward).
+// Forward needs S % 128 == 0; backward S == 128 or 256 (cudaErrorNotSupported otherwise: the caller falls back).
+cudaError_t attention_fwd(const __nv_bfloat16* qkv, __nv_bfloat16* o, float* lse, int B, int S, int H, float softmax_scale,
+                          cudaStream_t stream);
+// dqkv: [B, S, 3, H, 64] bf16, every element written.
+cudaError_t attention_bwd(const __nv_bfloat16* qkv, const __nv_bfloat16* o, const __nv_bfloat16* d_o, const float* lse,
+                          __nv_bfloat16* dqkv, int B, int S, int H, float softmax_scale, cudaStream_t stream);
+
 // ---- tcgen05 GEMM: D[M,N] = A[M,K] · B[N,K]^T (+ bias[N]) (GELU) ; A, B bf16 with K contiguous.
 enum GemmEpilogue : int {
   EPI_NONE = 0,       // D = acc
   EPI_BIAS = 1,       // D = acc + bias[n]
   EPI_BIAS_GELU = 2,  // Z = acc + bias[n] (written to aux), D = gelu(Z)
   EPI_GELU = 3,       // Z = acc (written to aux), D = gelu(Z)
+  EPI_BIAS_GELU_D = 4,  // Z = acc + bias[n], D = gelu(Z), aux = gelu'(Z): backward then only multiplies (see GemmArgs::mul)
+  EPI_GELU_D = 5,       // the same without bias
 };
 struct GemmArgs {
   const __nv_bfloat16* a = nullptr;  // [M, K], row stride lda (elements); a_mn_major: stored [K, M]
@@ -80,7 +91,7 @@ struct GemmArgs {
   __nv_bfloat16* aux = nullptr;      // [M, N] pre-activation (GELU epilogues)
   const float* bias = nullptr;       // [N]
   const __nv_bfloat16* residual = nullptr;  // [M, N] added after bias / activation, row stride ldd
-  const __nv_bfloat16* dgelu_z = nullptr;   // [M, N] pre-activation: D = acc * gelu'(z) (input gradient through a GELU), row stride ldd
+  const __nv_bfloat16* mul = nullptr;       // [M, N]: D = acc * mul (e.g. the saved gelu'(z): the input gradient through a GELU), row stride ldd
   int m = 0, n = 0, k = 0;
   int lda = 0, ldb = 0, ldd = 0;
   bool d_fp32 = false;

@@ -609,11 +609,10 @@ void DeviceComm::alltoallv(const void* const* ins, void* const* outs, const std:
 
 // ---------------------------------------------------------------- send/recv --
 namespace {
-int p2p_ctas(size_t nbytes, size_t slot) {
-  // both sides derive the same count from the message size alone
-  const size_t per_chunk = std::min(nbytes, slot);
-  const size_t want = (per_chunk + (256u << 10) - 1) / (256u << 10);
-  return static_cast<int>(std::max<size_t>(1, std::min<size_t>(want, dev::kP2PMaxCtas)));
+int p2p_ctas(size_t, size_t) {
+  // Always the same number: a slot byte is then owned by the same CTA index in every message of a pair, and the
+  // per-CTA ready / free flags are all the ordering the two slot buffers need across messages of any size.
+  return dev::kP2PMaxCtas;
 }
 }  // namespace
 

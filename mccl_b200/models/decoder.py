@@ -147,13 +147,18 @@ class Block(nn.Module):
         cfg = self.cfg
         B, S, D = x.shape
         h, x = self.ln1.with_residual(x, native)
-        qkv = self.qkv(h, native).view(B, S, 3, cfg.n_heads, cfg.head_dim)
-        # unbind, not three selects: its backward is one stack instead of three zero-filled tensors and two adds
-        q, k, v = (t.transpose(1, 2) for t in qkv.unbind(2))
-        if rope is not None:
-            q, k = apply_rope(q, *rope), apply_rope(k, *rope)
-        a = F.scaled_dot_product_attention(q, k, v, is_causal=True)
-        x = self.proj(a.transpose(1, 2).reshape(B, S, D), native, residual=x)
+        qkv = self.qkv(h, native)
+        if native and rope is None:
+            from .. import ops
+            a = ops.causal_attention(qkv, cfg.n_heads)   # own kernels for head dimension 64, S in {128, 256}
+        else:
+            qkv = qkv.view(B, S, 3, cfg.n_heads, cfg.head_dim)
+            # unbind, not three selects: its backward is one stack instead of three zero-filled tensors and two adds
+            q, k, v = (t.transpose(1, 2) for t in qkv.unbind(2))
+            if rope is not None:
+                q, k = apply_rope(q, *rope), apply_rope(k, *rope)
+            a = F.scaled_dot_product_attention(q, k, v, is_causal=True).transpose(1, 2).reshape(B, S, D)
+        x = self.proj(a, native, residual=x)
         h, x = self.ln2.with_residual(x, native)
         if cfg.act == "swiglu":
             g, u = self.gate_up(h, native).chunk(2, dim=-1)

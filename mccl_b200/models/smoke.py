@@ -10,9 +10,10 @@ def run_smoke(device: torch.device) -> float:
     from .decoder import build_decoder
 
     torch.manual_seed(0)
-    model = build_decoder("tiny", native=True).to(device)
+    # two heads of 64 and a sequence of 128, so that attention runs on this package's kernels too
+    model = build_decoder("tiny", native=True, n_heads=2, max_seq=128).to(device)
     trainer = DDPTrainer(model, device, use_graph=False)
-    tokens = torch.randint(0, model.cfg.vocab, (4, 65), device=device)
+    tokens = torch.randint(0, model.cfg.vocab, (4, 129), device=device)
     before = ops.launch_count()
     l0 = float(trainer.step(tokens[:, :-1].contiguous(), tokens[:, 1:].contiguous()).item())
     for _ in range(3):

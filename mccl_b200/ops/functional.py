@@ -9,7 +9,8 @@ import torch.nn.functional as F
 
 from .. import _C
 
-_HAS = {name: hasattr(_C, name) for name in ("gemm_bf16", "norm_fwd", "norm_bwd", "adamw_flat", "ce_fwd_bwd", "embed_fwd")}
+_HAS = {name: hasattr(_C, name) for name in ("gemm_bf16", "norm_fwd", "norm_bwd", "adamw_flat", "ce_fwd_bwd", "embed_fwd",
+                                             "attn_fwd")}
 _launches = 0
 
 
@@ -50,6 +51,26 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias=None, act: str = "none", 
     y = F.linear(x, weight.to(x.dtype), None if bias is None else bias.to(x.dtype))
     y = F.gelu(y) if act == "gelu" else y
     return y if residual is None else y + residual
+
+
+def native_attention_supported(seq: int, head_dim: int) -> bool:
+    """Shapes the attention kernels cover: head dimension 64, sequences of 128 or 256 (training needs backward)."""
+    return bool(_HAS.get("attn_fwd")) and head_dim == 64 and seq in (128, 256) and os.environ.get("MCCL_NATIVE_ATTN", "1") != "0"
+
+
+def causal_attention(qkv: torch.Tensor, n_heads: int) -> torch.Tensor:
+    """Causal self-attention.  qkv: [B, S, 3 * n_heads * head_dim] (or already [B, S, 3, H, Dh]), the output of a
+    fused QKV projection; returns [B, S, n_heads * head_dim].  On CUDA with head dimension 64 and S in {128, 256}
+    this is one kernel each way; otherwise PyTorch's scaled_dot_product_attention on views of the same tensor."""
+    B, S = qkv.shape[0], qkv.shape[1]
+    hd = qkv.numel() // (B * S * 3 * n_heads)
+    q5 = qkv.view(B, S, 3, n_heads, hd)
+    if qkv.is_cuda and qkv.dtype == torch.bfloat16 and native_attention_supported(S, hd):
+        from .native import CausalAttentionFn
+        return CausalAttentionFn.apply(q5, 1.0 / (hd ** 0.5))
+    q, k, v = (t.transpose(1, 2) for t in q5.unbind(2))
+    a = F.scaled_dot_product_attention(q, k, v, is_causal=True)
+    return a.transpose(1, 2).reshape(B, S, n_heads * hd)
 
 
 def mlp_gelu(x: torch.Tensor, w1: torch.Tensor, b1, w2: torch.Tensor, b2, residual=None) -> torch.Tensor:

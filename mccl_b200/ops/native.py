@@ -112,8 +112,10 @@ class LinearFn(torch.autograd.Function):
 
 class MlpGeluFn(torch.autograd.Function):
     """y = gelu(x @ W1^T + b1) @ W2^T + b2 (+ residual) as one autograd node, so that backward can fuse across
-    the two layers: the input-gradient GEMM of the second layer multiplies by gelu'(z) in its epilogue and
-    writes dz directly (no separate GELU-backward pass over the [tokens, d_ff] tensor)."""
+    the two layers: the first GEMM's epilogue saves gelu'(z) next to gelu(z) (they share the erf), and the
+    input-gradient GEMM of the second layer multiplies by it in its epilogue and writes dz directly, so there is
+    no separate GELU-backward pass over the [tokens, d_ff] tensor.  (Evaluating erf and exp in the backward
+    epilogue instead was measured slower than the separate kernel: four epilogue warps per SM are too few for it.)"""
 
     @staticmethod
     def forward(ctx, x, w1, b1, w2, b2, residual=None):
@@ -122,7 +124,7 @@ class MlpGeluFn(torch.autograd.Function):
         if not x2.is_contiguous():
             x2 = x2.contiguous()
         w1_16, w2_16 = _bf16_weight(w1), _bf16_weight(w2)
-        h, z = _C.gemm_bf16(x2, w1_16, b1, "gelu")
+        h, z = _C.gemm_bf16(x2, w1_16, b1, "gelu_d")   # z holds gelu'(pre-activation)
         res2 = None
         if residual is not None:
             res2 = residual.reshape(-1, w2.shape[0])
@@ -141,7 +143,7 @@ class MlpGeluFn(torch.autograd.Function):
         dy2 = dy.reshape(-1, w2_16.shape[0])
         if not dy2.is_contiguous():
             dy2 = dy2.contiguous()
-        # second layer: dz = (dy . W2) * gelu'(z) in one kernel; dW2 = dy^T . h; db2 = column sums of dy
+        # second layer: dz = (dy . W2) * gelu'(pre-activation) in one kernel; dW2 = dy^T . h; db2 = column sums of dy
         dz, _ = _C.gemm_bf16(dy2, w2_16, None, "none", False, None, False, False, True, None, z)
         grads = {}
         for name, (w, a_mat, b_mat) in (("w2", (w2, dy2, h)), ("w1", (w1, dz, x2))):
@@ -168,6 +170,26 @@ class MlpGeluFn(torch.autograd.Function):
             dx, _ = _C.gemm_bf16(dz, w1_16, None, "none", False, None, False, False, True)
             dx = dx.view(*dy.shape[:-1], w1_16.shape[1])
         return dx, grads["w1"], grads["b1"], grads["w2"], grads["b2"], (dy if ctx.has_residual else None)
+
+
+class CausalAttentionFn(torch.autograd.Function):
+    """Causal self-attention on the output of the fused QKV projection, viewed as [B, S, 3, H, 64]: one kernel
+    forward, one backward, both on the tcgen05 tensor cores; the gradient comes back for the whole qkv tensor, so
+    no slices, transposes or concatenations surround the kernels."""
+
+    @staticmethod
+    def forward(ctx, qkv, scale):
+        q5 = qkv if qkv.is_contiguous() else qkv.contiguous()
+        o, lse = _C.attn_fwd(q5, scale)
+        ctx.save_for_backward(q5, o, lse)
+        ctx.scale = scale
+        return o
+
+    @staticmethod
+    def backward(ctx, d_o):
+        q5, o, lse = ctx.saved_tensors
+        d = d_o if d_o.is_contiguous() else d_o.contiguous()
+        return _C.attn_bwd(q5, o, d, lse, ctx.scale), None
 
 
 class NormFn(torch.autograd.Function):

@@ -195,7 +195,10 @@ def test_allgather_broadcast_alltoall_emulated(comm):
     assert comm.status() == 0
     for r in range(world):
         want = torch.cat([torch.arange(osp[r][p], dtype=torch.float32) + 1000.0 * (p * world + r) for p in range(world)]).cuda()
-        assert torch.equal(outs[r], want), ("alltoall rounds", r)
+        if not torch.equal(outs[r], want):
+            bad = (outs[r] != want).nonzero().flatten()
+            raise AssertionError(("alltoall rounds", r, "mismatches", bad.numel(), "first", int(bad[0]), "last", int(bad[-1]),
+                                  "slot elements", slot // 4, "got", outs[r][bad[0]].item(), "want", want[bad[0]].item()))
     comm.barrier()
     torch.cuda.synchronize()
     assert comm.status() == 0

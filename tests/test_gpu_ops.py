@@ -284,3 +284,29 @@ def test_fused_mlp_matches_fp32_reference(with_residual):
     for g, w, name in zip(got, want, ["dx", "dw1", "db1", "dw2", "db2", "dres"]):
         assert _rel(g, w) < 2e-2, (name, _rel(g, w))
     assert _C().gemm_error_flag() == 0
+
+
+@pytest.mark.parametrize("B,S,H", [(2, 128, 2), (2, 256, 4), (16, 256, 8)])
+def test_causal_attention_forward_backward(B, S, H):
+    """The tcgen05 attention kernels (head dimension 64) against a plain fp32 PyTorch computation: softmax(q k^T / 8
+    + causal mask) v on the q, k, v slices of the fused projection's output, and the gradient of that whole tensor."""
+    from mccl_b200 import ops
+    torch.manual_seed(B * 1000 + S + H)
+    D = 64
+    qkv = (torch.randn(B, S, 3 * H * D, device="cuda") * 0.7).bfloat16().requires_grad_(True)
+    out = ops.causal_attention(qkv, H)
+    assert out.shape == (B, S, H * D)
+    d_out = (torch.randn(B, S, H * D, device="cuda") * 0.5).bfloat16()
+    out.backward(d_out)
+    ref_in = qkv.detach().float().requires_grad_(True)
+    q, k, v = (t.transpose(1, 2) for t in ref_in.view(B, S, 3, H, D).unbind(2))      # [B, H, S, D]
+    scores = (q @ k.transpose(-1, -2)) / (D ** 0.5)
+    mask = torch.ones(S, S, device="cuda", dtype=torch.bool).tril()
+    probs = scores.masked_fill(~mask, float("-inf")).softmax(-1)
+    ref = (probs @ v).transpose(1, 2).reshape(B, S, H * D)
+    ref.backward(d_out.float())
+    assert _rel(out, ref) < 2e-2, _rel(out, ref)
+    got, want = qkv.grad.view(B, S, 3, H, D), ref_in.grad.view(B, S, 3, H, D)
+    for t, name in enumerate(("dq", "dk", "dv")):
+        assert _rel(got[:, :, t], want[:, :, t]) < 2e-2, (name, _rel(got[:, :, t], want[:, :, t]))
+    assert _C().gemm_error_flag() == 0
