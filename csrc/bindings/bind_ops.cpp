@@ -59,10 +59,10 @@ void bind_ops(py::module_& m) {
   m.def("gemm_sm_count", &ops::gemm_sm_count);
 
   // ---- device timeline (kernels stamp %globaltimer; see csrc/core/timeline.hpp) ----
-  m.def("timeline_enable", [](int device, int capacity, int every) {
+  m.def("timeline_enable", [](int device, int capacity, int every, int detail) {
     c10::cuda::CUDAGuard g(at::Device(at::kCUDA, static_cast<c10::DeviceIndex>(device)));
-    timeline_enable(capacity, every);
-  }, py::arg("device"), py::arg("capacity") = 65536, py::arg("every") = 1);
+    timeline_enable(capacity, every, detail);
+  }, py::arg("device"), py::arg("capacity") = 65536, py::arg("every") = 1, py::arg("detail") = 0);
   m.def("timeline_disable", [](int device) {
     c10::cuda::CUDAGuard g(at::Device(at::kCUDA, static_cast<c10::DeviceIndex>(device)));
     timeline_disable();

@@ -25,7 +25,7 @@ int current_device() {
 }
 }  // namespace
 
-void timeline_enable(int capacity, int every) {
+void timeline_enable(int capacity, int every, int detail) {
   const int dev = current_device();
   capacity = std::max(capacity, 64);
   every = std::max(every, 1);
@@ -45,6 +45,7 @@ void timeline_enable(int capacity, int every) {
   head.cap = static_cast<uint32_t>(g_cap[dev]);
   head.count = 0;
   head.every = static_cast<uint32_t>(every);
+  head.detail = static_cast<uint32_t>(detail);
   MCCL_CUDA_CHECK(cudaMemcpy(g_buf[dev], &head, offsetof(TimelineBuf, rec), cudaMemcpyHostToDevice));
   g_on[dev] = true;
 }

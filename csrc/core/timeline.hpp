@@ -28,7 +28,7 @@ struct TimelineBuf {
   uint32_t cap;
   uint32_t count;          // records requested so far (may exceed cap; the excess is dropped)
   uint32_t every;          // a CTA records when blockIdx.x % every == 0
-  uint32_t reserved;
+  uint32_t detail;         // non-zero: kernels that have them also record their inner phases (TL_GEMM_PHASE)
   TimelineRec rec[1];      // cap entries follow
 };
 
@@ -37,11 +37,12 @@ enum TimelineKind : uint32_t {
   TL_ALLREDUCE = 2,
   TL_OTHER_COLL = 3,
   TL_OP = 4,
+  TL_GEMM_PHASE = 5,       // tag: phase << 24 | tile ordinal of the CTA; phases: 0 set-up, 1 wait for the accumulator, 2 epilogue
 };
 
 // Host side (timeline.cu).  All functions act on the current CUDA device.
 // Allocates (once) a buffer of `capacity` records; `every` selects which CTAs record.
-void timeline_enable(int capacity, int every);
+void timeline_enable(int capacity, int every, int detail = 0);
 void timeline_disable();
 // Device pointer kernels should receive, or nullptr while disabled.
 TimelineBuf* timeline_device_ptr();
@@ -69,6 +70,24 @@ __device__ __forceinline__ void tl_end(TimelineBuf* tl, unsigned long long t0, u
   TimelineRec r;
   r.t0 = t0;
   r.t1 = tl_now();
+  r.kind = kind;
+  r.tag = tag;
+  r.sm = sm;
+  r.cta = blockIdx.x;
+  tl->rec[i] = r;
+}
+// A record of an inner phase [t0, t1), written by one thread of a CTA that records.
+__device__ __forceinline__ bool tl_detail(const TimelineBuf* tl) {
+  return tl != nullptr && tl->detail != 0 && (blockIdx.x % tl->every) == 0;
+}
+__device__ __forceinline__ void tl_mark(TimelineBuf* tl, unsigned long long t0, unsigned long long t1, uint32_t kind, uint32_t tag) {
+  const uint32_t i = atomicAdd(&tl->count, 1u);
+  if (i >= tl->cap) return;
+  uint32_t sm;
+  asm volatile("mov.u32 %0, %%smid;" : "=r"(sm));
+  TimelineRec r;
+  r.t0 = t0;
+  r.t1 = t1;
   r.kind = kind;
   r.tag = tag;
   r.sm = sm;

@@ -6,7 +6,7 @@
 //
 //   warp 0      TMA producer (one thread): A / B k-blocks into a ring of stages
 //   warp 1      TMEM owner and tcgen05.mma issuer (one thread)
-//   warps 2-5   epilogue, one TMEM lane quarter each
+//   warps 2-9   epilogue: two warps per TMEM lane quarter, each finishing half of the tile's columns
 //
 // The same kernel carries the tensor-parallel fusions (see tp_gemm.cu):
 //   all-gather → GEMM   the A operand arrives in row chunks; the producer waits
@@ -37,7 +37,13 @@ struct PLayout {
   static constexpr int kReduceBarriers = 64;             // the reduce-scatter reducers' barriers and ring
   static constexpr int kSchedBytes = 4 * 8 * 2 + 4 * 4;  // tile scheduler: full / empty barriers and tile ring
   static constexpr int kBarriers = kGemmBarriers + kReduceBarriers + kSchedBytes;
-  static constexpr int kTotal = kTiles + kBarriers + 1024;
+  // behind the barriers: one 4 KB staging buffer per epilogue warp (output rows are transposed through it so that
+  // global stores cover whole 128-byte lines)
+  static constexpr int kStagingOff = kTiles + 512;
+  static constexpr int kStagingPerWarp = 4096;
+  static constexpr int kTotal = kStagingOff + 8 * kStagingPerWarp + 1024;
+  static_assert(kBarriers <= 512, "barriers overlap the epilogue staging");
+  static_assert(kTotal <= 227 * 1024, "shared memory of one CTA");
 };
 
 __device__ __forceinline__ unsigned long long now_ns() {
@@ -357,8 +363,11 @@ __global__ void bump_epoch_kernel(uint32_t* epoch, uint32_t* zeroed) {
   if (zeroed) *zeroed = 0;
 }
 
+constexpr int kEpiWarps = 8;
+constexpr int kGemmThreads = 32 * (2 + kEpiWarps);
+
 template <int BN, int STAGES, bool kAMn, bool kBMn>
-__global__ void __launch_bounds__(192, 1) gemm_persistent_kernel(const __grid_constant__ CUtensorMap tma_a,
+__global__ void __launch_bounds__(kGemmThreads, 1) gemm_persistent_kernel(const __grid_constant__ CUtensorMap tma_a,
                                                                  const __grid_constant__ CUtensorMap tma_b, GemmDev g,
                                                                  FusedDev f) {
   using L = PLayout<BN, STAGES>;
@@ -414,11 +423,11 @@ __global__ void __launch_bounds__(192, 1) gemm_persistent_kernel(const __grid_co
     }
     for (int b = 0; b < 2; ++b) {
       tc::mbar_init(&acc_full[b], 1);
-      tc::mbar_init(&acc_empty[b], 4);
+      tc::mbar_init(&acc_empty[b], kEpiWarps);
     }
     for (int b = 0; b < 4; ++b) {
       tc::mbar_init(&sched_full[b], 1);
-      tc::mbar_init(&sched_empty[b], 5);   // the MMA thread and the four epilogue warps
+      tc::mbar_init(&sched_empty[b], 1 + kEpiWarps);   // the MMA thread and the epilogue warps
     }
     *abort_flag = 0;
     tc::mbar_init_fence();
@@ -430,6 +439,7 @@ __global__ void __launch_bounds__(192, 1) gemm_persistent_kernel(const __grid_co
   __syncthreads();
   tc::fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  if (tl_t0 != 0ull && tl_detail(g.tl)) tl_mark(g.tl, tl_t0, tl_now(), TL_GEMM_PHASE, 0u);
   if (f.mode == FUSE_NONE) pdl_wait();   // set-up done: from here on operands are read and outputs written
 
   // Reduce-scatter fusion: phase-major order; inside a phase the chunks of the other ranks come first
@@ -554,7 +564,9 @@ __global__ void __launch_bounds__(192, 1) gemm_persistent_kernel(const __grid_co
     }
   } else {
     // ----------------------------------------------------------- epilogue --
-    const int quarter = warp & 3;
+    // a warp may read only the 32 tensor-memory lanes of its index modulo four; the two warps of a quarter split the columns
+    const int quarter = warp & 3, half = (warp - 2) >> 2;
+    constexpr int kHalfCols = BN / 2;
     bool ok = true;
     int i = 0;
     for (;; ++i) {
@@ -569,33 +581,36 @@ __global__ void __launch_bounds__(192, 1) gemm_persistent_kernel(const __grid_co
       int m_blk, n_blk, kb0;
       const int phase = tile_coords(t, m_blk, n_blk, kb0);
       const int buf = i & 1;
+      const bool stamp = warp == 2 && lane == 0 && tl_detail(g.tl);
+      const unsigned long long ts0 = stamp ? tl_now() : 0ull;
       ok = wait_or_abort(&acc_full[buf], (i >> 1) & 1, abort_flag, wait_ns);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc::fence_after_sync();
-      const int row = m_blk * BM + quarter * 32 + lane;
+      const unsigned long long ts1 = stamp ? tl_now() : 0ull;
       GemmDev gt = g;
       if (f.mode == FUSE_REDUCE_SCATTER_D) gt.d = f.rs_partial[epoch & 1u][f.rank];   // my partial product; the owners pull from it
-      const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(buf * BN) + (static_cast<uint32_t>(quarter * 32) << 16);
-#pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        uint32_t r[32];
-        tc::tmem_ld_32x32(tmem_d + static_cast<uint32_t>(c0), r);
-        tc::tmem_ld_wait();
-        if (c0 + 32 >= BN) {
-          // every column of this buffer is in registers: hand it back to the MMA warp
-          tc::fence_before_sync();
-          if (lane == 0) tc::mbar_arrive(&acc_empty[buf]);
-        }
-        const int col0 = n_blk * BN + c0;
-        if (row < g.m && col0 < g.n) epilogue_store(gt, row, col0, r);
+      const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(buf * BN + half * kHalfCols) + (static_cast<uint32_t>(quarter * 32) << 16);
+      const int col_base = n_blk * BN + half * kHalfCols;
+      uint8_t* stage = smem + L::kStagingOff + (warp - 2) * L::kStagingPerWarp;
+      const int row0 = m_blk * BM + quarter * 32;
+      auto last_read = [&]() {
+        // every column of this warp's part is in registers: hand the buffer back to the MMA warp
+        tc::fence_before_sync();
+        if (lane == 0) tc::mbar_arrive(&acc_empty[buf]);
+      };
+      if (gt.d_fp32) epilogue_fp32(gt, stage, tmem_d, row0, col_base, kHalfCols, lane, last_read);
+      else epilogue_bf16(gt, stage, tmem_d, row0, col_base, kHalfCols, lane, last_read);
+      if (stamp) {
+        tl_mark(g.tl, ts0, ts1, TL_GEMM_PHASE, (1u << 24) | static_cast<uint32_t>(i));
+        tl_mark(g.tl, ts1, tl_now(), TL_GEMM_PHASE, (2u << 24) | static_cast<uint32_t>(i));
       }
       if (f.mode == FUSE_REDUCE_SCATTER_D) {
-        // count this warp's quarter of the tile; the warp that completes a phase tells every rank
+        // count this warp's part of the tile; the warp that completes a phase tells every rank
         __syncwarp();
         if (lane == 0) {
           __threadfence();
-          const uint32_t target = static_cast<uint32_t>(per_phase) * 4u;
+          const uint32_t target = static_cast<uint32_t>(per_phase) * static_cast<uint32_t>(kEpiWarps);
           if (atomicAdd(f.phase_counters + phase, 1u) + 1u == target) {
             atomicExch(f.phase_counters + phase, 0u);
             __threadfence_system();
@@ -717,7 +732,7 @@ no_split:
   int gemm_ctas = ctas - f.copy_ctas;
   if (gemm_ctas < 1) return cudaErrorInvalidValue;
   if (tiles < gemm_ctas) gemm_ctas = tiles;
-  MCCL_LAUNCH_PDL((gemm_persistent_kernel<BN, STAGES, kAMn, kBMn>), gemm_ctas + f.copy_ctas, 192, L::kTotal, stream, ma, mb, g, f);
+  MCCL_LAUNCH_PDL((gemm_persistent_kernel<BN, STAGES, kAMn, kBMn>), gemm_ctas + f.copy_ctas, kGemmThreads, L::kTotal, stream, ma, mb, g, f);
   count_launch();
   return ::mccl::launch_status();
 }

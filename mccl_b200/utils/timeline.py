@@ -19,13 +19,14 @@ import numpy as np
 
 from .. import _C
 
-KIND_GEMM, KIND_ALLREDUCE, KIND_OTHER_COLL, KIND_OP = 1, 2, 3, 4
+KIND_GEMM, KIND_ALLREDUCE, KIND_OTHER_COLL, KIND_OP, KIND_GEMM_PHASE = 1, 2, 3, 4, 5
 _KIND_NAME = {KIND_GEMM: "gemm", KIND_ALLREDUCE: "allreduce", KIND_OTHER_COLL: "collective", KIND_OP: "op"}
 
 
-def enable(device: int, capacity: int = 1 << 17, every: int = 1) -> None:
-    """Starts recording on ``device``; CTAs whose index is a multiple of ``every`` record."""
-    _C.timeline_enable(device, capacity, every)
+def enable(device: int, capacity: int = 1 << 17, every: int = 1, detail: bool = False) -> None:
+    """Starts recording on ``device``; CTAs whose index is a multiple of ``every`` record.  With ``detail`` the GEMM
+    kernel also records its inner phases per tile (kind 5: set-up, wait for the accumulator, epilogue)."""
+    _C.timeline_enable(device, capacity, every, 1 if detail else 0)
 
 
 def disable(device: int) -> None:
