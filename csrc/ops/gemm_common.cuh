@@ -166,186 +166,104 @@ __device__ __forceinline__ void epilogue_store(const GemmDev& g, int row, int co
 }
 
 // ---- epilogue through shared memory ------------------------------------------------------------------------------------
-// Two measured facts shape this code.  (1) A thread owns one accumulator row (that is how tensor memory is read), so
-// storing straight from registers makes every warp-wide store touch 32 different 128-byte lines.  Each epilogue warp
-// therefore owns a 4 KB staging buffer of 32 rows x 128 bytes: a thread writes its row there, and the warp then moves
-// the buffer to global memory with several lanes per row, whole lines (or half lines) at a time; inputs that have the
-// layout of the output (gelu' multiplier, residual) come in the same way.  16-byte units are XOR-swizzled by the row
-// index so that both access patterns are free of bank conflicts.  (2) A CTA runs the epilogue of one or two tiles, so
-// straight-line code is executed once and every instruction is an instruction-cache miss: with the epilogue fully
-// unrolled, `no_instruction` was the top warp stall, and unrolling 32 columns per trip instead of 8 made the training
-// step 5 % slower.  The loops below are kept rolled (8 columns per trip) so that their instructions are fetched once.
+// Three measured facts shape this code.
+// (1) A thread owns one accumulator row (that is how tensor memory is read), so storing straight from registers makes
+//     every warp-wide store touch 32 different 128-byte lines.
+// (2) A CTA runs the epilogue of one or two tiles, so straight-line code is executed once and every instruction is an
+//     instruction-cache miss: with the epilogue fully unrolled, `no_instruction` was the top warp stall, and unrolling
+//     32 columns of epilogue math per trip instead of 8 made the training step 5 % slower.
+// (3) A tensor-memory read takes about 500 clocks before tcgen05.wait::ld returns: reading 8 columns per trip of a
+//     rolled loop cost 0.4 us per trip (3.4 us for a 128 x 128 tile) even with the next read in flight.
+// So: each epilogue warp reads 32 columns of its 32 rows at once (the next 32 are requested before these are used),
+// parks the raw fp32 values in a 4 KB staging buffer of its own (32 rows x 128 bytes, 16-byte units XOR-swizzled by
+// the row so that row-wise writes and unit-wise reads are both free of bank conflicts), and then finishes them in the
+// transposed assignment: lane = (row mod 4, 4 columns), 8 rolled trips over the rows.  There bias is a register, the
+// multiplier / residual loads and the output stores of 8 lanes cover 64 (bf16) or 128 (fp32) contiguous bytes of a
+// row, and the loop body is a few dozen instructions that are fetched once.
 __device__ __forceinline__ uint4* stage_unit(uint8_t* stage, int r, int u) {
   return reinterpret_cast<uint4*>(stage + r * 128 + ((u ^ (r & 7)) << 4));
 }
 
-// Staging <-> global for `upr` (8 or 4) 16-byte units per row, starting at unit `u0` of the staging rows; the global
-// side is rows [row0, row0 + 32) of a row-major matrix with `ldb` bytes per row, at byte offset `colb`.  `valid` units
-// of a row lie inside the matrix.
-__device__ __forceinline__ void stage_load(uint8_t* stage, const void* src, size_t ldb, size_t colb, int row0, int m, int upr, int valid, int lane) {
-  __syncwarp();
-  const int u = lane & (upr - 1), rsub = lane / upr, rows_per_trip = 32 / upr;
-#pragma unroll 1
-  for (int r = rsub; r < 32; r += rows_per_trip) {
-    uint4 v = make_uint4(0u, 0u, 0u, 0u);
-    if (row0 + r < m && u < valid)
-      v = *reinterpret_cast<const uint4*>(static_cast<const char*>(src) + static_cast<size_t>(row0 + r) * ldb + colb + u * 16);
-    *stage_unit(stage, r, u) = v;
-  }
-  __syncwarp();
-}
-
-__device__ __forceinline__ void stage_flush(uint8_t* stage, int u0, void* dst, size_t ldb, size_t colb, int row0, int m, int upr, int valid, int lane) {
-  __syncwarp();
-  const int u = lane & (upr - 1), rsub = lane / upr, rows_per_trip = 32 / upr;
-#pragma unroll 1
-  for (int r = rsub; r < 32; r += rows_per_trip) {
-    if (row0 + r < m && u < valid)
-      *reinterpret_cast<uint4*>(static_cast<char*>(dst) + static_cast<size_t>(row0 + r) * ldb + colb + u * 16) = *stage_unit(stage, r, u0 + u);
-  }
-  __syncwarp();
-}
-
-__device__ __forceinline__ uint4 pack8(const float (&v)[8]) {
-  uint4 pk;
-  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+__device__ __forceinline__ uint2 pack4(const float4& v) {
+  uint2 pk;
+  *reinterpret_cast<__nv_bfloat162*>(&pk.x) = __floats2bfloat162_rn(v.x, v.y);
+  *reinterpret_cast<__nv_bfloat162*>(&pk.y) = __floats2bfloat162_rn(v.z, v.w);
   return pk;
 }
-
-__device__ __forceinline__ void add_bias8(const GemmDev& g, int col, float (&v)[8]) {
-  if ((reinterpret_cast<uintptr_t>(g.bias) & 15) == 0) {
-    const float4 b0 = __ldg(reinterpret_cast<const float4*>(g.bias + col)), b1 = __ldg(reinterpret_cast<const float4*>(g.bias + col) + 1);
-    v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w;
-    v[4] += b1.x; v[5] += b1.y; v[6] += b1.z; v[7] += b1.w;
-  } else {
-#pragma unroll
-    for (int j = 0; j < 8; ++j) v[j] += __ldg(g.bias + col + j);
-  }
+__device__ __forceinline__ float4 unpack4(const uint2& pk) {
+  const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&pk.x));
+  const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&pk.y));
+  return make_float4(lo.x, lo.y, hi.x, hi.y);
 }
 
-__device__ __forceinline__ void apply8(const uint4& pk, bool multiply, float (&v)[8]) {
-  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&pk);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const float2 t = __bfloat1622float2(h[i]);
-    if (multiply) {
-      v[2 * i] *= t.x;
-      v[2 * i + 1] *= t.y;
-    } else {
-      v[2 * i] += t.x;
-      v[2 * i + 1] += t.y;
-    }
-  }
-}
-
-// Finishes `ncols` (a multiple of 64) accumulator columns of this warp's 32 rows, bf16 output.  `taddr` is the tensor-
-// memory address of the first column in this warp's lanes, `col0` its column in the matrix.  Calls last_read() right
-// after the last tensor-memory read, so that the accumulator can be handed back early.
+// Finishes `ncols` (a multiple of 32) accumulator columns of this warp's 32 rows [row0, row0 + 32).  `taddr` is the
+// tensor-memory address of the first column in this warp's lanes, `col0` its column in the matrix.  Calls last_read()
+// right after the last tensor-memory read has landed, so that the accumulator can be handed back early.
 template <typename F>
-__device__ __forceinline__ void epilogue_bf16(const GemmDev& g, uint8_t* stage, uint32_t taddr, int row0, int col0, int ncols, int lane, F&& last_read) {
+__device__ __forceinline__ void epilogue_tile(const GemmDev& g, uint8_t* stage, uint32_t taddr, int row0, int col0, int ncols, int lane, F&& last_read) {
   const bool has_bias = g.epilogue == EPI_BIAS || g.epilogue == EPI_BIAS_GELU || g.epilogue == EPI_BIAS_GELU_D;
   const bool gelu_d = g.epilogue == EPI_BIAS_GELU_D || g.epilogue == EPI_GELU_D;
   const bool gelu_z = g.epilogue == EPI_BIAS_GELU || g.epilogue == EPI_GELU;
-  const bool two_out = gelu_d || gelu_z;
-  // with a second output the staging row holds 32 columns of each (units 0-3: D, units 4-7: aux), otherwise 64 of D
-  const int upr = two_out ? 4 : 8, gcols = upr * 8;
-  const size_t ldb = static_cast<size_t>(g.ldd) * 2;
-  const __nv_bfloat16* staged_in = g.mul ? g.mul : g.residual;
-  const bool direct_residual = g.mul != nullptr && g.residual != nullptr;
-  const int row = row0 + lane;
-  const bool rows_ok = row0 < g.m;
-#pragma unroll 1
-  for (int c = 0; c < ncols; c += gcols) {
-    const int cg = col0 + c;
-    const int left = (g.n - cg) >> 3;
-    const int valid = left < upr ? (left < 0 ? 0 : left) : upr;
-    const bool active = rows_ok && valid > 0;
-    const size_t colb = static_cast<size_t>(cg) * 2;
-    if (active && staged_in) stage_load(stage, staged_in, ldb, colb, row0, g.m, upr, valid, lane);
-#pragma unroll 1
-    for (int u = 0; u < upr; ++u) {
-      uint32_t r[8];
-      tc::tmem_ld_32x8(taddr + static_cast<uint32_t>(c + u * 8), r);
-      tc::tmem_ld_wait();
-      if (c + gcols >= ncols && u + 1 == upr) last_read();
-      if (!active || u >= valid) continue;
-      float v[8];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[j]);
-      if (has_bias) add_bias8(g, cg + u * 8, v);
-      if (gelu_d) {
-        float dv[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) gelu_value_grad(v[j], v[j], dv[j]);
-        *stage_unit(stage, lane, 4 + u) = pack8(dv);
-      } else if (gelu_z) {
-        *stage_unit(stage, lane, 4 + u) = pack8(v);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) v[j] = gelu_erf(v[j]);
-      }
-      if (staged_in) apply8(*stage_unit(stage, lane, u), g.mul != nullptr, v);
-      if (direct_residual && row < g.m)
-        apply8(*reinterpret_cast<const uint4*>(g.residual + static_cast<size_t>(row) * g.ldd + cg + u * 8), false, v);
-      *stage_unit(stage, lane, u) = pack8(v);   // the unit this thread has just consumed, in its own row
-    }
-    if (active) {
-      stage_flush(stage, 0, g.d, ldb, colb, row0, g.m, upr, valid, lane);
-      if (two_out) stage_flush(stage, 4, g.aux, ldb, colb, row0, g.m, upr, valid, lane);
-    }
-  }
-}
-
-// The same for an fp32 output (`ncols` a multiple of 32): plain store, read-add-store, or red.global.add.
-template <typename F>
-__device__ __forceinline__ void epilogue_fp32(const GemmDev& g, uint8_t* stage, uint32_t taddr, int row0, int col0, int ncols, int lane, F&& last_read) {
-  const bool has_bias = g.epilogue == EPI_BIAS;
-  const int row = row0 + lane;
-  const bool rows_ok = row0 < g.m;
-  float* d = static_cast<float*>(g.d);
+  const int u = lane & 7, rsub = lane >> 3;   // transposed assignment: columns [4u, 4u + 4) of rows rsub, rsub + 4, ...
+  uint32_t acc[32];
+  tc::tmem_ld_32x32(taddr, acc);
 #pragma unroll 1
   for (int c = 0; c < ncols; c += 32) {
-    const int cg = col0 + c;
-    const int left = (g.n - cg) >> 2;                          // 16-byte units (4 floats) inside the matrix
-    const int valid = left < 8 ? (left < 0 ? 0 : left) : 8;
-    const bool active = rows_ok && valid > 0;
-#pragma unroll 1
-    for (int u = 0; u < 8; u += 2) {
-      uint32_t r[8];
-      tc::tmem_ld_32x8(taddr + static_cast<uint32_t>(c + u * 4), r);
-      tc::tmem_ld_wait();
-      if (c + 32 >= ncols && u == 6) last_read();
-      if (!active || u >= valid) continue;
-      float v[8];
+    tc::tmem_ld_wait();
+    __syncwarp();   // the previous group's reads of the staging buffer are done
 #pragma unroll
-      for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[j]);
-      if (has_bias) add_bias8(g, cg + u * 4, v);
-      if (g.residual && row < g.m) apply8(*reinterpret_cast<const uint4*>(g.residual + static_cast<size_t>(row) * g.ldd + cg + u * 4), false, v);
-      *reinterpret_cast<float4*>(stage_unit(stage, lane, u)) = make_float4(v[0], v[1], v[2], v[3]);
-      *reinterpret_cast<float4*>(stage_unit(stage, lane, u + 1)) = make_float4(v[4], v[5], v[6], v[7]);
-    }
+    for (int j = 0; j < 8; ++j) *stage_unit(stage, lane, j) = make_uint4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]);
+    if (c + 32 < ncols) tc::tmem_ld_32x32(taddr + static_cast<uint32_t>(c + 32), acc);
+    else last_read();
     __syncwarp();
-    if (active) {
-      const int u = lane & 7;
-#pragma unroll 1
-      for (int rr = lane >> 3; rr < 32; rr += 4) {
-        if (row0 + rr < g.m && u < valid) {
-          float4 o = *reinterpret_cast<const float4*>(stage_unit(stage, rr, u));
-          float4* p = reinterpret_cast<float4*>(d + static_cast<size_t>(row0 + rr) * g.ldd + cg + 4 * u);
-          if (g.atomic_add) {
-            atomicAdd(p, o);
-          } else {
-            if (g.accumulate) {
-              const float4 old = *p;
-              o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
-            }
-            *p = o;
+    const int col = col0 + c + 4 * u;
+    if (row0 >= g.m || col >= g.n) continue;   // N is a multiple of 8: a unit of 4 columns is inside or outside as a whole
+    float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (has_bias) {
+      if ((reinterpret_cast<uintptr_t>(g.bias) & 15) == 0) b = __ldg(reinterpret_cast<const float4*>(g.bias + col));
+      else b = make_float4(__ldg(g.bias + col), __ldg(g.bias + col + 1), __ldg(g.bias + col + 2), __ldg(g.bias + col + 3));
+    }
+#pragma unroll 2
+    for (int r = rsub; r < 32; r += 4) {
+      const int row = row0 + r;
+      if (row >= g.m) break;
+      float4 v = *reinterpret_cast<const float4*>(stage_unit(stage, r, u));
+      const size_t at = static_cast<size_t>(row) * g.ldd + col;
+      v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
+      if (gelu_d) {
+        float4 d;
+        gelu_value_grad(v.x, v.x, d.x);
+        gelu_value_grad(v.y, v.y, d.y);
+        gelu_value_grad(v.z, v.z, d.z);
+        gelu_value_grad(v.w, v.w, d.w);
+        *reinterpret_cast<uint2*>(g.aux + at) = pack4(d);
+      } else if (gelu_z) {
+        *reinterpret_cast<uint2*>(g.aux + at) = pack4(v);
+        v.x = gelu_erf(v.x); v.y = gelu_erf(v.y); v.z = gelu_erf(v.z); v.w = gelu_erf(v.w);
+      }
+      if (g.mul) {
+        const float4 t = unpack4(*reinterpret_cast<const uint2*>(g.mul + at));
+        v.x *= t.x; v.y *= t.y; v.z *= t.z; v.w *= t.w;
+      }
+      if (g.residual) {
+        const float4 t = unpack4(*reinterpret_cast<const uint2*>(g.residual + at));
+        v.x += t.x; v.y += t.y; v.z += t.z; v.w += t.w;
+      }
+      if (g.d_fp32) {
+        float4* p = reinterpret_cast<float4*>(static_cast<float*>(g.d) + at);
+        if (g.atomic_add) {
+          atomicAdd(p, v);
+        } else {
+          if (g.accumulate) {
+            const float4 old = *p;
+            v.x += old.x; v.y += old.y; v.z += old.z; v.w += old.w;
           }
+          *p = v;
         }
+      } else {
+        *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(g.d) + at) = pack4(v);
       }
     }
-    __syncwarp();
   }
 }
 
@@ -367,6 +285,25 @@ inline bool encode_map(CUtensorMap* map, const void* base, int rows, int cols, i
   return rc == CUDA_SUCCESS;
 }
 
+// Output matrix [rows, cols] (bf16, or fp32 when `fp32`) as the target of TMA stores of 32-row boxes whose rows are
+// 128 bytes (64 bf16 or 32 fp32 columns), 128-byte swizzle: the layout of an epilogue warp's staging buffer.
+inline bool encode_out_map(CUtensorMap* map, const void* base, int rows, int cols, int ld_elems, bool fp32) {
+  const CuDriver& cu = CuDriver::get();
+  if (!cu.loaded || !cu.TensorMapEncodeTiled) return false;
+  int device = 0;
+  cudaGetDevice(&device);
+  cu.ensure_context(device);
+  const int es = fp32 ? 4 : 2;
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld_elems) * es};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(128 / es), 32u};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult rc = cu.TensorMapEncodeTiled(map, fp32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                                        const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return rc == CUDA_SUCCESS;
+}
 
 }  // namespace ops
 }  // namespace mccl

@@ -599,8 +599,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_persistent_kernel(const 
         tc::fence_before_sync();
         if (lane == 0) tc::mbar_arrive(&acc_empty[buf]);
       };
-      if (gt.d_fp32) epilogue_fp32(gt, stage, tmem_d, row0, col_base, kHalfCols, lane, last_read);
-      else epilogue_bf16(gt, stage, tmem_d, row0, col_base, kHalfCols, lane, last_read);
+      epilogue_tile(gt, stage, tmem_d, row0, col_base, kHalfCols, lane, last_read);
       if (stamp) {
         tl_mark(g.tl, ts0, ts1, TL_GEMM_PHASE, (1u << 24) | static_cast<uint32_t>(i));
         tl_mark(g.tl, ts1, tl_now(), TL_GEMM_PHASE, (2u << 24) | static_cast<uint32_t>(i));
@@ -739,6 +738,7 @@ no_split:
 
 }  // namespace
 
+int gemm_choose_splits(int tiles, int num_kb, int workers) { return choose_splits(tiles, num_kb, workers); }
 void set_gemm_cta_limit(int ctas) { g_gemm_cta_limit.store(ctas > 0 ? ctas : 0, std::memory_order_relaxed); }
 int gemm_cta_limit() { return g_gemm_cta_limit.load(std::memory_order_relaxed); }
 int gemm_sm_count() { return sm_count(); }

@@ -59,6 +59,8 @@ constexpr int kFuseSigWords = kFuseSigAg + 8 * kFuseCopyCtas;
 
 // max_ctas <= 0: one CTA per SM.
 cudaError_t launch_gemm_persistent(const GemmArgs& a, const FusedDev& f, int max_ctas, cudaStream_t stream);
+// The same product on CTA pairs (tcgen05.mma.cta_group::2; gemm_pair.cu): no fused roles, fewer operand bytes per SM.
+cudaError_t launch_gemm_pair(const GemmArgs& a, cudaStream_t stream);
 // ++*epoch and *zeroed = 0 (zeroed may be null), one thread; enqueue before a fused launch.
 cudaError_t launch_bump_epoch(uint32_t* epoch, uint32_t* zeroed, cudaStream_t stream);
 

@@ -202,6 +202,10 @@ cudaError_t launch_cfg(const GemmArgs& a, cudaStream_t stream) {
 
 }  // namespace
 
+#ifndef MCCL_GEMM_DEFAULT_KERNEL
+#define MCCL_GEMM_DEFAULT_KERNEL 1
+#endif
+
 const char* gemm_last_reason() { return t_reason; }
 
 cudaError_t gemm_bf16_tn(const GemmArgs& a, cudaStream_t stream) {
@@ -221,14 +225,15 @@ cudaError_t gemm_bf16_tn(const GemmArgs& a, cudaStream_t stream) {
   if (a.residual && (reinterpret_cast<uintptr_t>(a.residual) & 15u)) return unsupported("residual pointer must be 16-byte aligned");
   if (a.mul && ((reinterpret_cast<uintptr_t>(a.mul) & 15u) || a.d_fp32)) return unsupported("mul must be 16-byte aligned and the output bf16");
   if (a.a_mn_major && a.m % 8 != 0) return unsupported("an MN-major A needs M to be a multiple of 8");
-  // Default: persistent kernel (one CTA per SM, double-buffered accumulator).
-  // MCCL_GEMM_KERNEL=tile selects the one-tile-per-CTA kernel below.
-  static const bool tile_kernel = [] {
+  // MCCL_GEMM_KERNEL: "pair" = CTA pairs (tcgen05.mma.cta_group::2), "persistent" = one CTA per SM,
+  // "tile" = the one-tile-per-CTA kernel below.
+  static const int kernel_choice = [] {
     const char* v = std::getenv("MCCL_GEMM_KERNEL");
-    return v && std::string(v) == "tile";
+    const std::string s = v ? v : "";
+    return s == "tile" ? 2 : (s == "pair" ? 1 : (s == "persistent" ? 0 : MCCL_GEMM_DEFAULT_KERNEL));
   }();
-  if (!tile_kernel) {
-    cudaError_t rc = launch_gemm_persistent(a, FusedDev{}, 0, stream);
+  if (kernel_choice != 2) {
+    cudaError_t rc = kernel_choice == 1 ? launch_gemm_pair(a, stream) : launch_gemm_persistent(a, FusedDev{}, 0, stream);
     if (rc == cudaErrorNotSupported) return unsupported("cuTensorMapEncodeTiled rejected an operand");
     return rc;
   }
