@@ -152,7 +152,13 @@ void bind_comm(py::module_& m) {
                                                       static_cast<int64_t>(a->bytes),
                               "view exceeds the symmetric allocation");
             auto opts = at::TensorOptions().dtype(dtype).device(at::Device(at::kCUDA, static_cast<c10::DeviceIndex>(device)));
-            return at::from_blob(static_cast<char*>(a->ptrs[r]) + byte_offset, shape, [a](void*) {}, opts);
+            // target_device: a peer's block is physically on another GPU, which the pointer query behind from_blob
+            // would report; the mapping is addressable from `device`, and that is where kernels on it run
+            return at::for_blob(static_cast<char*>(a->ptrs[r]) + byte_offset, shape)
+                .deleter([a](void*) {})
+                .options(opts)
+                .target_device(opts.device())
+                .make_tensor();
           },
           py::arg("rank"), py::arg("byte_offset"), py::arg("shape"), py::arg("dtype"), py::arg("device"),
           "View of rank `rank`'s block (as mapped in this process) as a tensor; the view keeps the allocation alive.  For "

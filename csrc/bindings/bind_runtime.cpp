@@ -406,7 +406,9 @@ void bind_runtime(py::module_& m) {
       "pass the same name (node 0 creates the shared directory).");
   m.def(
       "init_dmem_symm",
-      [](c10::intrusive_ptr<ProcessGroupMCCL> pg, int device_index) {
+      [](ProcessGroupMCCL& pg_ref, int device_index) {
+        // the Python object owns the group; share that ownership for as long as dmem is initialised
+        c10::intrusive_ptr<ProcessGroupMCCL> pg = c10::intrusive_ptr<ProcessGroupMCCL>::reclaim_copy(&pg_ref);
         GlobalDmem& g = gd();
         MCCL_CHECK(g.nodes.empty(), "dmem is already initialised");
         MCCL_CHECK(pg->getSize() <= kDmemMaxNodes, "init_dmem_symm: group too large");
@@ -425,12 +427,16 @@ void bind_runtime(py::module_& m) {
       "alloc_symm_heap",
       [](uint64_t nbytes) {
         MCCL_CHECK(gd().symm != nullptr, "alloc_symm_heap needs init_dmem_symm(process_group, device)");
-        auto a = gd().comm->symm_alloc(nbytes);
+        std::shared_ptr<SymmAlloc> a;
+        {
+          py::gil_scoped_release nogil;   // collective: may wait for the peers
+          a = gd().comm->symm_alloc(nbytes);
+        }
         const uint32_t heap_id = a->id + 1;   // 0 means "not in a heap"
         gd().symm->add_heap(heap_id, a);
         return py::make_tuple(heap_id, a);
       },
-      py::arg("nbytes"), py::call_guard<py::gil_scoped_release>(),
+      py::arg("nbytes"),
       "Collective.  Returns (heap id, SymmAlloc): device memory of `nbytes` on every rank, each block mapped in every process.");
   m.def("shutdown_dmem", [] {
     gd().nodes.clear();

@@ -41,6 +41,12 @@ def free_port() -> int:
 
 def _worker(rank: int, world: int, port: int, fn: Callable, kwargs: Dict[str, Any], env: Dict[str, str], queue) -> None:
     try:
+        # a rank that is still running shortly before the harness gives up prints where it is (shown with the failure)
+        dump_after = kwargs.pop("_dump_after", 0.0)
+        if dump_after > 0:
+            import faulthandler
+            faulthandler.enable()
+            faulthandler.dump_traceback_later(dump_after, exit=False)
         os.environ.update(env)
         os.environ["MASTER_ADDR"] = "127.0.0.1"
         os.environ["MASTER_PORT"] = str(port)
@@ -76,6 +82,7 @@ def spawn(fn: Callable, world: int = WORLD, timeout: float = 120.0, env: Dict[st
     ctx = mp.get_context("spawn")
     queue = ctx.Queue()
     port = free_port()
+    kwargs.setdefault("_dump_after", max(5.0, timeout - 10.0))
     procs = [ctx.Process(target=_worker, args=(r, world, port, fn, dict(kwargs), env or {}, queue), daemon=True)
              for r in range(world)]
     for p in procs:
@@ -91,6 +98,11 @@ def spawn(fn: Callable, world: int = WORLD, timeout: float = 120.0, env: Dict[st
         except pyqueue.Empty:
             if errors and all(not p.is_alive() for p in procs):
                 break
+            # a rank that died without a word (a signal, os._exit) is a failure now, not a timeout later
+            dead = [(r, p.exitcode) for r, p in enumerate(procs) if not p.is_alive() and p.exitcode not in (0, None) and r not in results]
+            if dead and not errors:
+                errors.extend(f"[rank {r}] process died with exit code {code}" for r, code in dead)
+                deadline = min(deadline, time.time() + 10)
             continue
         if status == "ok":
             results[rank] = payload

@@ -97,7 +97,7 @@ def _dmem_put_get(rank, world):
 
 
 def test_dmem_put_get_imm_atomics_between_gpus():
-    assert all(spawn(_dmem_put_get, _world(), timeout=180, _cuda=True, env=_ENV))
+    assert all(spawn(_dmem_put_get, _world(), timeout=90, _cuda=True, env=_ENV))
 
 
 def _coherence_pingpong(rank, world):
