@@ -33,6 +33,38 @@ def _notify(p: torch.Tensor) -> None:
         cb()
 
 
+# Weight-gradient GEMMs have no consumer until the gradient is reduced or applied, so a trainer can give them a
+# stream of their own: they then run beside the input-gradient chain and fill the SMs its small kernels leave idle.
+_wgrad = {"stream": None, "pending": False}
+
+
+def set_wgrad_stream(stream) -> None:
+    """Side stream for weight-gradient GEMMs that write into a trainer's gradient buffer (None: current stream)."""
+    _wgrad["stream"] = stream
+    _wgrad["pending"] = False
+
+
+def join_wgrad(stream=None) -> None:
+    """Makes ``stream`` (default: the current one) wait for the weight gradients queued on the side stream."""
+    s = _wgrad["stream"]
+    if s is not None and _wgrad["pending"]:
+        (stream if stream is not None else torch.cuda.current_stream()).wait_stream(s)
+
+
+def _wgrad_gemm(a_mat: torch.Tensor, b_mat: torch.Tensor, sink: torch.Tensor) -> None:
+    """sink += a_mat^T . b_mat (both [tokens, features]) on the weight-gradient stream."""
+    s = _wgrad["stream"]
+    if s is None:
+        _C.gemm_bf16(a_mat, b_mat, None, "none", True, sink, True, True, True)
+        return
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        _C.gemm_bf16(a_mat, b_mat, None, "none", True, sink, True, True, True)
+    a_mat.record_stream(s)
+    b_mat.record_stream(s)
+    _wgrad["pending"] = True
+
+
 def _gemm_ok(m: int, n: int, k: int) -> bool:
     return k % 64 == 0 and n % 8 == 0 and m > 0
 
@@ -90,7 +122,7 @@ class LinearFn(torch.autograd.Function):
             if _gemm_ok(N, K, M) and N % 8 == 0:
                 # dW[N,K] = dz^T · x: both operands stored [tokens, features], read MN-major
                 if sink is not None:
-                    _C.gemm_bf16(dz, x2, None, "none", True, sink, True, True, True)
+                    _wgrad_gemm(dz, x2, sink)
                     _notify(weight)
                 else:
                     dw, _ = _C.gemm_bf16(dz, x2, None, "none", True, None, False, True, True)
@@ -149,7 +181,7 @@ class MlpGeluFn(torch.autograd.Function):
         for name, (w, a_mat, b_mat) in (("w2", (w2, dy2, h)), ("w1", (w1, dz, x2))):
             sink = _sink(w)
             if sink is not None:
-                _C.gemm_bf16(a_mat, b_mat, None, "none", True, sink, True, True, True)
+                _wgrad_gemm(a_mat, b_mat, sink)
                 _notify(w)
                 grads[name] = None
             else:
@@ -288,7 +320,7 @@ class LinearCrossEntropyFn(torch.autograd.Function):
             sink = _sink(weight)
             if _gemm_ok(V, D, T) and V % 8 == 0:
                 if sink is not None:
-                    _C.gemm_bf16(dlogits, h, None, "none", True, sink, True, True, True)
+                    _wgrad_gemm(dlogits, h, sink)
                     _notify(weight)
                 else:
                     dw, _ = _C.gemm_bf16(dlogits, h, None, "none", True, None, False, True, True)

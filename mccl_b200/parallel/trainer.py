@@ -34,6 +34,7 @@ import torch
 import torch.distributed as dist
 
 from .. import _C, ops
+from ..ops import native as _native
 
 
 class _Bucket:
@@ -88,6 +89,10 @@ class DDPTrainer:
         # Hooks are needed whenever something happens per bucket.
         self._per_bucket = self.world > 1
         self._body_done = None   # event on the side stream: every non-tail bucket has been reduced
+        # weight-gradient GEMMs on a stream of their own, beside the input-gradient chain (MCCL_SIDE_WGRAD=0: in line)
+        self.wgrad_stream = None
+        if device.type == "cuda" and os.environ.get("MCCL_SIDE_WGRAD", "1") != "0":
+            self.wgrad_stream = torch.cuda.Stream(device=device)
         self._flatten(bucket_mb, last_bucket_mb)
         self.step_t = torch.zeros((), device=device, dtype=torch.float32)
         self.m = torch.zeros_like(self.flat_p)
@@ -230,6 +235,7 @@ class DDPTrainer:
         stream = self.comm_stream if (self.overlap and self.comm_stream is not None) else main
         if stream is not main:
             stream.wait_stream(main)
+        _native.join_wgrad(stream)   # the bucket's weight gradients may still be running on their own stream
         shaped = self.comm is not None and (self.comm_sms > 0 or self.comm_threads > 0) and self._in_backward and not b.tail
         if shaped:
             saved = (self.comm.max_ctas, self.comm.launch_threads)
@@ -263,9 +269,13 @@ class DDPTrainer:
         if self.comm_sms > 0:
             _C.set_gemm_cta_limit(max(_C.gemm_sm_count() - self.comm_sms, 1))
         self._in_backward = True
+        _native.set_wgrad_stream(self.wgrad_stream)
         try:
             loss.backward()
+            if self.wgrad_stream is not None:
+                _native.join_wgrad(torch.cuda.current_stream(self.device))
         finally:
+            _native.set_wgrad_stream(None)
             self._in_backward = False
             if self.comm_sms > 0:
                 _C.set_gemm_cta_limit(0)
