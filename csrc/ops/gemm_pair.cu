@@ -151,11 +151,13 @@ __device__ __forceinline__ uint4 pack8(const float (&v)[8]) {
 }
 
 // `ncols` (a multiple of 64) accumulator columns of this warp's 32 rows; the thread's row is row0 + lane.
-template <typename F>
-__device__ __forceinline__ void epilogue_tma(const GemmDev& g, const CUtensorMap* map_d, uint8_t* stage, uint32_t taddr, int row0, int col0,
-                                             int ncols, int lane, F&& last_read) {
+template <bool kGelu, typename F>
+__device__ __forceinline__ void epilogue_tma(const GemmDev& g, const CUtensorMap* map_d, const CUtensorMap* map_aux, uint8_t* stage, uint32_t taddr,
+                                             int row0, int col0, int ncols, int lane, F&& last_read) {
   const int row = row0 + lane;
-  const bool has_bias = g.epilogue == EPI_BIAS;
+  const bool has_bias = g.epilogue == EPI_BIAS || g.epilogue == EPI_BIAS_GELU || g.epilogue == EPI_BIAS_GELU_D;
+  const bool gelu_d = kGelu && (g.epilogue == EPI_BIAS_GELU_D || g.epilogue == EPI_GELU_D);
+  const bool gelu_z = kGelu && (g.epilogue == EPI_BIAS_GELU || g.epilogue == EPI_GELU);
   const bool bias_vec = (reinterpret_cast<uintptr_t>(g.bias) & 15) == 0;
   if (g.d_fp32) {
     const bool add = g.atomic_add || g.accumulate;
@@ -195,7 +197,7 @@ __device__ __forceinline__ void epilogue_tma(const GemmDev& g, const CUtensorMap
     if (c + 64 >= ncols) last_read();
     const int cg = col0 + c;
     if (row0 >= g.m || cg >= g.n) continue;   // uniform over the warp
-    uint4 out[8];
+    uint4 out[8], aux_out[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       float v[8];
@@ -212,6 +214,17 @@ __device__ __forceinline__ void epilogue_tma(const GemmDev& g, const CUtensorMap
 #pragma unroll
           for (int e = 0; e < 8; ++e) v[e] += __ldg(g.bias + col + e);
         }
+      }
+      if (kGelu && gelu_d) {
+        // value and derivative share one exponential; the derivative is what backward needs, so it is saved instead of z
+        float dv[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) gelu_value_grad(v[e], v[e], dv[e]);
+        aux_out[j] = pack8(dv);
+      } else if (kGelu && gelu_z) {
+        aux_out[j] = pack8(v);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] = gelu_erf(v[e]);
       }
       if (g.mul && inside && row < g.m) {
         const uint4 pk = *reinterpret_cast<const uint4*>(g.mul + static_cast<size_t>(row) * g.ldd + col);
@@ -245,13 +258,27 @@ __device__ __forceinline__ void epilogue_tma(const GemmDev& g, const CUtensorMap
       tma_store_2d(map_d, stage, cg, row0);
       bulk_commit();
     }
+    if (kGelu && (gelu_d || gelu_z)) {
+      if (lane == 0) bulk_wait_read();
+      __syncwarp();
+#pragma unroll
+      for (int j = 0; j < 8; ++j) *stage_unit(stage, lane, j) = aux_out[j];
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        tma_store_2d(map_aux, stage, cg, row0);
+        bulk_commit();
+      }
+    }
   }
 }
 
-template <int BN, int STAGES, bool kAMn, bool kBMn>
+// kGelu: the instantiation for GELU epilogues (two outputs, 25 instructions of arithmetic per value).  It is a kernel of
+// its own so that every other product runs without that code in its instruction stream.
+template <int BN, int STAGES, bool kAMn, bool kBMn, bool kGelu>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-                 const __grid_constant__ CUtensorMap tma_d, GemmDev g, int k_splits) {
+                 const __grid_constant__ CUtensorMap tma_d, const __grid_constant__ CUtensorMap tma_aux, GemmDev g, int k_splits) {
   using L = PairLayout<BN, STAGES>;
   constexpr int BNH = BN / 2;
   extern __shared__ uint8_t smem_raw[];
@@ -288,6 +315,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     tc::tma_prefetch_desc(&tma_a);
     tc::tma_prefetch_desc(&tma_b);
     tc::tma_prefetch_desc(&tma_d);
+    if (g.aux) tc::tma_prefetch_desc(&tma_aux);
   }
   if (warp == 1) tmem_alloc_pair(tmem_slot, 2 * BN);
   tc::fence_before_sync();
@@ -383,7 +411,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     const int quarter = warp & 3, half = (warp - 2) >> 2;
     constexpr int kHalfCols = BN / 2;
     uint8_t* stage = smem + L::kStagingOff + (warp - 2) * L::kStagingPerWarp;
-    const bool gelu = g.epilogue == EPI_BIAS_GELU || g.epilogue == EPI_GELU || g.epilogue == EPI_BIAS_GELU_D || g.epilogue == EPI_GELU_D;
     bool ok = true;
     int i = 0;
     for (int w = pair; w < total; w += pairs, ++i) {
@@ -406,15 +433,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         tc::fence_before_sync();
         if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
       };
-      // GELU epilogues have a second output and much arithmetic per value: they keep the transposed, rolled path
-      if (gelu) epilogue_tile(g, stage, tmem_d, row0, col_base, kHalfCols, lane, last_read);
-      else epilogue_tma(g, &tma_d, stage, tmem_d, row0, col_base, kHalfCols, lane, last_read);
+      epilogue_tma<kGelu>(g, &tma_d, &tma_aux, stage, tmem_d, row0, col_base, kHalfCols, lane, last_read);
       if (stamp) {
         tl_mark(g.tl, ts0, ts1, TL_GEMM_PHASE, (1u << 24) | static_cast<uint32_t>(i));
         tl_mark(g.tl, ts1, tl_now(), TL_GEMM_PHASE, (2u << 24) | static_cast<uint32_t>(i));
       }
     }
-    if (lane == 0) bulk_wait_all();   // this lane's stores have been written before the CTA retires
+    if (lane == 0) bulk_wait_read();   // the stores have read this warp's staging buffer; kernel completion publishes them
     if (!ok && lane == 0) {
       *abort_flag = 1;
       atomicExch(g.err, 13);
@@ -437,7 +462,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
 }
 
 // Clusters of two that can be resident at once (GPCs with an odd number of free SMs leave one SM out).
-template <int BN, int STAGES, bool kAMn, bool kBMn>
+template <int BN, int STAGES, bool kAMn, bool kBMn, bool kGelu>
 int max_pairs() {
   using L = PairLayout<BN, STAGES>;
   static int cached = 0;
@@ -448,7 +473,7 @@ int max_pairs() {
   cfg.dynamicSmemBytes = L::kTotal;
   cfg.numAttrs = 0;   // the cluster shape is part of the kernel (__cluster_dims__)
   int n = 0;
-  if (cudaOccupancyMaxActiveClusters(&n, gemm_pair_kernel<BN, STAGES, kAMn, kBMn>, &cfg) != cudaSuccess || n <= 0) {
+  if (cudaOccupancyMaxActiveClusters(&n, gemm_pair_kernel<BN, STAGES, kAMn, kBMn, kGelu>, &cfg) != cudaSuccess || n <= 0) {
     (void)cudaGetLastError();
     n = gemm_sm_count() / 2 - 2;
   }
@@ -456,20 +481,25 @@ int max_pairs() {
   return n;
 }
 
-template <int BN, int STAGES, bool kAMn, bool kBMn>
+template <int BN, int STAGES, bool kAMn, bool kBMn, bool kGelu = false>
 cudaError_t launch_pair_cfg(const GemmArgs& a, cudaStream_t stream) {
   using L = PairLayout<BN, STAGES>;
   static bool configured = false;
   if (!configured) {
-    cudaError_t rc = cudaFuncSetAttribute(gemm_pair_kernel<BN, STAGES, kAMn, kBMn>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal);
+    cudaError_t rc = cudaFuncSetAttribute(gemm_pair_kernel<BN, STAGES, kAMn, kBMn, kGelu>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal);
     if (rc != cudaSuccess) return rc;
     configured = true;
   }
   CUtensorMap ma, mb;
   const bool oka = kAMn ? encode_map(&ma, a.a, a.k, a.m, a.lda, BK) : encode_map(&ma, a.a, a.m, a.k, a.lda, BM);
   const bool okb = kBMn ? encode_map(&mb, a.b, a.k, a.n, a.ldb, BK) : encode_map(&mb, a.b, a.n, a.k, a.ldb, BN / 2);
-  CUtensorMap md;
+  CUtensorMap md, maux;
   if (!oka || !okb || !encode_out_map(&md, a.d, a.m, a.n, a.ldd, a.d_fp32)) return cudaErrorNotSupported;
+  if (a.aux) {
+    if (!encode_out_map(&maux, a.aux, a.m, a.n, a.ldd, false)) return cudaErrorNotSupported;
+  } else {
+    maux = md;   // never used
+  }
   (void)cudaGetLastError();
   GemmDev g;
   g.d = a.d;
@@ -488,7 +518,7 @@ cudaError_t launch_pair_cfg(const GemmArgs& a, cudaStream_t stream) {
   g.err = gemm_error_device_ptr();
   if (!g.err) return cudaErrorNotSupported;
   g.tl = timeline_device_ptr();
-  int pairs = max_pairs<BN, STAGES, kAMn, kBMn>();
+  int pairs = max_pairs<BN, STAGES, kAMn, kBMn, kGelu>();
   const int limit = gemm_cta_limit();
   if (limit > 0 && limit / 2 < pairs) pairs = limit / 2;
   if (pairs < 1) return cudaErrorInvalidValue;
@@ -509,7 +539,7 @@ cudaError_t launch_pair_cfg(const GemmArgs& a, cudaStream_t stream) {
     }
   }
   if (tiles < pairs) pairs = tiles;
-  MCCL_LAUNCH((gemm_pair_kernel<BN, STAGES, kAMn, kBMn>), 2 * pairs, kPairThreads, L::kTotal, stream, ma, mb, md, g, splits);
+  MCCL_LAUNCH((gemm_pair_kernel<BN, STAGES, kAMn, kBMn, kGelu>), 2 * pairs, kPairThreads, L::kTotal, stream, ma, mb, md, maux, g, splits);
   count_launch();
   return ::mccl::launch_status();
 }
@@ -517,14 +547,34 @@ cudaError_t launch_pair_cfg(const GemmArgs& a, cudaStream_t stream) {
 }  // namespace
 
 cudaError_t launch_gemm_pair(const GemmArgs& a, cudaStream_t stream) {
-  const int pairs = gemm_sm_count() / 2;
-  const long long tiles256 = static_cast<long long>((a.m + 2 * BM - 1) / (2 * BM)) * ((a.n + 255) / 256);
-  const bool wide = a.n % 256 == 0 && tiles256 >= pairs;
+  // Tile width by a small cost model (microseconds, fitted to device timelines of this kernel): a k-block of a
+  // 256 x 256 pair tile takes 0.45 us and one of a 256 x 128 tile 0.33 us, so the wide tile does twice the work for
+  // 1.4 times the time whenever it leaves no SM idle; its epilogue is about twice as long.  Split-K (fp32 outputs
+  // only) multiplies the work items, which is what lets small weight-gradient products use wide tiles at all.
+  int pairs = gemm_sm_count() / 2;
+  const int limit = gemm_cta_limit();
+  if (limit > 0 && limit / 2 < pairs) pairs = limit / 2;
+  if (pairs < 1) pairs = 1;
+  const int kb = a.k / BK;
+  const bool splittable = a.d_fp32 && a.epilogue == EPI_NONE && !a.residual && !a.mul && (a.accumulate || a.ldd == a.n);
+  auto estimate = [&](int bn) {
+    const int tiles = ((a.m + 2 * BM - 1) / (2 * BM)) * ((a.n + bn - 1) / bn);
+    const int s = splittable ? gemm_choose_splits(tiles, kb, pairs) : 1;
+    const int rounds = (tiles * s + pairs - 1) / pairs;
+    const double t_kb = bn == 256 ? 0.45 : 0.33, t_epi = bn == 256 ? 3.0 : 1.8;
+    return rounds * ((kb / s) * t_kb + t_epi + (s > 1 ? 1.0 : 0.0));
+  };
+  const bool wide = a.n > 128 && estimate(256) < estimate(128);
 #define MCCL_PAIR(BN, ST)                                                                               \
   (a.a_mn_major ? (a.b_mn_major ? launch_pair_cfg<BN, ST, true, true>(a, stream)                        \
                                 : launch_pair_cfg<BN, ST, true, false>(a, stream))                      \
                 : (a.b_mn_major ? launch_pair_cfg<BN, ST, false, true>(a, stream)                       \
                                 : launch_pair_cfg<BN, ST, false, false>(a, stream)))
+  const bool gelu = a.epilogue == EPI_BIAS_GELU || a.epilogue == EPI_GELU || a.epilogue == EPI_BIAS_GELU_D || a.epilogue == EPI_GELU_D;
+  if (gelu) {
+    if (a.a_mn_major || a.b_mn_major) return cudaErrorNotSupported;   // activations are applied in forward products only
+    return wide ? launch_pair_cfg<256, 6, false, false, true>(a, stream) : launch_pair_cfg<128, 8, false, false, true>(a, stream);
+  }
   return wide ? MCCL_PAIR(256, 6) : MCCL_PAIR(128, 8);
 #undef MCCL_PAIR
 }

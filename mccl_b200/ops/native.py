@@ -36,6 +36,7 @@ def _notify(p: torch.Tensor) -> None:
 # Weight-gradient GEMMs have no consumer until the gradient is reduced or applied, so a trainer can give them a
 # stream of their own: they then run beside the input-gradient chain and fill the SMs its small kernels leave idle.
 _wgrad = {"stream": None, "pending": False}
+_SIDE_COLSUM = __import__("os").environ.get("MCCL_SIDE_COLSUM", "1") != "0"
 
 
 def set_wgrad_stream(stream) -> None:
@@ -62,6 +63,19 @@ def _wgrad_gemm(a_mat: torch.Tensor, b_mat: torch.Tensor, sink: torch.Tensor) ->
         _C.gemm_bf16(a_mat, b_mat, None, "none", True, sink, True, True, True)
     a_mat.record_stream(s)
     b_mat.record_stream(s)
+    _wgrad["pending"] = True
+
+
+def _wgrad_colsum(src: torch.Tensor, sink: torch.Tensor) -> None:
+    """sink += column sums of src (a bias gradient), on the weight-gradient stream."""
+    s = _wgrad["stream"] if _SIDE_COLSUM else None
+    if s is None:
+        _C.colsum_bf16(src, sink, True)
+        return
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        _C.colsum_bf16(src, sink, True)
+    src.record_stream(s)
     _wgrad["pending"] = True
 
 
@@ -132,7 +146,7 @@ class LinearFn(torch.autograd.Function):
             bsink = _sink(ctx.bias)
             if N % 8 == 0:
                 if bsink is not None:
-                    _C.colsum_bf16(dz, bsink, True)
+                    _wgrad_colsum(dz, bsink)
                     _notify(ctx.bias)
                 else:
                     db = _C.colsum_bf16(dz)
@@ -192,7 +206,7 @@ class MlpGeluFn(torch.autograd.Function):
                 continue
             bsink = _sink(b)
             if bsink is not None:
-                _C.colsum_bf16(src, bsink, True)
+                _wgrad_colsum(src, bsink)
                 _notify(b)
                 grads[name] = None
             else:
