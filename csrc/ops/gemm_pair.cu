@@ -153,12 +153,11 @@ __device__ __forceinline__ uint4 pack8(const float (&v)[8]) {
 // `ncols` (a multiple of 64) accumulator columns of this warp's 32 rows; the thread's row is row0 + lane.
 template <bool kGelu, typename F>
 __device__ __forceinline__ void epilogue_tma(const GemmDev& g, const CUtensorMap* map_d, const CUtensorMap* map_aux, uint8_t* stage, uint32_t taddr,
-                                             int row0, int col0, int ncols, int lane, F&& last_read) {
+                                             int row0, int col0, int ncols, int lane, const float4& bias4, F&& last_read) {
   const int row = row0 + lane;
   const bool has_bias = g.epilogue == EPI_BIAS || g.epilogue == EPI_BIAS_GELU || g.epilogue == EPI_BIAS_GELU_D;
   const bool gelu_d = kGelu && (g.epilogue == EPI_BIAS_GELU_D || g.epilogue == EPI_GELU_D);
   const bool gelu_z = kGelu && (g.epilogue == EPI_BIAS_GELU || g.epilogue == EPI_GELU);
-  const bool bias_vec = (reinterpret_cast<uintptr_t>(g.bias) & 15) == 0;
   if (g.d_fp32) {
     const bool add = g.atomic_add || g.accumulate;
 #pragma unroll 1
@@ -205,15 +204,17 @@ __device__ __forceinline__ void epilogue_tma(const GemmDev& g, const CUtensorMap
       for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(j < 4 ? ra[j * 8 + e] : rb[(j - 4) * 8 + e]);
       const int col = cg + j * 8;
       const bool inside = col < g.n;   // N is a multiple of 8
-      if (has_bias && inside) {
-        if (bias_vec) {
-          const float4 b0 = __ldg(reinterpret_cast<const float4*>(g.bias + col)), b1 = __ldg(reinterpret_cast<const float4*>(g.bias + col) + 1);
-          v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w;
-          v[4] += b1.x; v[5] += b1.y; v[6] += b1.z; v[7] += b1.w;
-        } else {
-#pragma unroll
-          for (int e = 0; e < 8; ++e) v[e] += __ldg(g.bias + col + e);
-        }
+      if (has_bias) {
+        // lane l holds the bias of columns [col0 + 4 l, col0 + 4 l + 4) of this warp's span (zero outside the matrix)
+        const int src = (c >> 2) + 2 * j;
+        v[0] += __shfl_sync(0xffffffffu, bias4.x, src);
+        v[1] += __shfl_sync(0xffffffffu, bias4.y, src);
+        v[2] += __shfl_sync(0xffffffffu, bias4.z, src);
+        v[3] += __shfl_sync(0xffffffffu, bias4.w, src);
+        v[4] += __shfl_sync(0xffffffffu, bias4.x, src + 1);
+        v[5] += __shfl_sync(0xffffffffu, bias4.y, src + 1);
+        v[6] += __shfl_sync(0xffffffffu, bias4.z, src + 1);
+        v[7] += __shfl_sync(0xffffffffu, bias4.w, src + 1);
       }
       if (kGelu && gelu_d) {
         // value and derivative share one exponential; the derivative is what backward needs, so it is saved instead of z
@@ -411,6 +412,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     const int quarter = warp & 3, half = (warp - 2) >> 2;
     constexpr int kHalfCols = BN / 2;
     uint8_t* stage = smem + L::kStagingOff + (warp - 2) * L::kStagingPerWarp;
+    const bool has_bias = g.epilogue == EPI_BIAS || g.epilogue == EPI_BIAS_GELU || g.epilogue == EPI_BIAS_GELU_D;
     bool ok = true;
     int i = 0;
     for (int w = pair; w < total; w += pairs, ++i) {
@@ -419,6 +421,15 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       const int buf = i & 1;
       const bool stamp = warp == 2 && lane == 0 && tl_detail(g.tl);
       const unsigned long long ts0 = stamp ? tl_now() : 0ull;
+      // this warp's bias values, one float4 per lane, fetched while the MMAs of the tile still run
+      float4 bias4 = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (has_bias) {
+        const int bc = n_blk * BN + half * kHalfCols + 4 * lane;
+        if (4 * lane < kHalfCols && bc < g.n) {   // N is a multiple of 8: four columns are inside or outside together
+          if ((reinterpret_cast<uintptr_t>(g.bias) & 15) == 0) bias4 = __ldg(reinterpret_cast<const float4*>(g.bias + bc));
+          else bias4 = make_float4(__ldg(g.bias + bc), __ldg(g.bias + bc + 1), __ldg(g.bias + bc + 2), __ldg(g.bias + bc + 3));
+        }
+      }
       ok = pair_wait(&acc_full[buf], (i >> 1) & 1, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
@@ -433,10 +444,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         tc::fence_before_sync();
         if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
       };
-      epilogue_tma<kGelu>(g, &tma_d, &tma_aux, stage, tmem_d, row0, col_base, kHalfCols, lane, last_read);
+      epilogue_tma<kGelu>(g, &tma_d, &tma_aux, stage, tmem_d, row0, col_base, kHalfCols, lane, bias4, last_read);
       if (stamp) {
+        const unsigned long long ts2 = tl_now();   // before the records below: their atomics take a microsecond
         tl_mark(g.tl, ts0, ts1, TL_GEMM_PHASE, (1u << 24) | static_cast<uint32_t>(i));
-        tl_mark(g.tl, ts1, tl_now(), TL_GEMM_PHASE, (2u << 24) | static_cast<uint32_t>(i));
+        tl_mark(g.tl, ts1, ts2, TL_GEMM_PHASE, (2u << 24) | static_cast<uint32_t>(i));
       }
     }
     if (lane == 0) bulk_wait_read();   // the stores have read this warp's staging buffer; kernel completion publishes them

@@ -601,8 +601,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_persistent_kernel(const 
       };
       epilogue_tile(gt, stage, tmem_d, row0, col_base, kHalfCols, lane, last_read);
       if (stamp) {
+        const unsigned long long ts2 = tl_now();   // before the records below: their atomics take a microsecond
         tl_mark(g.tl, ts0, ts1, TL_GEMM_PHASE, (1u << 24) | static_cast<uint32_t>(i));
-        tl_mark(g.tl, ts1, tl_now(), TL_GEMM_PHASE, (2u << 24) | static_cast<uint32_t>(i));
+        tl_mark(g.tl, ts1, ts2, TL_GEMM_PHASE, (2u << 24) | static_cast<uint32_t>(i));
       }
       if (f.mode == FUSE_REDUCE_SCATTER_D) {
         // count this warp's part of the tile; the warp that completes a phase tells every rank
