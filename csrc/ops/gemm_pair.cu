@@ -138,8 +138,6 @@ __device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, const 
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // the stores committed so far have read their shared-memory source (it may be overwritten)
 __device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
-// ... and have been written
-__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 __device__ __forceinline__ uint4 pack8(const float (&v)[8]) {
@@ -158,6 +156,9 @@ __device__ __forceinline__ void epilogue_tma(const GemmDev& g, const CUtensorMap
   const bool has_bias = g.epilogue == EPI_BIAS || g.epilogue == EPI_BIAS_GELU || g.epilogue == EPI_BIAS_GELU_D;
   const bool gelu_d = kGelu && (g.epilogue == EPI_BIAS_GELU_D || g.epilogue == EPI_GELU_D);
   const bool gelu_z = kGelu && (g.epilogue == EPI_BIAS_GELU || g.epilogue == EPI_GELU);
+  // one input with the layout of the output is prefetched (the GELU instantiation takes none: its launcher refuses them)
+  const __nv_bfloat16* extra_in = kGelu ? nullptr : (g.mul ? g.mul : g.residual);
+  const bool both_in = !kGelu && g.mul != nullptr && g.residual != nullptr;
   if (g.d_fp32) {
     const bool add = g.atomic_add || g.accumulate;
 #pragma unroll 1
@@ -192,9 +193,16 @@ __device__ __forceinline__ void epilogue_tma(const GemmDev& g, const CUtensorMap
     uint32_t ra[32], rb[32];
     tc::tmem_ld_32x32(taddr + static_cast<uint32_t>(c), ra);
     tc::tmem_ld_32x32(taddr + static_cast<uint32_t>(c + 32), rb);
+    const int cg = col0 + c;
+    // the thread's 64 values of the multiplier (or residual): eight independent loads in flight during the wait below
+    uint4 extra[8];
+    if (extra_in && row < g.m) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (cg + j * 8 < g.n) extra[j] = __ldg(reinterpret_cast<const uint4*>(extra_in + static_cast<size_t>(row) * g.ldd + cg + j * 8));
+    }
     tc::tmem_ld_wait();
     if (c + 64 >= ncols) last_read();
-    const int cg = col0 + c;
     if (row0 >= g.m || cg >= g.n) continue;   // uniform over the warp
     uint4 out[8], aux_out[8];
 #pragma unroll
@@ -227,17 +235,21 @@ __device__ __forceinline__ void epilogue_tma(const GemmDev& g, const CUtensorMap
 #pragma unroll
         for (int e = 0; e < 8; ++e) v[e] = gelu_erf(v[e]);
       }
-      if (g.mul && inside && row < g.m) {
-        const uint4 pk = *reinterpret_cast<const uint4*>(g.mul + static_cast<size_t>(row) * g.ldd + col);
-        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&pk);
+      if (extra_in && inside && row < g.m) {
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&extra[j]);
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const float2 t = __bfloat1622float2(h[e]);
-          v[2 * e] *= t.x;
-          v[2 * e + 1] *= t.y;
+          if (g.mul) {
+            v[2 * e] *= t.x;
+            v[2 * e + 1] *= t.y;
+          } else {
+            v[2 * e] += t.x;
+            v[2 * e + 1] += t.y;
+          }
         }
       }
-      if (g.residual && inside && row < g.m) {
+      if (both_in && inside && row < g.m) {
         const uint4 pk = *reinterpret_cast<const uint4*>(g.residual + static_cast<size_t>(row) * g.ldd + col);
         const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&pk);
 #pragma unroll
@@ -584,7 +596,8 @@ cudaError_t launch_gemm_pair(const GemmArgs& a, cudaStream_t stream) {
                                 : launch_pair_cfg<BN, ST, false, false>(a, stream)))
   const bool gelu = a.epilogue == EPI_BIAS_GELU || a.epilogue == EPI_GELU || a.epilogue == EPI_BIAS_GELU_D || a.epilogue == EPI_GELU_D;
   if (gelu) {
-    if (a.a_mn_major || a.b_mn_major) return cudaErrorNotSupported;   // activations are applied in forward products only
+    // activations are applied in forward products only; combined with a multiplier or residual they take the one-CTA kernel
+    if (a.a_mn_major || a.b_mn_major || a.mul || a.residual) return launch_gemm_persistent(a, FusedDev{}, 0, stream);
     return wide ? launch_pair_cfg<256, 6, false, false, true>(a, stream) : launch_pair_cfg<128, 8, false, false, true>(a, stream);
   }
   return wide ? MCCL_PAIR(256, 6) : MCCL_PAIR(128, 8);
