@@ -188,7 +188,7 @@ void bind_ops(py::module_& m) {
       "norm_bwd",
       [](const at::Tensor& dy, const at::Tensor& x, const at::Tensor& w, const at::Tensor& mean, const at::Tensor& rstd,
          bool layernorm, const c10::optional<at::Tensor>& dw_out, const c10::optional<at::Tensor>& db_out, bool accumulate,
-         const c10::optional<at::Tensor>& dx_add) {
+         const c10::optional<at::Tensor>& dx_add, int parts) {
         need(dy, at::kBFloat16, "norm_bwd(dy)");
         const __nv_bfloat16* addp = nullptr;
         if (dx_add.has_value() && dx_add->defined()) {
@@ -202,7 +202,7 @@ void bind_ops(py::module_& m) {
         need(rstd, at::kFloat, "norm_bwd(rstd)");
         c10::cuda::CUDAGuard guard(x.device());
         const int64_t dim = x.size(-1), rows = x.numel() / dim;
-        at::Tensor dx = at::empty_like(x);
+        at::Tensor dx = (parts & 1) ? at::empty_like(x) : at::Tensor();   // parts: 1 = dx only, 2 = parameter gradients only
         // dw_out / db_out: write the parameter gradients straight into these fp32 buffers
         at::Tensor dw = dw_out.has_value() ? *dw_out : at::empty({dim}, x.options().dtype(at::kFloat));
         at::Tensor db = !layernorm ? at::Tensor() : (db_out.has_value() ? *db_out : at::empty({dim}, x.options().dtype(at::kFloat)));
@@ -213,17 +213,19 @@ void bind_ops(py::module_& m) {
         at::Tensor scratch;
         if (!accumulate)
           scratch = at::empty({2 * ops::colsum_slabs(static_cast<int>(rows)) * dim}, x.options().dtype(at::kFloat));
-        check_launch(ops::norm_bwd(bf(dy), bf(x), w.data_ptr<float>(), mean.data_ptr<float>(), rstd.data_ptr<float>(), bf(dx),
+        check_launch(ops::norm_bwd(bf(dy), bf(x), w.data_ptr<float>(), mean.data_ptr<float>(), rstd.data_ptr<float>(),
+                                   dx.defined() ? bf(dx) : nullptr,
                                    dw.data_ptr<float>(), layernorm ? db.data_ptr<float>() : nullptr,
                                    accumulate ? nullptr : scratch.data_ptr<float>(),
                                    static_cast<int>(rows),
-                                   static_cast<int>(dim), layernorm, stream_of(x), addp),
+                                   static_cast<int>(dim), layernorm, stream_of(x), addp, parts),
                      "norm_bwd");
-        return std::make_tuple(dx, dw, db.defined() ? c10::optional<at::Tensor>(db) : c10::nullopt);
+        return std::make_tuple(dx.defined() ? c10::optional<at::Tensor>(dx) : c10::nullopt, dw,
+                               db.defined() ? c10::optional<at::Tensor>(db) : c10::nullopt);
       },
       py::arg("dy"), py::arg("x"), py::arg("weight"), py::arg("mean"), py::arg("rstd"), py::arg("layernorm"),
       py::arg("dw_out") = py::none(), py::arg("db_out") = py::none(), py::arg("accumulate") = false,
-      py::arg("dx_add") = py::none());
+      py::arg("dx_add") = py::none(), py::arg("parts") = 3);
 
   m.def(
       "adamw_flat",

@@ -1044,10 +1044,12 @@ __global__ void __launch_bounds__(kThreads) alltoall_kernel(DevComm c, A2AArgs a
     for (int k = 0; k < N; ++k) {
       const int q = (rank + k) % N;
       const unsigned long long len = a.in_len[vr][q] > lo ? (a.in_len[vr][q] - lo < slot ? a.in_len[vr][q] - lo : slot) : 0;
-      // The slot is cut among the CTAs once, whatever the round's length: a byte of the slot then belongs to the same
-      // CTA index in every round, and the per-CTA meetings below are all the ordering a slot byte needs.
+      // The slot is cut among the CTAs once per pair, whatever the round's length: a byte of the slot then belongs to
+      // the same CTA index in every round, and the per-CTA meetings below are all the ordering a slot byte needs.
+      // A segment shorter than the slot has one round and is cut by its own length, so that every CTA moves a share
+      // (both sides know the length: what this rank sends to q is what q receives from this rank).
       unsigned long long b0, b1;
-      cta_byte_span(slot, b0, b1);
+      cta_byte_span(a.in_len[vr][q] < slot ? a.in_len[vr][q] : slot, b0, b1);
       b0 = b0 < len ? b0 : len;
       b1 = b1 < len ? b1 : len;
       if (q == rank)
@@ -1060,7 +1062,7 @@ __global__ void __launch_bounds__(kThreads) alltoall_kernel(DevComm c, A2AArgs a
       const int p = (rank + k) % N;
       const unsigned long long len = a.out_len[vr][p] > lo ? (a.out_len[vr][p] - lo < slot ? a.out_len[vr][p] - lo : slot) : 0;
       unsigned long long b0, b1;
-      cta_byte_span(slot, b0, b1);
+      cta_byte_span(a.out_len[vr][p] < slot ? a.out_len[vr][p] : slot, b0, b1);
       b0 = b0 < len ? b0 : len;
       b1 = b1 < len ? b1 : len;
       cta_copy_bytes_uncached(out + a.out_off[vr][p] + lo + b0, c.arena[rank] + base + static_cast<size_t>(p) * slot + b0, b1 - b0);

@@ -30,7 +30,7 @@ cudaError_t norm_fwd(const __nv_bfloat16* x, const float* w, const float* b, __n
 // second gradient of x (a residual path) that is added to dx before the one rounding to bf16.
 cudaError_t norm_bwd(const __nv_bfloat16* dy, const __nv_bfloat16* x, const float* w, const float* mean, const float* rstd,
                      __nv_bfloat16* dx, float* dw, float* db, float* scratch, int rows, int dim, bool layernorm,
-                     cudaStream_t stream, const __nv_bfloat16* dx_add = nullptr);
+                     cudaStream_t stream, const __nv_bfloat16* dx_add = nullptr, int parts = 3);
 // out[c] = sum over rows of in[r, c] (bias gradients).  scratch: colsum_slabs(rows) * dim floats,
 // or nullptr to add into out atomically in one pass.
 cudaError_t colsum_bf16(const __nv_bfloat16* in, float* out, float* scratch, int rows, int dim, cudaStream_t stream);

@@ -66,6 +66,20 @@ def _wgrad_gemm(a_mat: torch.Tensor, b_mat: torch.Tensor, sink: torch.Tensor) ->
     _wgrad["pending"] = True
 
 
+def _norm_param_grads(dyc, x, weight, mean, rstd, layernorm, wsink, bsink) -> bool:
+    """dw / db of a norm on the weight-gradient stream; False when there is none (the caller then computes them in line)."""
+    s = _wgrad["stream"] if _SIDE_COLSUM else None
+    if s is None:
+        return False
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        _C.norm_bwd(dyc, x, weight, mean, rstd, layernorm, wsink, bsink, True, None, 2)
+    for t in (dyc, x, mean, rstd):
+        t.record_stream(s)
+    _wgrad["pending"] = True
+    return True
+
+
 def _wgrad_colsum(src: torch.Tensor, sink: torch.Tensor) -> None:
     """sink += column sums of src (a bias gradient), on the weight-gradient stream."""
     s = _wgrad["stream"] if _SIDE_COLSUM else None
@@ -257,7 +271,8 @@ class NormFn(torch.autograd.Function):
         wsink, bsink = _sink(ctx.weight), (_sink(ctx.bias) if ctx.bias is not None else None)
         if wsink is not None and (not ctx.layernorm or bsink is not None):
             # the sinks were zeroed at the start of the step; the kernel adds into them
-            dx, _, _ = _C.norm_bwd(dyc, x, weight, mean, rstd, ctx.layernorm, wsink, bsink, True)
+            side = _norm_param_grads(dyc, x, weight, mean, rstd, ctx.layernorm, wsink, bsink)
+            dx, _, _ = _C.norm_bwd(dyc, x, weight, mean, rstd, ctx.layernorm, wsink, bsink, True, None, 1 if side else 3)
             _notify(ctx.weight)
             if ctx.bias is not None:
                 _notify(ctx.bias)
@@ -289,7 +304,8 @@ class NormResidualFn(torch.autograd.Function):
         add = None if dres is None else (dres if dres.is_contiguous() else dres.contiguous())
         wsink, bsink = _sink(ctx.weight), (_sink(ctx.bias) if ctx.bias is not None else None)
         if wsink is not None and (not ctx.layernorm or bsink is not None):
-            dx, _, _ = _C.norm_bwd(dyc, x, weight, mean, rstd, ctx.layernorm, wsink, bsink, True, add)
+            side = _norm_param_grads(dyc, x, weight, mean, rstd, ctx.layernorm, wsink, bsink)
+            dx, _, _ = _C.norm_bwd(dyc, x, weight, mean, rstd, ctx.layernorm, wsink, bsink, True, add, 1 if side else 3)
             _notify(ctx.weight)
             if ctx.bias is not None:
                 _notify(ctx.bias)

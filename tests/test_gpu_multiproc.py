@@ -345,6 +345,12 @@ def _tp_gemms(rank, world):
 
 
 def test_fused_tensor_parallel_gemms():
+    """All-gather -> GEMM and GEMM -> reduce-scatter against fp32 matmuls of the gathered / summed operands.
+
+    Tolerance: the reduce-scatter fusion rounds every rank's partial product to bf16 before the owner adds the
+    `world` partials in fp32 and rounds the sum once more, so the result carries up to world + 1 bf16 roundings
+    (relative 2^-8 each) of values of magnitude sqrt(K) ~ 23 where an unfused fp32 reduction would carry one;
+    2e-2 relative to the largest output covers 8 ranks with margin."""
     worst = spawn(_tp_gemms, _world(), timeout=300, _cuda=True)
     assert max(worst) < 2e-2, worst
 
