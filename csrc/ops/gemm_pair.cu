@@ -32,10 +32,14 @@ int gemm_choose_splits(int tiles, int num_kb, int workers);   // gemm_persistent
 
 namespace {
 
-constexpr int kPairEpiWarps = 8;
-constexpr int kPairThreads = 32 * (2 + kPairEpiWarps);
+// Epilogue warps per CTA: two per tensor-memory lane quarter; the GELU instantiation, whose epilogue is 25 instructions
+// of arithmetic per value, takes four per quarter (each a quarter of the tile's columns) so that twice as many
+// dependent chains are in flight per scheduler.
+// (Wide tiles only: a warp finishes 64-column groups, and a 128-wide tile has just two of them per lane quarter.)
+constexpr int pair_epi_warps(bool gelu, int bn) { return gelu && bn == 256 ? 16 : 8; }
+constexpr int pair_threads(bool gelu, int bn) { return 32 * (2 + pair_epi_warps(gelu, bn)); }
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, bool kGelu = false>
 struct PairLayout {
   static constexpr int kABytes = BM * BK * 2;             // this CTA's 128 rows of A
   static constexpr int kBBytes = (BN / 2) * BK * 2;       // this CTA's half of the B tile
@@ -44,7 +48,7 @@ struct PairLayout {
   static constexpr int kBarriers = (2 * STAGES + 4) * 8 + 16;
   static constexpr int kStagingOff = kTiles + 1024;      // 1024-byte aligned: TMA stores read it with the 128-byte swizzle
   static constexpr int kStagingPerWarp = 4096;
-  static constexpr int kTotal = kStagingOff + kPairEpiWarps * kStagingPerWarp + 1024;
+  static constexpr int kTotal = kStagingOff + pair_epi_warps(kGelu, BN) * kStagingPerWarp + 1024;
   static_assert(kBarriers <= 1024, "barriers overlap the epilogue staging");
   static_assert(kTotal <= 227 * 1024, "shared memory of one CTA");
 };
@@ -188,6 +192,75 @@ __device__ __forceinline__ void epilogue_tma(const GemmDev& g, const CUtensorMap
     }
     return;
   }
+  if constexpr (kGelu) {
+    // 32 columns at a time (one tensor-memory read, 32 live accumulators): this instantiation runs 576 threads and
+    // has 112 registers per thread.  D goes to the staging buffer as it is produced, the second output waits packed
+    // in registers until D's store has read the buffer.
+#pragma unroll 1
+    for (int c = 0; c < ncols; c += 64) {
+      const int cg = col0 + c;
+      const bool active = row0 < g.m && cg < g.n;   // uniform over the warp
+      uint4 aux_out[8];
+      if (lane == 0) bulk_wait_read();
+      __syncwarp();
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        uint32_t r[32];
+        tc::tmem_ld_32x32(taddr + static_cast<uint32_t>(c + 32 * h), r);
+        tc::tmem_ld_wait();
+        if (h == 1 && c + 64 >= ncols) last_read();
+        if (!active) continue;
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) {
+          const int j = 4 * h + jj;
+          float v[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(r[jj * 8 + e]);
+          if (has_bias) {
+            const int src = (c >> 2) + 2 * j;
+            v[0] += __shfl_sync(0xffffffffu, bias4.x, src);
+            v[1] += __shfl_sync(0xffffffffu, bias4.y, src);
+            v[2] += __shfl_sync(0xffffffffu, bias4.z, src);
+            v[3] += __shfl_sync(0xffffffffu, bias4.w, src);
+            v[4] += __shfl_sync(0xffffffffu, bias4.x, src + 1);
+            v[5] += __shfl_sync(0xffffffffu, bias4.y, src + 1);
+            v[6] += __shfl_sync(0xffffffffu, bias4.z, src + 1);
+            v[7] += __shfl_sync(0xffffffffu, bias4.w, src + 1);
+          }
+          if (gelu_d) {
+            // value and derivative share one exponential; the derivative is what backward needs, so it is saved instead of z
+            float dv[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) gelu_value_grad(v[e], v[e], dv[e]);
+            aux_out[j] = pack8(dv);
+          } else {
+            aux_out[j] = pack8(v);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[e] = gelu_erf(v[e]);
+          }
+          *stage_unit(stage, lane, j) = pack8(v);
+        }
+      }
+      if (!active) continue;
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        tma_store_2d(map_d, stage, cg, row0);
+        bulk_commit();
+        bulk_wait_read();
+      }
+      __syncwarp();
+#pragma unroll
+      for (int j = 0; j < 8; ++j) *stage_unit(stage, lane, j) = aux_out[j];
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        tma_store_2d(map_aux, stage, cg, row0);
+        bulk_commit();
+      }
+    }
+    return;
+  }
 #pragma unroll 1
   for (int c = 0; c < ncols; c += 64) {
     uint32_t ra[32], rb[32];
@@ -289,10 +362,10 @@ __device__ __forceinline__ void epilogue_tma(const GemmDev& g, const CUtensorMap
 // kGelu: the instantiation for GELU epilogues (two outputs, 25 instructions of arithmetic per value).  It is a kernel of
 // its own so that every other product runs without that code in its instruction stream.
 template <int BN, int STAGES, bool kAMn, bool kBMn, bool kGelu>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair_threads(kGelu, BN), 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                  const __grid_constant__ CUtensorMap tma_d, const __grid_constant__ CUtensorMap tma_aux, GemmDev g, int k_splits) {
-  using L = PairLayout<BN, STAGES>;
+  using L = PairLayout<BN, STAGES, kGelu>;
   constexpr int BNH = BN / 2;
   extern __shared__ uint8_t smem_raw[];
   // the same offset in both CTAs: the MMA addresses the peer's operands by this CTA's offsets
@@ -305,6 +378,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
+  // Dependent launch (only with MCCL_PDL=1): the kernel after this one may become resident as SMs free up; this
+  // kernel's own set-up below touches no global data and runs while the kernel before it drains.
+  pdl_trigger();
   const unsigned long long tl_t0 = tl_begin(g.tl);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
@@ -321,7 +397,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     }
     for (int b = 0; b < 2; ++b) {
       tc::mbar_init(&acc_full[b], 1);
-      tc::mbar_init(&acc_empty[b], 2 * kPairEpiWarps);   // the epilogue warps of both CTAs
+      tc::mbar_init(&acc_empty[b], 2 * pair_epi_warps(kGelu, BN));   // the epilogue warps of both CTAs
     }
     *abort_flag = 0;
     tc::mbar_init_fence();
@@ -337,6 +413,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   cluster_sync_all();
   tc::fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();   // set-up done: from here on operands are read and outputs written
   if (tl_t0 != 0ull && tl_detail(g.tl)) tl_mark(g.tl, tl_t0, tl_now(), TL_GEMM_PHASE, 0u);
 
   auto tile_coords = [&](int w, int& m_blk, int& n_blk, int& kb0) {
@@ -422,7 +499,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   } else {
     // ----------------------------------------------------------- epilogue --
     const int quarter = warp & 3, half = (warp - 2) >> 2;
-    constexpr int kHalfCols = BN / 2;
+    constexpr int kHalfCols = BN / (pair_epi_warps(kGelu, BN) / 4);   // columns per epilogue warp
     uint8_t* stage = smem + L::kStagingOff + (warp - 2) * L::kStagingPerWarp;
     const bool has_bias = g.epilogue == EPI_BIAS || g.epilogue == EPI_BIAS_GELU || g.epilogue == EPI_BIAS_GELU_D;
     bool ok = true;
@@ -488,12 +565,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
 // Clusters of two that can be resident at once (GPCs with an odd number of free SMs leave one SM out).
 template <int BN, int STAGES, bool kAMn, bool kBMn, bool kGelu>
 int max_pairs() {
-  using L = PairLayout<BN, STAGES>;
+  using L = PairLayout<BN, STAGES, kGelu>;
   static int cached = 0;
   if (cached > 0) return cached;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2 * 74);
-  cfg.blockDim = dim3(kPairThreads);
+  cfg.blockDim = dim3(pair_threads(kGelu, BN));
   cfg.dynamicSmemBytes = L::kTotal;
   cfg.numAttrs = 0;   // the cluster shape is part of the kernel (__cluster_dims__)
   int n = 0;
@@ -507,7 +584,7 @@ int max_pairs() {
 
 template <int BN, int STAGES, bool kAMn, bool kBMn, bool kGelu = false>
 cudaError_t launch_pair_cfg(const GemmArgs& a, cudaStream_t stream) {
-  using L = PairLayout<BN, STAGES>;
+  using L = PairLayout<BN, STAGES, kGelu>;
   static bool configured = false;
   if (!configured) {
     cudaError_t rc = cudaFuncSetAttribute(gemm_pair_kernel<BN, STAGES, kAMn, kBMn, kGelu>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal);
@@ -563,7 +640,7 @@ cudaError_t launch_pair_cfg(const GemmArgs& a, cudaStream_t stream) {
     }
   }
   if (tiles < pairs) pairs = tiles;
-  MCCL_LAUNCH((gemm_pair_kernel<BN, STAGES, kAMn, kBMn, kGelu>), 2 * pairs, kPairThreads, L::kTotal, stream, ma, mb, md, maux, g, splits);
+  MCCL_LAUNCH_PDL((gemm_pair_kernel<BN, STAGES, kAMn, kBMn, kGelu>), 2 * pairs, pair_threads(kGelu, BN), L::kTotal, stream, ma, mb, md, maux, g, splits);
   count_launch();
   return ::mccl::launch_status();
 }
@@ -598,7 +675,8 @@ cudaError_t launch_gemm_pair(const GemmArgs& a, cudaStream_t stream) {
   if (gelu) {
     // activations are applied in forward products only; combined with a multiplier or residual they take the one-CTA kernel
     if (a.a_mn_major || a.b_mn_major || a.mul || a.residual) return launch_gemm_persistent(a, FusedDev{}, 0, stream);
-    return wide ? launch_pair_cfg<256, 6, false, false, true>(a, stream) : launch_pair_cfg<128, 8, false, false, true>(a, stream);
+    // sixteen staging buffers in the wide instantiation: one TMA stage fewer
+    return wide ? launch_pair_cfg<256, 5, false, false, true>(a, stream) : launch_pair_cfg<128, 8, false, false, true>(a, stream);
   }
   return wide ? MCCL_PAIR(256, 6) : MCCL_PAIR(128, 8);
 #undef MCCL_PAIR

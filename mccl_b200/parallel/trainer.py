@@ -317,7 +317,10 @@ class DDPTrainer:
         torch.cuda.synchronize(self.device)
         before = ops.launch_count() + (self.comm.launches if self.comm is not None else 0)
         self.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.graph):
+        # the step is captured on a high-priority stream: its kernels are placed before those of the weight-gradient
+        # stream (default priority), which then only fills what the main chain leaves free
+        capture_stream = torch.cuda.Stream(device=self.device, priority=-1)
+        with torch.cuda.graph(self.graph, stream=capture_stream):
             self.static_loss = self._step_body(self.static_tokens, self.static_targets)
         self.launches_per_step = ops.launch_count() + (self.comm.launches if self.comm is not None else 0) - before
 
