@@ -53,6 +53,9 @@ void bind_ops(py::module_& m) {
   m.def("launch_counts", [] { return launch_counts(); }, "Launches per kernel name since the process started.");
   m.def("launch_counts_reset", [] { launch_counts_reset(); });
   m.def("launch_total", [] { return launch_total(); });
+  m.def("set_gemm_kernel", &ops::set_gemm_kernel, py::arg("name"),
+        "Kernel for plain products from now on: 'pair' (CTA pairs, tcgen05.mma.cta_group::2; the default), 'persistent' "
+        "(one CTA per SM), 'tile' (one tile per CTA); '' returns to MCCL_GEMM_KERNEL / the default.");
   m.def("set_gemm_cta_limit", &ops::set_gemm_cta_limit, py::arg("ctas"),
         "Caps the CTAs (SMs) of plain GEMM launches from now on; 0 = one per SM.");
   m.def("gemm_cta_limit", &ops::gemm_cta_limit);

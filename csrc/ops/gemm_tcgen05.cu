@@ -19,6 +19,8 @@
 #include "gemm_common.cuh"
 #include "gemm_persistent.cuh"
 
+#include <atomic>
+
 #include <cstdlib>
 #include <string>
 
@@ -206,6 +208,18 @@ cudaError_t launch_cfg(const GemmArgs& a, cudaStream_t stream) {
 #define MCCL_GEMM_DEFAULT_KERNEL 1
 #endif
 
+namespace {
+std::atomic<int> g_gemm_kernel_override{-1};
+int kernel_index(const std::string& s) {
+  return s == "tile" ? 2 : (s == "pair" ? 1 : (s == "persistent" ? 0 : MCCL_GEMM_DEFAULT_KERNEL));
+}
+}  // namespace
+
+// "pair", "persistent" or "tile" for the calls that follow; "" returns to MCCL_GEMM_KERNEL / the default.
+void set_gemm_kernel(const std::string& name) {
+  g_gemm_kernel_override.store(name.empty() ? -1 : kernel_index(name), std::memory_order_relaxed);
+}
+
 const char* gemm_last_reason() { return t_reason; }
 
 cudaError_t gemm_bf16_tn(const GemmArgs& a, cudaStream_t stream) {
@@ -227,11 +241,12 @@ cudaError_t gemm_bf16_tn(const GemmArgs& a, cudaStream_t stream) {
   if (a.a_mn_major && a.m % 8 != 0) return unsupported("an MN-major A needs M to be a multiple of 8");
   // MCCL_GEMM_KERNEL: "pair" = CTA pairs (tcgen05.mma.cta_group::2), "persistent" = one CTA per SM,
   // "tile" = the one-tile-per-CTA kernel below.
-  static const int kernel_choice = [] {
+  static const int env_choice = [] {
     const char* v = std::getenv("MCCL_GEMM_KERNEL");
-    const std::string s = v ? v : "";
-    return s == "tile" ? 2 : (s == "pair" ? 1 : (s == "persistent" ? 0 : MCCL_GEMM_DEFAULT_KERNEL));
+    return kernel_index(v ? v : "");
   }();
+  const int forced = g_gemm_kernel_override.load(std::memory_order_relaxed);
+  const int kernel_choice = forced >= 0 ? forced : env_choice;
   if (kernel_choice != 2) {
     cudaError_t rc = kernel_choice == 1 ? launch_gemm_pair(a, stream) : launch_gemm_persistent(a, FusedDev{}, 0, stream);
     if (rc == cudaErrorNotSupported) return unsupported("cuTensorMapEncodeTiled rejected an operand");

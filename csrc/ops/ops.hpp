@@ -11,6 +11,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdint>
+#include <string>
 
 namespace mccl {
 namespace ops {
@@ -105,6 +106,8 @@ cudaError_t gemm_bf16_tn(const GemmArgs& args, cudaStream_t stream);
 // data-parallel trainer lowers it during backward so that a few SMs stay free for the gradient collectives
 // that run beside the GEMMs.  The value is read at launch time, so it is baked into a captured CUDA graph.
 void set_gemm_cta_limit(int ctas);
+// Which kernel plain products use: "pair" (CTA pairs, the default), "persistent" (one CTA per SM), "tile"; "" = default.
+void set_gemm_kernel(const std::string& name);
 int gemm_cta_limit();
 int gemm_sm_count();
 // Why the last gemm_bf16_tn call on this thread returned cudaErrorNotSupported ("" otherwise).

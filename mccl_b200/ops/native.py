@@ -45,6 +45,11 @@ def set_wgrad_stream(stream) -> None:
     _wgrad["pending"] = False
 
 
+def mark_wgrad_pending() -> None:
+    """A trainer queued work of its own on the weight-gradient stream."""
+    _wgrad["pending"] = True
+
+
 def join_wgrad(stream=None) -> None:
     """Makes ``stream`` (default: the current one) wait for the weight gradients queued on the side stream."""
     s = _wgrad["stream"]
@@ -205,6 +210,12 @@ class MlpGeluFn(torch.autograd.Function):
             dy2 = dy2.contiguous()
         # second layer: dz = (dy . W2) * gelu'(pre-activation) in one kernel; dW2 = dy^T . h; db2 = column sums of dy
         dz, _ = _C.gemm_bf16(dy2, w2_16, None, "none", False, None, False, False, True, None, z)
+        # the input gradient first: every reader of this node's weights is queued before a parameter is reported
+        # complete (a trainer may start that parameter's optimizer update on another stream as soon as it is)
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dx, _ = _C.gemm_bf16(dz, w1_16, None, "none", False, None, False, False, True)
+            dx = dx.view(*dy.shape[:-1], w1_16.shape[1])
         grads = {}
         for name, (w, a_mat, b_mat) in (("w2", (w2, dy2, h)), ("w1", (w1, dz, x2))):
             sink = _sink(w)
@@ -225,10 +236,6 @@ class MlpGeluFn(torch.autograd.Function):
                 grads[name] = None
             else:
                 grads[name] = _C.colsum_bf16(src)
-        dx = None
-        if ctx.needs_input_grad[0]:
-            dx, _ = _C.gemm_bf16(dz, w1_16, None, "none", False, None, False, False, True)
-            dx = dx.view(*dy.shape[:-1], w1_16.shape[1])
         return dx, grads["w1"], grads["b1"], grads["w2"], grads["b2"], (dy if ctx.has_residual else None)
 
 

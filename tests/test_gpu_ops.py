@@ -15,9 +15,18 @@ def _rel(a, b):
     return ((a.double() - b.double()).abs().max() / b.double().abs().max().clamp_min(1e-6)).item()
 
 
+@pytest.fixture(params=["pair", "persistent"])
+def gemm_kernel(request):
+    """Runs a GEMM test once per kernel: CTA pairs (the default) and the one-CTA persistent kernel."""
+    C = _C()
+    C.set_gemm_kernel(request.param)
+    yield request.param
+    C.set_gemm_kernel("")
+
+
 @pytest.mark.parametrize("M,N,K", [(128, 128, 64), (256, 384, 128), (4096, 512, 512), (4096, 1536, 512), (1000, 264, 192),
-                                   (4096, 512, 2048), (130, 8, 64), (4096, 32000, 512)])
-def test_gemm_matches_fp32_reference(M, N, K):
+                                   (4096, 512, 2048), (130, 8, 64), (4096, 32000, 512), (4096, 2048, 512), (300, 2048, 64)])
+def test_gemm_matches_fp32_reference(M, N, K, gemm_kernel):
     C = _C()
     torch.manual_seed(M + N + K)
     a = torch.randn(M, K, device="cuda").bfloat16()
@@ -39,7 +48,7 @@ def test_gemm_matches_fp32_reference(M, N, K):
 
 @pytest.mark.parametrize("a_t,b_t", [(True, False), (False, True), (True, True)])
 @pytest.mark.parametrize("M,N,K", [(128, 128, 64), (512, 384, 256), (2048, 512, 4096), (200, 72, 128)])
-def test_gemm_mn_major_operands(a_t, b_t, M, N, K):
+def test_gemm_mn_major_operands(a_t, b_t, M, N, K, gemm_kernel):
     """Operands stored [K, M] / [K, N] are read MN-major: same product, no transposed copy."""
     C = _C()
     torch.manual_seed(M * 3 + N * 5 + K)
@@ -54,10 +63,10 @@ def test_gemm_mn_major_operands(a_t, b_t, M, N, K):
     assert _rel(d, ref) < 1e-5 * max(1, K // 64), (_rel(d, ref), a_t, b_t)
 
 
-def test_gemm_epilogues_and_strides():
+@pytest.mark.parametrize("M,N,K", [(512, 256, 128), (1000, 2048, 192), (4096, 2048, 512)])
+def test_gemm_epilogues_and_strides(M, N, K, gemm_kernel):
     C = _C()
     torch.manual_seed(1)
-    M, N, K = 512, 256, 128
     a = torch.randn(M, K, device="cuda").bfloat16()
     b = torch.randn(N, K, device="cuda").bfloat16() * 0.1
     bias = torch.randn(N, device="cuda")
@@ -68,6 +77,18 @@ def test_gemm_epilogues_and_strides():
     assert _rel(z, ref_z) < 1e-2 and _rel(d, F.gelu(ref_z)) < 1e-2
     d, z = C.gemm_bf16(a, b, None, "gelu")
     assert _rel(d, F.gelu(a.float() @ b.float().t())) < 1e-2
+    # gelu_d: the second output is gelu'(z) instead of z
+    d, dz = C.gemm_bf16(a, b, bias, "gelu_d")
+    zz = ref_z.clone().requires_grad_(True)
+    F.gelu(zz).sum().backward()
+    assert _rel(d, F.gelu(ref_z)) < 1e-2 and _rel(dz, zz.grad) < 1e-2
+    # residual added after the bias; multiplier applied to the product (the backward of a GELU)
+    res = torch.randn(M, N, device="cuda").bfloat16()
+    d, _ = C.gemm_bf16(a, b, bias, "none", False, None, False, False, False, res)
+    assert _rel(d, ref_z + res.float()) < 1e-2
+    mul = torch.randn(M, N, device="cuda").bfloat16()
+    d, _ = C.gemm_bf16(a, b, None, "none", False, None, False, False, False, None, mul)
+    assert _rel(d, (a.float() @ b.float().t()) * mul.float()) < 1e-2
     # row strides larger than K (views into wider buffers)
     wide_a = torch.randn(M, 3 * K, device="cuda").bfloat16()
     av = wide_a[:, K:2 * K]
