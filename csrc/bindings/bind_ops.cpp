@@ -233,7 +233,7 @@ void bind_ops(py::module_& m) {
   m.def(
       "adamw_flat",
       [](at::Tensor p, const at::Tensor& g, at::Tensor mm, at::Tensor v, const c10::optional<at::Tensor>& p16, double lr,
-         double b1, double b2, double eps, double wd, const at::Tensor& step, double grad_scale, bool zero_grad) {
+         double b1, double b2, double eps, double wd, const at::Tensor& step, double grad_scale, bool zero_grad, int ctas_per_sm) {
         need(p, at::kFloat, "adamw(p)");
         need(g, at::kFloat, "adamw(g)");
         need(mm, at::kFloat, "adamw(m)");
@@ -250,12 +250,12 @@ void bind_ops(py::module_& m) {
         check_launch(ops::adamw_flat(p.data_ptr<float>(), const_cast<float*>(g.data_ptr<float>()), mm.data_ptr<float>(),
                                      v.data_ptr<float>(), p16p, p.numel(), static_cast<float>(lr), static_cast<float>(b1),
                                      static_cast<float>(b2), static_cast<float>(eps), static_cast<float>(wd),
-                                     step.data_ptr<float>(), static_cast<float>(grad_scale), stream_of(p), zero_grad),
+                                     step.data_ptr<float>(), static_cast<float>(grad_scale), stream_of(p), zero_grad, ctas_per_sm),
                      "adamw_flat");
       },
       py::arg("p"), py::arg("g"), py::arg("m"), py::arg("v"), py::arg("p_bf16") = py::none(), py::arg("lr") = 1e-3,
       py::arg("beta1") = 0.9, py::arg("beta2") = 0.999, py::arg("eps") = 1e-8, py::arg("weight_decay") = 0.01,
-      py::arg("step") = at::Tensor(), py::arg("grad_scale") = 1.0, py::arg("zero_grad") = false);
+      py::arg("step") = at::Tensor(), py::arg("grad_scale") = 1.0, py::arg("zero_grad") = false, py::arg("ctas_per_sm") = 8);
 
   m.def(
       "ce_fwd_bwd",
@@ -437,25 +437,34 @@ void bind_ops(py::module_& m) {
                  "embed_fwd");
     return y;
   }, py::arg("ids"), py::arg("tok"), py::arg("pos") = py::none(), py::arg("seq") = 1);
-  m.def("embed_bwd", [](const at::Tensor& ids, const at::Tensor& dy, at::Tensor dtok, const c10::optional<at::Tensor>& dpos,
-                        int64_t seq) {
+  m.def("embed_bwd", [](const at::Tensor& ids, const at::Tensor& dy, const c10::optional<at::Tensor>& dtok,
+                        const c10::optional<at::Tensor>& dpos, int64_t seq, double scale) {
     need(ids, at::kLong, "embed_bwd(ids)");
     need(dy, at::kBFloat16, "embed_bwd(dy)");
-    need(dtok, at::kFloat, "embed_bwd(dtok)");
-    MCCL_CHECK_TENSOR(dtok.dim() == 2 && dtok.size(1) % 8 == 0 && dy.numel() == ids.numel() * dtok.size(1),
-                      "embed_bwd: dy must be [tokens, dim] and dtok [vocab, dim] with dim % 8 == 0");
+    MCCL_CHECK_TENSOR(dy.dim() == 2 && dy.size(1) % 8 == 0 && dy.size(0) == ids.numel(), "embed_bwd: dy must be [tokens, dim] with dim % 8 == 0");
+    const int64_t dim = dy.size(1);
+    float* tp = nullptr;
+    int64_t vocab = 0;
+    if (dtok.has_value() && dtok->defined()) {
+      need(*dtok, at::kFloat, "embed_bwd(dtok)");
+      MCCL_CHECK_TENSOR(dtok->dim() == 2 && dtok->size(1) == dim, "embed_bwd: dtok must be [vocab, dim]");
+      tp = dtok->data_ptr<float>();
+      vocab = dtok->size(0);
+    }
     float* pp = nullptr;
     if (dpos.has_value() && dpos->defined()) {
       need(*dpos, at::kFloat, "embed_bwd(dpos)");
-      MCCL_CHECK_TENSOR(dpos->dim() == 2 && dpos->size(1) == dtok.size(1) && dpos->size(0) >= seq, "embed_bwd: position table too small");
+      MCCL_CHECK_TENSOR(dpos->dim() == 2 && dpos->size(1) == dim && dpos->size(0) >= seq, "embed_bwd: position table too small");
       pp = dpos->data_ptr<float>();
     }
+    MCCL_CHECK_TENSOR(tp != nullptr || pp != nullptr, "embed_bwd: no gradient buffer given");
     c10::cuda::CUDAGuard guard(ids.device());
-    check_launch(ops::embed_bwd(reinterpret_cast<const long long*>(ids.data_ptr<int64_t>()), bf(dy), dtok.data_ptr<float>(), pp,
-                                static_cast<int>(ids.numel()), static_cast<int>(seq), static_cast<int>(dtok.size(1)),
-                                static_cast<int>(dtok.size(0)), stream_of(ids)),
+    check_launch(ops::embed_bwd(reinterpret_cast<const long long*>(ids.data_ptr<int64_t>()), bf(dy), tp, pp,
+                                static_cast<int>(ids.numel()), static_cast<int>(seq), static_cast<int>(dim),
+                                static_cast<int>(vocab), stream_of(ids), static_cast<float>(scale)),
                  "embed_bwd");
-  }, py::arg("ids"), py::arg("dy"), py::arg("dtok"), py::arg("dpos") = py::none(), py::arg("seq") = 1);
+  }, py::arg("ids"), py::arg("dy"), py::arg("dtok"), py::arg("dpos") = py::none(), py::arg("seq") = 1, py::arg("scale") = 1.0,
+        "Adds scale * dy[t] into dtok[ids[t]] and dpos[t % seq] (either table may be None).");
 }
 
 }  // namespace mccl

@@ -348,14 +348,19 @@ __global__ void __launch_bounds__(256) adamw_kernel(float* __restrict__ p, float
 }
 
 cudaError_t adamw_flat(float* p, float* g, float* m, float* v, __nv_bfloat16* p16, long long n, float lr, float beta1,
-                       float beta2, float eps, float wd, const float* step, float grad_scale, cudaStream_t stream, bool zero_grad) {
+                       float beta2, float eps, float wd, const float* step, float grad_scale, cudaStream_t stream, bool zero_grad,
+                       int ctas_per_sm) {
   if (n <= 0) return cudaSuccess;
   if ((reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(m) |
        reinterpret_cast<uintptr_t>(v)) & 15u)
     return cudaErrorNotSupported;
   const long long n4 = n / 4;
+  // The CTAs stride over the buffer and live as long as the kernel: eight of 256 threads fill an SM, so a kernel
+  // launched beside this one (a collective of the buckets still in flight) would wait for the whole update.
+  // ctas_per_sm < 8 leaves it room.
+  if (ctas_per_sm < 1 || ctas_per_sm > 8) ctas_per_sm = 8;
   long long blocks = (n4 + 255) / 256;
-  if (blocks > 148 * 8) blocks = 148 * 8;
+  if (blocks > 148 * ctas_per_sm) blocks = 148 * ctas_per_sm;
   if (blocks < 1) blocks = 1;
   MCCL_LAUNCH_PDL(adamw_kernel, static_cast<int>(blocks), 256, 0, stream, p, g, m, v, p16, n4, n, lr, beta1, beta2, eps, wd, step, grad_scale,
               zero_grad ? 1 : 0);
@@ -569,7 +574,7 @@ __global__ void __launch_bounds__(256) embed_fwd_kernel(const long long* __restr
 
 __global__ void __launch_bounds__(256) embed_bwd_kernel(const long long* __restrict__ ids, const __nv_bfloat16* __restrict__ dy,
                                                         float* __restrict__ dtok, float* __restrict__ dpos, long long n8, int seq,
-                                                        int dim8, int vocab) {
+                                                        int dim8, int vocab, float scale) {
   // dependent launch: the CTA may be resident before the previous kernel of the stream has finished
   ::mccl::pdl_trigger();
   ::mccl::pdl_wait();
@@ -579,9 +584,10 @@ __global__ void __launch_bounds__(256) embed_bwd_kernel(const long long* __restr
     const int c = static_cast<int>(i % dim8);
     float g[8];
     unpack8(reinterpret_cast<const uint4*>(dy)[i], g);
-    const float4 lo = make_float4(g[0], g[1], g[2], g[3]), hi = make_float4(g[4], g[5], g[6], g[7]);
+    const float4 lo = make_float4(g[0] * scale, g[1] * scale, g[2] * scale, g[3] * scale);
+    const float4 hi = make_float4(g[4] * scale, g[5] * scale, g[6] * scale, g[7] * scale);
     const long long id = ids[t];
-    if (id >= 0 && id < vocab) {
+    if (dtok != nullptr && id >= 0 && id < vocab) {
       float4* row = reinterpret_cast<float4*>(dtok + id * dim8 * 8) + 2 * c;
       atomicAdd(row, lo);
       atomicAdd(row + 1, hi);
@@ -610,10 +616,10 @@ cudaError_t embed_fwd(const long long* ids, const float* tok, const float* pos, 
 }
 
 cudaError_t embed_bwd(const long long* ids, const __nv_bfloat16* dy, float* dtok, float* dpos, int tokens, int seq, int dim,
-                      int vocab, cudaStream_t stream) {
+                      int vocab, cudaStream_t stream, float scale) {
   if (dim % 8 != 0 || tokens <= 0 || seq <= 0) return cudaErrorNotSupported;
   const long long n8 = static_cast<long long>(tokens) * (dim / 8);
-  MCCL_LAUNCH_PDL(embed_bwd_kernel, embed_blocks(n8), 256, 0, stream, ids, dy, dtok, dpos, n8, seq, dim / 8, vocab);
+  MCCL_LAUNCH_PDL(embed_bwd_kernel, embed_blocks(n8), 256, 0, stream, ids, dy, dtok, dpos, n8, seq, dim / 8, vocab, scale);
   count_launch();
   return ::mccl::launch_status();
 }

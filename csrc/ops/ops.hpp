@@ -42,7 +42,7 @@ int colsum_slabs(int rows);
 // is cleared in the same pass (it has just been read), which replaces the memset at the start of the next step.
 cudaError_t adamw_flat(float* p, float* g, float* m, float* v, __nv_bfloat16* p16, long long n, float lr, float beta1,
                        float beta2, float eps, float wd, const float* step, float grad_scale, cudaStream_t stream,
-                       bool zero_grad = false);
+                       bool zero_grad = false, int ctas_per_sm = 8);
 
 // ---- softmax cross entropy, forward and backward in one pass over the logits:
 // loss_rows[t] = logsumexp(logits[t]) - logits[t, target[t]];
@@ -63,7 +63,7 @@ cudaError_t embed_fwd(const long long* ids, const float* tok, const float* pos, 
                       int vocab, cudaStream_t stream);
 // Adds dy[t, :] into dtok[ids[t], :] and dpos[t % seq, :] (fp32, atomically; dpos may be null).
 cudaError_t embed_bwd(const long long* ids, const __nv_bfloat16* dy, float* dtok, float* dpos, int tokens, int seq, int dim,
-                      int vocab, cudaStream_t stream);
+                      int vocab, cudaStream_t stream, float scale = 1.f);
 
 // ---- causal self-attention, head dimension 64, straight from the fused QKV projection.
 // qkv: [B, S, 3, H, 64] bf16; o: [B, S, H, 64] bf16; lse: [B, H, S] fp32 (log2 domain, saved for backward).

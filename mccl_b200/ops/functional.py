@@ -107,10 +107,10 @@ def linear_cross_entropy(h: torch.Tensor, weight: torch.Tensor, targets: torch.T
     return F.cross_entropy(logits.float(), targets)
 
 
-def adamw_step(p, g, m, v, lr, beta1, beta2, eps, wd, step, p_bf16=None, grad_scale=1.0, zero_grad=False):
+def adamw_step(p, g, m, v, lr, beta1, beta2, eps, wd, step, p_bf16=None, grad_scale=1.0, zero_grad=False, ctas_per_sm=8):
     """In-place fused AdamW over flat fp32 tensors (optionally refreshing a bf16 copy of p and clearing g)."""
     if p.is_cuda and _HAS["adamw_flat"]:
-        _C.adamw_flat(p, g, m, v, p_bf16, lr, beta1, beta2, eps, wd, step, grad_scale, zero_grad)
+        _C.adamw_flat(p, g, m, v, p_bf16, lr, beta1, beta2, eps, wd, step, grad_scale, zero_grad, ctas_per_sm)
         return
     g_buf = g
     g = g * grad_scale if grad_scale != 1.0 else g
