@@ -35,14 +35,17 @@ def _notify(p: torch.Tensor) -> None:
 
 # Weight-gradient GEMMs have no consumer until the gradient is reduced or applied, so a trainer can give them a
 # stream of their own: they then run beside the input-gradient chain and fill the SMs its small kernels leave idle.
-_wgrad = {"stream": None, "pending": False}
+_wgrad = {"stream": None, "pending": False, "side_ctas": 0, "main_ctas": 0}
 _SIDE_COLSUM = __import__("os").environ.get("MCCL_SIDE_COLSUM", "1") != "0"
 
 
-def set_wgrad_stream(stream) -> None:
-    """Side stream for weight-gradient GEMMs that write into a trainer's gradient buffer (None: current stream)."""
+def set_wgrad_stream(stream, main_ctas: int = 0, side_ctas: int = 0) -> None:
+    """Side stream for weight-gradient GEMMs that write into a trainer's gradient buffer (None: current stream).
+    main_ctas / side_ctas: CTA caps of the GEMMs on the caller's stream and on the side stream while it is set
+    (0: no cap); with caps that add up to the SM count a GEMM of one stream never waits for CTAs of the other."""
     _wgrad["stream"] = stream
     _wgrad["pending"] = False
+    _wgrad["main_ctas"], _wgrad["side_ctas"] = main_ctas, side_ctas
 
 
 def mark_wgrad_pending() -> None:
@@ -64,8 +67,12 @@ def _wgrad_gemm(a_mat: torch.Tensor, b_mat: torch.Tensor, sink: torch.Tensor) ->
         _C.gemm_bf16(a_mat, b_mat, None, "none", True, sink, True, True, True)
         return
     s.wait_stream(torch.cuda.current_stream())
+    if _wgrad["side_ctas"]:
+        _C.set_gemm_cta_limit(_wgrad["side_ctas"])
     with torch.cuda.stream(s):
         _C.gemm_bf16(a_mat, b_mat, None, "none", True, sink, True, True, True)
+    if _wgrad["side_ctas"]:
+        _C.set_gemm_cta_limit(_wgrad["main_ctas"])
     a_mat.record_stream(s)
     b_mat.record_stream(s)
     _wgrad["pending"] = True
