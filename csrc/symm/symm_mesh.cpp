@@ -178,8 +178,20 @@ struct SymmAlloc::Priv {
   CUdevice cu_dev = 0;
   void* ipc_opened[kSymmMaxRanks] = {};
   void* owned[kSymmMaxRanks] = {};  // cudaMalloc'd blocks (IPC: own block, LOCAL: all)
+  int device = -1;                  // CUDA device the mappings belong to
 
   ~Priv() {
+    // Unmapping is immediate, not stream-ordered: kernels this process has queued on the allocation (the views it hands
+    // out are ordinary tensors) must have finished first, or they touch unmapped addresses.  A peer that still reads
+    // this rank's block keeps it alive through its own imported handle.
+    if (device >= 0) {
+      int cur = -1;
+      if (cudaGetDevice(&cur) == cudaSuccess) {
+        if (cur != device) cudaSetDevice(device);
+        cudaDeviceSynchronize();
+        if (cur != device && cur >= 0) cudaSetDevice(cur);
+      }
+    }
     // Teardown is best effort: the context may already be gone at exit.
     const CuDriver& cu = CuDriver::get();
     if (mode == SymmMesh::Mode::VMM && cu.loaded) {
@@ -283,6 +295,7 @@ std::shared_ptr<SymmAlloc> SymmMesh::alloc_local(size_t bytes) {
   auto a = std::make_shared<SymmAlloc>();
   a->priv = std::make_shared<SymmAlloc::Priv>();
   a->priv->mode = Mode::LOCAL;
+  a->priv->device = device_;
   a->bytes = (bytes + 255) / 256 * 256;
   a->world = world_;
   a->rank = 0;
@@ -300,6 +313,7 @@ std::shared_ptr<SymmAlloc> SymmMesh::alloc_ipc(size_t bytes) {
   auto a = std::make_shared<SymmAlloc>();
   a->priv = std::make_shared<SymmAlloc::Priv>();
   a->priv->mode = Mode::IPC;
+  a->priv->device = device_;
   a->bytes = (bytes + 255) / 256 * 256;
   a->world = world_;
   a->rank = rank_;
@@ -335,6 +349,7 @@ std::shared_ptr<SymmAlloc> SymmMesh::alloc_vmm(size_t bytes, bool want_mc) {
   a->priv = std::make_shared<SymmAlloc::Priv>();
   SymmAlloc::Priv& pv = *a->priv;
   pv.mode = Mode::VMM;
+  pv.device = device_;
   pv.world = world_;
   pv.rank = rank_;
   a->world = world_;
@@ -373,9 +388,14 @@ std::shared_ptr<SymmAlloc> SymmMesh::alloc_vmm(size_t bytes, bool want_mc) {
   server_->publish(a->id, 0, my_fd);
 
   // 2. import every peer's block
-  std::vector<std::string> names(world_);
-  for (int r = 0; r < world_; ++r)
-    if (r != rank_) names[r] = store_->get_str(prefix_ + "/uds/" + std::to_string(r), timeout_ms_);
+  // the peers' socket names never change: asked from the store once per mesh, not once per allocation
+  if (peer_names_.empty()) {
+    std::vector<std::string> fetched(world_);
+    for (int r = 0; r < world_; ++r)
+      if (r != rank_) fetched[r] = store_->get_str(prefix_ + "/uds/" + std::to_string(r), timeout_ms_);
+    peer_names_ = std::move(fetched);
+  }
+  const std::vector<std::string>& names = peer_names_;
   for (int r = 0; r < world_; ++r) {
     if (r == rank_) continue;
     int fd = FdServer::fetch(names[r], a->id, 0, timeout_ms_);

@@ -87,6 +87,7 @@ class SymmMesh {
   bool multicast_ = false;
   uint32_t next_id_ = 0;
   std::unique_ptr<FdServer> server_;
+  std::vector<std::string> peer_names_;   // fd servers of the peers (VMM mode), looked up at the first allocation
 };
 
 }  // namespace mccl
