@@ -189,6 +189,7 @@ void bind_comm(py::module_& m) {
       .def_property_readonly("device_timeout_ms", &DeviceComm::device_timeout_ms)
       .def_property_readonly("max_ctas", &DeviceComm::max_ctas)
       .def_property_readonly("launch_threads", &DeviceComm::launch_threads)
+      .def_property_readonly("launch_shape_auto", &DeviceComm::launch_shape_auto)
       .def("set_launch_shape", &DeviceComm::set_launch_shape, py::arg("max_ctas") = 0, py::arg("threads") = 0)
       .def("decide_allreduce",
            [](DeviceComm& c, const std::string& algo, int64_t numel, at::ScalarType dt, const std::string& op,

@@ -149,8 +149,9 @@ class DeviceComm {
   // Geometry of the collective kernels launched from now on: at most `max_ctas` CTAs of `threads` threads
   // (0 keeps the current value, threads < 0 restores the default).  512-thread CTAs need a whole register file and so only run on SMs that
   // hold no persistent GEMM CTA; a trainer that leaves k SMs free of GEMM work asks for (k, 512).
-  void set_launch_shape(int max_ctas, int threads);
+  void set_launch_shape(int max_ctas, int threads);   // max_ctas < 0: back to the defaults (and automatic shaping)
   int max_ctas() const;
+  bool launch_shape_auto() const;   // no shape was asked for: large messages take every CTA, 512 threads each
   int launch_threads() const;   // 0 = kernel default
 
   SymmMesh& mesh() { return *mesh_; }

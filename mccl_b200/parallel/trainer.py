@@ -265,9 +265,15 @@ class DDPTrainer:
             stream.wait_stream(main)
         _native.join_wgrad(stream)   # the bucket's weight gradients may still be running on their own stream
         shaped = self.comm is not None and (self.comm_sms > 0 or self.comm_threads > 0) and self._in_backward and not b.tail
+        was_auto = self.comm is not None and self.comm.launch_shape_auto
         if shaped:
             saved = (self.comm.max_ctas, self.comm.launch_threads)
             self.comm.set_launch_shape(self.comm_sms, self.comm_threads)
+        elif was_auto:
+            # tail buckets run beside the optimizer update: keep the compact default shape (the automatic shape for
+            # large messages wants 512 free thread slots on 128 SMs and would wait for the update to finish)
+            saved = (self.comm.max_ctas, self.comm.launch_threads)
+            self.comm.set_launch_shape(saved[0], 256)
         with torch.cuda.stream(stream):
             if self.comm is not None:
                 if self.wire == "bf16":
@@ -281,7 +287,9 @@ class DDPTrainer:
                     self._body_done = torch.cuda.Event()
                 self._body_done.record(stream)
                 self._body_recorded = True
-        if shaped:
+        if was_auto:
+            self.comm.set_launch_shape(-1, -1)
+        elif shaped:
             self.comm.set_launch_shape(saved[0], saved[1] if saved[1] > 0 else -1)
 
     # ---------------------------------------------------------------- step --
