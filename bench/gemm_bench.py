@@ -54,7 +54,11 @@ def main():
     ap.add_argument("--model", default="70m")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--shape", type=int, nargs=3, metavar=("M", "N", "K"), help="time one forward GEMM of this shape only")
+    ap.add_argument("--kernel", default="", choices=["", "pair", "persistent", "tile"],
+                    help="which of this package's GEMM kernels to time (default: the package's default, CTA pairs)")
     args = ap.parse_args()
+    if args.kernel:
+        C.set_gemm_kernel(args.kernel)
     peak = None
     p = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
     if os.path.exists(p):
